@@ -1,0 +1,185 @@
+/*
+ * C ABI of the sm_100a backend for libnd4j's legacy op families.
+ *
+ * Each entry point replaces one family of member functions of the reference's NativeOps class
+ * (blas/NativeOps.h; CUDA implementation blas/cuda/NativeOps.cu). The Float / Double / Half
+ * flavours of the reference collapse into one function with a `dtype` argument
+ * (ND4JB200_FLOAT / _DOUBLE / _HALF); op numbers are the reference's (include/loops/legacy_ops.h).
+ *
+ * Conventions, identical for every call:
+ *   - x, y, z, scalars, extraParams / extraArguments are DEVICE pointers owned by the caller
+ *     (as in the reference's CUDA build). extraParams may be NULL when the op reads none.
+ *   - every *ShapeInfo and `dimension` argument is a HOST pointer. The reference's CUDA build
+ *     receives the same host copies through extraPointers[0], [7], [8], [9]
+ *     (blas/cuda/NativeOps.cu:2107-2118); here they are explicit arguments.
+ *   - `stream` is a cudaStream_t (NULL = default stream). Calls are asynchronous on it, except
+ *     the *_scalar calls, which synchronise the stream and return the value through `result`,
+ *     as the reference's scalar calls do (blas/cuda/NativeOps.cu:2209-2232).
+ *   - the return value is 0 on success, otherwise one of the ND4JB200_E* codes;
+ *     nd4jb200_last_error() then describes the failure (thread-local string).
+ *   - nothing here falls back to the CPU: without a usable GPU every compute call fails with
+ *     ND4JB200_ECUDA.
+ */
+#ifndef ND4J_B200_H
+#define ND4J_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef long long Nd4jLong;   /* include/pointercast.h:10-12 */
+typedef void *Nd4jPointer;
+
+enum { ND4JB200_FLOAT = 0, ND4JB200_DOUBLE = 1, ND4JB200_HALF = 2 };
+enum {
+    ND4JB200_OK = 0, ND4JB200_EARG = 1, ND4JB200_EOP = 2, ND4JB200_EUNSUPPORTED = 3,
+    ND4JB200_ECUDA = 4, ND4JB200_ETOOLARGE = 5
+};
+
+const char *nd4jb200_last_error(void);
+/* kernels launched by this library since it was loaded */
+unsigned long long nd4jb200_launch_count(void);
+
+/* ---- reduce: NativeOps::execReduce{Float,Double,Half} along dimension
+ *      (blas/NativeOps.h:845-876; blas/cuda/NativeOps.cu:2098-2185) ------------------------- */
+int nd4jb200_exec_reduce(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                         const void *extraParams, void *z, const Nd4jLong *zShapeInfo,
+                         const int *dimension, int dimensionLength);
+/* NativeOps::execReduceScalar* (blas/NativeOps.h:886-906; blas/cuda/NativeOps.cu:2195-2233) */
+int nd4jb200_exec_reduce_scalar(void *stream, int dtype, int opNum, const void *x,
+                                const Nd4jLong *xShapeInfo, const void *extraParams, double *result);
+
+/* ---- indexreduce: NativeOps::execIndexReduce* (blas/NativeOps.h:576-602;
+ *      blas/cuda/NativeOps.cu:1699-1781). Indices are written in the element type, as in the
+ *      reference (include/loops/cpu/indexreduce.cpp:206,223). ---------------------------------- */
+int nd4jb200_exec_index_reduce(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                               const void *extraParams, void *z, const Nd4jLong *zShapeInfo,
+                               const int *dimension, int dimensionLength);
+/* NativeOps::execIndexReduceScalar* (blas/NativeOps.h:544-563) */
+int nd4jb200_exec_index_reduce_scalar(void *stream, int dtype, int opNum, const void *x,
+                                      const Nd4jLong *xShapeInfo, const void *extraParams, double *result);
+
+/* ---- summarystats: NativeOps::execSummaryStats* (blas/NativeOps.h:1291-1325;
+ *      blas/cuda/NativeOps.cu:2957-3020) and execSummaryStatsScalar* (:1223-1242) ---------- */
+int nd4jb200_exec_summary_stats(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                                const void *extraParams, void *z, const Nd4jLong *zShapeInfo,
+                                const int *dimension, int dimensionLength, int biasCorrected);
+int nd4jb200_exec_summary_stats_scalar(void *stream, int dtype, int opNum, const void *x,
+                                       const Nd4jLong *xShapeInfo, const void *extraParams,
+                                       int biasCorrected, double *result);
+
+/* ---- reduce3: NativeOps::execReduce3* along dimension (blas/NativeOps.h:998-1034;
+ *      blas/cuda/NativeOps.cu:2502-2629) and execReduce3Scalar* (blas/NativeOps.h:962-986).
+ *      When one operand holds exactly one TAD it is paired with every TAD of the other. ---- */
+int nd4jb200_exec_reduce3(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                          const void *extraParams, const void *y, const Nd4jLong *yShapeInfo,
+                          void *z, const Nd4jLong *zShapeInfo, const int *dimension, int dimensionLength);
+int nd4jb200_exec_reduce3_scalar(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                                 const void *extraParams, const void *y, const Nd4jLong *yShapeInfo,
+                                 double *result);
+
+/* ---- transform: NativeOps::execTransform* shaped and strided (blas/NativeOps.h:1337-1443;
+ *      blas/cuda/NativeOps.cu:3033-3343) -------------------------------------------------------- */
+int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                            void *z, const Nd4jLong *zShapeInfo, const void *extraParams);
+int nd4jb200_exec_transform_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
+                                    void *z, Nd4jLong zStride, const void *extraParams, Nd4jLong n);
+
+/* ---- pairwise transform: NativeOps::execPairwiseTransform* (blas/NativeOps.h:665-798;
+ *      blas/cuda/NativeOps.cu:1883-2005) -------------------------------------------------------- */
+int nd4jb200_exec_pairwise(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                           const void *y, const Nd4jLong *yShapeInfo, void *z, const Nd4jLong *zShapeInfo,
+                           const void *extraParams);
+int nd4jb200_exec_pairwise_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
+                                   const void *y, Nd4jLong yStride, void *z, Nd4jLong zStride,
+                                   const void *extraParams, Nd4jLong n);
+
+/* ---- broadcast: NativeOps::execBroadcast* (blas/NativeOps.h:615-649;
+ *      blas/cuda/NativeOps.cu:1795-1867) -------------------------------------------------------- */
+int nd4jb200_exec_broadcast(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                            const void *y, const Nd4jLong *yShapeInfo, void *z, const Nd4jLong *zShapeInfo,
+                            const int *dimension, int dimensionLength);
+
+/* ---- scalar: NativeOps::execScalar* shaped / strided / along dimension
+ *      (blas/NativeOps.h:1046-1214; blas/cuda/NativeOps.cu:2642-2816, 5135-5190) ------------ */
+int nd4jb200_exec_scalar(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                         void *z, const Nd4jLong *zShapeInfo, double scalar, const void *extraParams);
+int nd4jb200_exec_scalar_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
+                                 void *z, Nd4jLong zStride, double scalar, const void *extraParams, Nd4jLong n);
+int nd4jb200_exec_scalar_along_dimension(void *stream, int dtype, int opNum, const void *x,
+                                         const Nd4jLong *xShapeInfo, const void *extraParams, void *z,
+                                         const Nd4jLong *zShapeInfo, const void *scalars,
+                                         const int *dimension, int dimensionLength);
+
+/* ---- random: NativeOps::initRandom / refreshBuffer / reSeedBuffer / destroyRandom
+ *      (blas/NativeOps.h:2510-2539; blas/cuda/NativeOps.cu:5384-5447) and execRandom* in its
+ *      three arities (blas/NativeOps.h:2327-2505; blas/cuda/NativeOps.cu:5312-5382).
+ *      hostTable / deviceTable may be NULL, in which case the library allocates them. The state
+ *      handle is a host object; execRandom advances it by length(z) like RandomBuffer::rewindH
+ *      (include/helpers/helper_generator.h:322-334). ------------------------------------------- */
+Nd4jPointer nd4jb200_init_random(void *stream, Nd4jLong seed, Nd4jLong bufferSize, void *hostTable,
+                                 void *deviceTable);
+int nd4jb200_refresh_buffer(void *stream, Nd4jLong seed, Nd4jPointer state);
+int nd4jb200_reseed_buffer(Nd4jLong seed, Nd4jPointer state);
+int nd4jb200_destroy_random(Nd4jPointer state);
+int nd4jb200_exec_random(void *stream, int dtype, int opNum, Nd4jPointer state, void *z,
+                         const Nd4jLong *zShapeInfo, const void *extraArguments);
+int nd4jb200_exec_random_x(void *stream, int dtype, int opNum, Nd4jPointer state, const void *x,
+                           const Nd4jLong *xShapeInfo, void *z, const Nd4jLong *zShapeInfo,
+                           const void *extraArguments);
+int nd4jb200_exec_random_xy(void *stream, int dtype, int opNum, Nd4jPointer state, const void *x,
+                            const Nd4jLong *xShapeInfo, const void *y, const Nd4jLong *yShapeInfo,
+                            void *z, const Nd4jLong *zShapeInfo, const void *extraArguments);
+/* Offset-sharded generation: produces elements [first, first+count) of a logical call of
+ * `length` elements into dense buffers that hold only that range (x, y, z point at the range's
+ * first element). The state is NOT advanced; the owner of the logical call advances it once
+ * with nd4jb200_rng_rewind(state, length). `first` must be even for the Gaussian family.
+ * arity: 0 = z only, 1 = x, 2 = x and y (pass y == z to take the mean from extraArguments[0]). */
+int nd4jb200_exec_random_range(void *stream, int dtype, int opNum, int arity, Nd4jPointer state,
+                               const void *x, const void *y, void *z, const void *extraArguments,
+                               Nd4jLong first, Nd4jLong count, Nd4jLong length);
+int nd4jb200_rng_rewind(Nd4jPointer state, Nd4jLong count);
+/* words: seed, currentPosition, generation, amplifier, size (RandomBuffer fields,
+ * include/helpers/helper_generator.h:64-74) */
+int nd4jb200_rng_get_state(Nd4jPointer state, Nd4jLong words[5]);
+int nd4jb200_rng_set_state(Nd4jPointer state, const Nd4jLong words[4]);
+void *nd4jb200_rng_device_table(Nd4jPointer state);
+
+/* ---- shape helpers: NativeOps::tadOnlyShapeInfo (blas/NativeOps.h:1880;
+ *      blas/cuda/NativeOps.cu:4781-4791). target needs 2*rank+4 longs, offsets numTads. ------- */
+int nd4jb200_tad_only_shape_info(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength,
+                                 Nd4jLong *target, Nd4jLong *offsets);
+Nd4jLong nd4jb200_tad_count(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength);
+
+/* ---- device / memory / stream utilities the same object offers
+ *      (blas/NativeOps.h:1607-1870; blas/cuda/NativeOps.cu:3854-4260) ------------------------- */
+int nd4jb200_get_available_devices(void);
+int nd4jb200_set_device(int device);
+int nd4jb200_get_device(void);
+Nd4jPointer nd4jb200_malloc_device(Nd4jLong bytes);
+int nd4jb200_free_device(Nd4jPointer p);
+Nd4jPointer nd4jb200_malloc_host(Nd4jLong bytes);   /* pinned */
+int nd4jb200_free_host(Nd4jPointer p);
+Nd4jPointer nd4jb200_create_stream(void);
+int nd4jb200_destroy_stream(Nd4jPointer stream);
+int nd4jb200_stream_synchronize(Nd4jPointer stream);
+Nd4jPointer nd4jb200_create_event(void);
+int nd4jb200_register_event(Nd4jPointer event, Nd4jPointer stream);
+int nd4jb200_event_synchronize(Nd4jPointer event);
+int nd4jb200_destroy_event(Nd4jPointer event);
+/* milliseconds between two recorded events (cudaEventElapsedTime) */
+int nd4jb200_event_elapsed_ms(Nd4jPointer start, Nd4jPointer stop, float *ms);
+/* flags: 0 host->host, 1 host->device, 2 device->host, 3 device->device (NativeOps.cu:4038-4075) */
+int nd4jb200_memcpy_async(Nd4jPointer dst, Nd4jPointer src, Nd4jLong bytes, int flags, Nd4jPointer stream);
+int nd4jb200_memcpy(Nd4jPointer dst, Nd4jPointer src, Nd4jLong bytes, int flags);
+int nd4jb200_memset_async(Nd4jPointer dst, int value, Nd4jLong bytes, Nd4jPointer stream);
+Nd4jLong nd4jb200_device_free_memory(int device);
+Nd4jLong nd4jb200_device_total_memory(int device);
+int nd4jb200_device_major(int device);
+int nd4jb200_device_minor(int device);
+const char *nd4jb200_device_name(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ND4J_B200_H */

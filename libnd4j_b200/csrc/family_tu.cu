@@ -1,0 +1,167 @@
+// One translation unit per (family, element type): instantiates that family's kernels for every
+// opNum of the reference's table and exposes a switch-based dispatcher.
+//   ND_DTYPE:  0 float, 1 double, 2 half
+//   ND_FAMILY: 0 transform, 1 binary (pairwise, scalar, broadcast, scalar-along-dimension),
+//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random
+#include "dispatch.h"
+#include "functors.cuh"
+#include "policies.cuh"
+
+#if ND_DTYPE == 0
+#define ND_T float
+#define ND_S(name) name##_f32
+#elif ND_DTYPE == 1
+#define ND_T double
+#define ND_S(name) name##_f64
+#else
+#define ND_T __half
+#define ND_S(name) name##_f16
+#endif
+
+namespace nd4jb200 {
+
+typedef Elem<ND_T>::C CT;
+
+#if ND_FAMILY == 0
+Status ND_S(transform)(int opNum, const EwArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 1>(a, st);
+        ND_TRANSFORM_TABLE(X)
+#undef X
+        case 36: case 37: case 38: case 39: case 40: case 41: case 48: case 70: case 71:
+            return unsupported("transform opNum " + std::to_string(opNum) +
+                               " is a composite (special) transform, not an elementwise functor");
+        case 43: case 44:
+            return unsupported("transform DropOut/DropOutInverted draw from rand()/clock in the reference and are "
+                               "not reproducible; use the random family (execRandom opNum 1/2)");
+        default: return unknown_op("transform", opNum);
+    }
+}
+#elif ND_FAMILY == 1
+Status ND_S(pairwise)(int opNum, const EwArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 2>(a, st);
+        ND_PAIRWISE_TABLE(X)
+#undef X
+        default: return unknown_op("pairwise transform", opNum);
+    }
+}
+Status ND_S(scalar)(int opNum, const EwArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 3>(a, st);
+        ND_SCALAR_TABLE(X)
+#undef X
+        default: return unknown_op("scalar", opNum);
+    }
+}
+Status ND_S(broadcast)(int opNum, const BcArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_broadcast<ND_T, fn::Name, false>(a, st);
+        ND_BROADCAST_TABLE(X)
+#undef X
+        default: return unknown_op("broadcast", opNum);
+    }
+}
+Status ND_S(scalar_tad)(int opNum, const BcArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_broadcast<ND_T, fn::Name, true>(a, st);
+        ND_SCALAR_TABLE(X)
+#undef X
+        default: return unknown_op("scalar along dimension", opNum);
+    }
+}
+#elif ND_FAMILY == 2
+Status ND_S(reduce)(int opNum, const ReduceCall &c, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_reduction<ND_T, pol::Reduce<fn::Name, CT> >(c, st);
+        ND_REDUCE_TABLE(X)
+#undef X
+        case 19: return run_reduction<ND_T, pol::LogSumExp<CT> >(c, st);
+        default: return unknown_op("reduce", opNum);
+    }
+}
+#elif ND_FAMILY == 3
+Status ND_S(reduce3)(int opNum, const ReduceCall &c, cudaStream_t st) {
+    switch (opNum) {
+        case 0: return run_reduction<ND_T, pol::Reduce3<0, CT> >(c, st);
+        case 1: return run_reduction<ND_T, pol::Reduce3<1, CT> >(c, st);
+        case 2: return run_reduction<ND_T, pol::Reduce3<2, CT> >(c, st);
+        case 3: return run_reduction<ND_T, pol::Reduce3<3, CT> >(c, st);
+        case 4: return run_reduction<ND_T, pol::Reduce3<4, CT> >(c, st);
+        case 5: return run_reduction<ND_T, pol::Reduce3<5, CT> >(c, st);
+        case 6: return run_reduction<ND_T, pol::Reduce3<6, CT> >(c, st);
+        case 7: return run_reduction<ND_T, pol::Reduce3<7, CT> >(c, st);
+        default: return unknown_op("reduce3", opNum);
+    }
+}
+Status ND_S(index_reduce)(int opNum, const ReduceCall &c, cudaStream_t st) {
+    switch (opNum) {
+        case 0: return run_reduction<ND_T, pol::IndexExtreme<0, CT> >(c, st);
+        case 1: return run_reduction<ND_T, pol::IndexExtreme<1, CT> >(c, st);
+        case 2: return run_reduction<ND_T, pol::IndexExtreme<2, CT> >(c, st);
+        case 3: return run_reduction<ND_T, pol::IndexExtreme<3, CT> >(c, st);
+        case 4: return run_reduction<ND_T, pol::IndexMatch<4, CT> >(c, st);
+        case 5: return run_reduction<ND_T, pol::IndexMatch<5, CT> >(c, st);
+        default: return unknown_op("index reduce", opNum);
+    }
+}
+Status ND_S(summary_stats)(int opNum, const ReduceCall &c, cudaStream_t st) {
+    switch (opNum) {
+        case 0: return run_reduction<ND_T, pol::Stats<0, CT> >(c, st);
+        case 1: return run_reduction<ND_T, pol::Stats<1, CT> >(c, st);
+        default: return unknown_op("summary stats", opNum);
+    }
+}
+#elif ND_FAMILY == 4
+template <int OP, int ARITY>
+static Status launch_random(const RngArgs &a, cudaStream_t st) {
+    if (a.count <= 0) return kOk;
+    constexpr int V = Elem<ND_T>::kVec;
+    LL work = a.mode == 0 ? ceil_div(a.count, V) : a.count;
+    LL blocks = ceil_div(work, kRngBlock);
+    const LL cap = (LL) kNumSMs * 32;
+    if (blocks > cap) blocks = cap;
+    k_random<ND_T, OP, ARITY><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
+    count_launch();
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+template <bool LOGNORMAL>
+static Status launch_gaussian(const RngArgs &a, cudaStream_t st) {
+    if (a.count <= 0) return kOk;
+    LL blocks = ceil_div(ceil_div(a.count, 2), kRngBlock);
+    const LL cap = (LL) kNumSMs * 32;
+    if (blocks > cap) blocks = cap;
+    k_random_gaussian<ND_T, LOGNORMAL><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
+    count_launch();
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+template <int OP>
+static Status by_arity(int arity, const RngArgs &a, cudaStream_t st) {
+    if (arity == 0) return launch_random<OP, 0>(a, st);
+    if (arity == 1) return launch_random<OP, 1>(a, st);
+    return launch_random<OP, 2>(a, st);
+}
+Status ND_S(random)(int opNum, int arity, const RngArgs &a, cudaStream_t st) {
+    switch (opNum) {
+        case 0: return by_arity<0>(arity, a, st);
+        case 1: return by_arity<1>(arity, a, st);
+        case 2: return by_arity<2>(arity, a, st);
+        case 3: return by_arity<3>(arity, a, st);
+        case 4: return by_arity<4>(arity, a, st);
+        case 7: return by_arity<7>(arity, a, st);
+        case 12: return by_arity<12>(arity, a, st);
+        case 13: return by_arity<13>(arity, a, st);
+        case 100: return by_arity<100>(arity, a, st);
+        case 6: return launch_gaussian<false>(a, st);    // reached only in the three-operand form
+        case 10: return launch_gaussian<true>(a, st);
+        case 5: case 8: case 9: case 11:
+            return unsupported("random opNum " + std::to_string(opNum) +
+                               " (Choice / Binomial / BinomialEx / TruncatedNormal) is not served yet");
+        default: return unknown_op("random", opNum);
+    }
+}
+#endif
+
+}  // namespace nd4jb200

@@ -1,0 +1,228 @@
+// Reduction engine shared by the reduce, reduce3, indexreduce and summarystats families.
+//
+// A reduction call is "for every TAD r: z[r] = finish(fold(elements of TAD r))". The host
+// plan (shape_host.h) describes the TADs as two views: `outer` maps r to the TAD's base offset
+// and `inner` maps an element index j (c-order inside the TAD) to an offset from that base.
+// Two memory patterns get their own kernels so that global loads stay coalesced:
+//
+//   along-TAD  (k_reduce_tads): consecutive elements of one TAD are (close to) adjacent in
+//              memory. A group of g threads (1..32 lanes of a warp, or a whole 256-thread CTA)
+//              walks one TAD segment with 128-bit loads when alignment allows.
+//   across-TAD (k_reduce_cols): consecutive TADs are adjacent in memory and a TAD's own
+//              elements are far apart (column reductions of row-major arrays, row reductions of
+//              f-order views). 32 lanes read 32 neighbouring TADs per row; 8 row-lanes per CTA
+//              and `splits` CTAs share the rows of one TAD tile.
+//
+// A TAD may be cut into `splits` segments handled by different groups/CTAs; each writes its
+// partial state to a scratch array and k_reduce_finalize merges the partials of a TAD in
+// segment order. All merges (lanes, warps, segments) happen in an order fixed by indices, never
+// by arrival, so a call is bit-reproducible run to run.
+//
+// Policy concept (see policies.cuh):
+//   typedef State;  static constexpr int kInputs (1|2), kParams;
+//   init(State&);  accum(State&, C x, C y, LL j, const C* p);  merge(State&, const State&);
+//   C finish(const State&, LL n, const C* p);
+#pragma once
+#include "device_utils.cuh"
+
+namespace nd4jb200 {
+
+struct ReduceArgs {
+    const void *x;
+    const void *y;       // second operand (reduce3) or null
+    const void *extra;   // device extra parameters or null
+    void *z;             // one result per TAD, written densely
+    void *partials;      // scratch for split TADs: State[numTads * splits]
+    LL numTads;
+    LL tadLen;
+    View xOuter, xInner;
+    View yOuter, yInner;
+    int group;           // threads cooperating on one TAD segment (along-TAD kernel)
+    int splits;          // segments per TAD
+    int mode;            // along-TAD: 0 = unit-stride inner + 128-bit loads, 1 = rank-1 inner, 2 = general inner view
+    LL colLo;            // across-TAD: extent of the contiguous outer axis
+    LL colStrideX, colStrideY;   // across-TAD: element stride between consecutive elements of a TAD
+    View xOuterHi, yOuterHi;     // across-TAD: outer view without its contiguous axis
+    LL finishLen;        // n handed to finish() (tadLen)
+};
+
+constexpr int kBlock = 256;
+
+template <class T, class P>
+__global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
+    typedef typename Elem<T>::C C;
+    typedef typename P::State State;
+    constexpr int V = Elem<T>::kVec;
+    C p[P::kParams ? P::kParams : 1];
+    load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
+    const T *ax = static_cast<const T *>(a.x);
+    const T *ay = static_cast<const T *>(a.y);
+    T *az = static_cast<T *>(a.z);
+
+    const int g = a.group;
+    const int groupsPerBlock = kBlock / g;
+    const int lane = threadIdx.x % g;
+    const LL totalSegs = a.numTads * a.splits;
+    const LL segLen = (a.tadLen + a.splits - 1) / a.splits;
+    // segments start on a vector boundary so the 128-bit path stays aligned
+    const LL segLenAligned = (segLen + V - 1) / V * V;
+
+    __shared__ State warpStates[kBlock / 32];
+
+    for (LL seg = (LL) blockIdx.x * groupsPerBlock + threadIdx.x / g; ; seg += (LL) gridDim.x * groupsPerBlock) {
+        // a warp- or CTA-wide group leaves as a whole (seg is uniform across it)
+        bool active = seg < totalSegs;
+        if (g < 32) {
+            // sub-warp groups: lanes of finished groups stay in the loop for the shuffles
+            if (__all_sync(0xffffffffu, !active)) break;
+        } else if (!active) break;
+
+        State s;
+        P::init(s);
+        LL r = 0, sp = 0;
+        if (active) {
+            r = seg / a.splits;
+            sp = seg - r * a.splits;
+            const LL j0 = sp * segLenAligned;
+            LL j1 = j0 + segLenAligned;
+            if (j1 > a.tadLen) j1 = a.tadLen;
+            const T *xb = ax + view_offset(a.xOuter, r);
+            const T *yb = P::kInputs == 2 ? ay + view_offset(a.yOuter, r) : nullptr;
+            if (a.mode == 0) {
+                LL j = j0 + (LL) lane * V;
+                const LL step = (LL) g * V;
+                // two packs in flight per operand before any dependent arithmetic
+                for (; j + step < j1; j += 2 * step) {
+                    Pack<T> xa = load_pack(xb + j), xc = load_pack(xb + j + step);
+                    Pack<T> ya, yc;
+                    if (P::kInputs == 2) { ya = load_pack(yb + j); yc = load_pack(yb + j + step); }
+#pragma unroll
+                    for (int k = 0; k < V; k++)
+                        P::accum(s, Elem<T>::to_c(xa.v[k]), P::kInputs == 2 ? Elem<T>::to_c(ya.v[k]) : C(0), j + k, p);
+#pragma unroll
+                    for (int k = 0; k < V; k++)
+                        P::accum(s, Elem<T>::to_c(xc.v[k]), P::kInputs == 2 ? Elem<T>::to_c(yc.v[k]) : C(0), j + step + k, p);
+                }
+                for (; j < j1; j += step) {
+                    Pack<T> xa = load_pack(xb + j);
+                    Pack<T> ya;
+                    if (P::kInputs == 2) ya = load_pack(yb + j);
+#pragma unroll
+                    for (int k = 0; k < V; k++)
+                        P::accum(s, Elem<T>::to_c(xa.v[k]), P::kInputs == 2 ? Elem<T>::to_c(ya.v[k]) : C(0), j + k, p);
+                }
+            } else if (a.mode == 1) {
+                const LL sx = a.xInner.rank ? a.xInner.stride[0] : 0;
+                const LL sy = (P::kInputs == 2 && a.yInner.rank) ? a.yInner.stride[0] : 0;
+#pragma unroll 4
+                for (LL j = j0 + lane; j < j1; j += g) {
+                    C xv = Elem<T>::load(xb + j * sx);
+                    C yv = P::kInputs == 2 ? Elem<T>::load(yb + j * sy) : C(0);
+                    P::accum(s, xv, yv, j, p);
+                }
+            } else {
+                for (LL j = j0 + lane; j < j1; j += g) {
+                    C xv = Elem<T>::load(xb + view_offset(a.xInner, j));
+                    C yv = P::kInputs == 2 ? Elem<T>::load(yb + view_offset(a.yInner, j)) : C(0);
+                    P::accum(s, xv, yv, j, p);
+                }
+            }
+        }
+
+        if (g > 1) group_merge<P>(s, g < 32 ? g : 32);
+        if (g == kBlock) {
+            const int w = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) warpStates[w] = s;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                s = warpStates[0];
+                for (int k = 1; k < kBlock / 32; k++) P::merge(s, warpStates[k]);
+            }
+            __syncthreads();
+        }
+        if (active && lane == 0) {
+            if (a.splits == 1) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+            else reinterpret_cast<State *>(a.partials)[seg] = s;
+        }
+    }
+}
+
+// blockDim = (32, 8). blockIdx.x enumerates (hi, tile of 32 consecutive TADs); blockIdx.y is the
+// row split.
+constexpr int kColRows = 8;
+
+template <class T, class P>
+__global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs a) {
+    typedef typename Elem<T>::C C;
+    typedef typename P::State State;
+    C p[P::kParams ? P::kParams : 1];
+    load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
+    const T *ax = static_cast<const T *>(a.x);
+    const T *ay = static_cast<const T *>(a.y);
+    T *az = static_cast<T *>(a.z);
+
+    const LL tilesPerHi = (a.colLo + 31) / 32;
+    const LL hi = blockIdx.x / tilesPerHi;
+    const LL tile = blockIdx.x - hi * tilesPerHi;
+    const LL lo = tile * 32 + threadIdx.x;
+    const bool active = lo < a.colLo;
+    const LL r = hi * a.colLo + lo;
+
+    State s;
+    P::init(s);
+    if (active) {
+        const T *xb = ax + view_offset(a.xOuterHi, hi) + lo;
+        const T *yb = P::kInputs == 2 ? ay + view_offset(a.yOuterHi, hi) + lo : nullptr;
+        const LL step = (LL) gridDim.y * kColRows;
+        LL j = (LL) blockIdx.y * kColRows + threadIdx.y;
+        // four independent rows in flight per thread
+        for (; j + 3 * step < a.tadLen; j += 4 * step) {
+            C x0 = Elem<T>::load(xb + j * a.colStrideX);
+            C x1 = Elem<T>::load(xb + (j + step) * a.colStrideX);
+            C x2 = Elem<T>::load(xb + (j + 2 * step) * a.colStrideX);
+            C x3 = Elem<T>::load(xb + (j + 3 * step) * a.colStrideX);
+            C y0 = C(0), y1 = C(0), y2 = C(0), y3 = C(0);
+            if (P::kInputs == 2) {
+                y0 = Elem<T>::load(yb + j * a.colStrideY);
+                y1 = Elem<T>::load(yb + (j + step) * a.colStrideY);
+                y2 = Elem<T>::load(yb + (j + 2 * step) * a.colStrideY);
+                y3 = Elem<T>::load(yb + (j + 3 * step) * a.colStrideY);
+            }
+            P::accum(s, x0, y0, j, p);
+            P::accum(s, x1, y1, j + step, p);
+            P::accum(s, x2, y2, j + 2 * step, p);
+            P::accum(s, x3, y3, j + 3 * step, p);
+        }
+        for (; j < a.tadLen; j += step) {
+            C xv = Elem<T>::load(xb + j * a.colStrideX);
+            C yv = P::kInputs == 2 ? Elem<T>::load(yb + j * a.colStrideY) : C(0);
+            P::accum(s, xv, yv, j, p);
+        }
+    }
+    __shared__ State rows[kColRows][32];
+    rows[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && active) {
+        for (int k = 1; k < kColRows; k++) P::merge(s, rows[k][threadIdx.x]);
+        if (a.splits == 1) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+        else reinterpret_cast<State *>(a.partials)[r * a.splits + blockIdx.y] = s;
+    }
+}
+
+// One thread per TAD merges that TAD's `splits` partial states in segment order.
+template <class T, class P>
+__global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) {
+    typedef typename Elem<T>::C C;
+    typedef typename P::State State;
+    C p[P::kParams ? P::kParams : 1];
+    load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
+    T *az = static_cast<T *>(a.z);
+    const State *parts = reinterpret_cast<const State *>(a.partials);
+    for (LL r = (LL) blockIdx.x * kBlock + threadIdx.x; r < a.numTads; r += (LL) gridDim.x * kBlock) {
+        State s = parts[r * a.splits];
+        for (int k = 1; k < a.splits; k++) P::merge(s, parts[r * a.splits + k]);
+        az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+    }
+}
+
+}  // namespace nd4jb200

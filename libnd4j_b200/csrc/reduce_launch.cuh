@@ -1,0 +1,123 @@
+// Host side of the reduction engine: picks the memory pattern, the group width and the number
+// of segments per TAD, obtains scratch for split TADs and launches the kernels.
+#pragma once
+#include "reduce_engine.cuh"
+#include "runtime.h"
+
+namespace nd4jb200 {
+
+struct ReduceCall {
+    const void *x = nullptr;
+    const void *y = nullptr;
+    const void *extra = nullptr;
+    void *z = nullptr;           // device results, numTads elements; may be the workspace for scalar calls
+    TadPlan xPlan;
+    TadPlan yPlan;               // only when y != nullptr
+    bool yBroadcast = false;     // y (or x) is a single TAD reused for every TAD of the other operand
+    LL finishLen = 0;            // n handed to the policy's finish()
+};
+
+// Enough resident threads to cover HBM latency on every SM.
+constexpr LL kTargetThreads = (LL) kNumSMs * 2048;
+
+template <class T, class P>
+Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
+    typedef typename P::State State;
+    constexpr int V = Elem<T>::kVec;
+    const bool two = P::kInputs == 2;
+    if (c.xPlan.numTads <= 0 || c.xPlan.tadLen < 0) return kOk;
+
+    ReduceArgs a;
+    a.x = c.x; a.y = c.y; a.extra = c.extra; a.z = c.z;
+    a.partials = nullptr;
+    a.numTads = c.xPlan.numTads;
+    a.tadLen = c.xPlan.tadLen;
+    a.xOuter = c.xPlan.outer; a.xInner = c.xPlan.inner;
+    a.yOuter = two ? c.yPlan.outer : c.xPlan.outer;
+    a.yInner = two ? c.yPlan.inner : c.xPlan.inner;
+    a.finishLen = c.finishLen;
+    a.splits = 1; a.group = 32; a.mode = 2;
+    a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;
+    a.xOuterHi = a.xOuter; a.yOuterHi = a.yOuter;
+
+    const View &xi = a.xInner, &yi = a.yInner, &xo = a.xOuter, &yo = a.yOuter;
+    const bool xUnit = xi.rank == 0 || (xi.rank == 1 && xi.stride[0] == 1);
+    const bool yUnit = !two || yi.rank == 0 || (yi.rank == 1 && yi.stride[0] == 1);
+    const bool rank1 = xi.rank <= 1 && (!two || yi.rank <= 1);
+
+    // across-TAD pattern: strided walk inside a TAD, neighbouring TADs adjacent in memory
+    bool cols = !xUnit && xi.rank == 1 && xo.rank >= 1 && xo.stride[xo.rank - 1] == 1 && xo.shape[xo.rank - 1] >= 16;
+    if (cols && two) {
+        cols = yi.rank == 1 && yo.rank == xo.rank && yo.stride[yo.rank - 1] == 1;
+        for (int d = 0; cols && d < xo.rank; d++) cols = yo.shape[d] == xo.shape[d];
+    }
+
+    void *ws = nullptr;
+    if (cols) {
+        a.colLo = xo.shape[xo.rank - 1];
+        a.colStrideX = xi.stride[0];
+        a.colStrideY = two ? yi.stride[0] : 0;
+        a.xOuterHi = xo; a.xOuterHi.rank = xo.rank - 1;
+        a.yOuterHi = yo; a.yOuterHi.rank = yo.rank - 1;
+        const LL hiCount = a.numTads / a.colLo;
+        const LL tiles = hiCount * ceil_div(a.colLo, 32);
+        LL splits = ceil_div((LL) kNumSMs * 8, tiles);
+        const LL maxSplits = a.tadLen / (kColRows * 8);   // at least 8 rows per thread
+        if (splits > maxSplits) splits = maxSplits;
+        if (splits < 1) splits = 1;
+        if (splits > 4096) splits = 4096;
+        a.splits = (int) splits;
+        if (a.splits > 1) {
+            ND_TRY(workspace(stream, 256 + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
+            a.partials = static_cast<char *>(ws) + 256;
+        }
+        dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
+        k_reduce_cols<T, P><<<grid, block, 0, stream>>>(a);
+        count_launch();
+    } else {
+        if (xUnit && yUnit) {
+            bool vec = a.tadLen % V == 0 && aligned16(a.x) && view_strides_multiple_of(xo, V);
+            if (two) vec = vec && aligned16(a.y) && view_strides_multiple_of(yo, V);
+            a.mode = vec ? 0 : 1;
+        } else {
+            a.mode = rank1 ? 1 : 2;
+        }
+        const LL perLane = a.mode == 0 ? V : 1;
+        if (a.tadLen * (LL) sizeof(T) >= 8192) a.group = kBlock;
+        else {
+            int g = 1;
+            while (g < 32 && (LL) g * perLane * 4 < a.tadLen) g <<= 1;
+            a.group = g;
+        }
+        // few, long TADs: cut each into segments so that every SM has work
+        LL groups = a.numTads;
+        LL splits = 1;
+        if (groups * a.group < kTargetThreads) {
+            splits = ceil_div(kTargetThreads, groups * a.group);
+            const LL maxSplits = a.tadLen / ((LL) a.group * perLane * 8);
+            if (splits > maxSplits) splits = maxSplits;
+            if (splits < 1) splits = 1;
+        }
+        a.splits = (int) splits;
+        if (a.splits > 1) {
+            ND_TRY(workspace(stream, 256 + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
+            a.partials = static_cast<char *>(ws) + 256;
+        }
+        const LL totalSegs = a.numTads * a.splits;
+        LL blocks = ceil_div(totalSegs, kBlock / a.group);
+        const LL cap = (LL) kNumSMs * 64;
+        if (blocks > cap) blocks = cap;
+        k_reduce_tads<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
+        count_launch();
+    }
+    if (a.splits > 1) {
+        LL blocks = ceil_div(a.numTads, kBlock);
+        if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+        k_reduce_finalize<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
+        count_launch();
+    }
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+}  // namespace nd4jb200

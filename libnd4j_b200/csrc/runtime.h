@@ -1,0 +1,45 @@
+// Host-side runtime shared by the launchers: CUDA error capture, the per-stream scratch
+// workspace and the launch-geometry helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <string>
+#include "common.h"
+#include "shape_host.h"
+
+namespace nd4jb200 {
+
+Status cuda_fail(cudaError_t e, const char *where);
+#define ND_CUDA(call)                                                  \
+    do {                                                               \
+        cudaError_t e__ = (call);                                      \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call);          \
+    } while (0)
+#define ND_TRY(call)                                                   \
+    do {                                                               \
+        Status s__ = (call);                                           \
+        if (s__ != kOk) return s__;                                    \
+    } while (0)
+
+// Scratch memory owned by the library, one block per (device, stream) so that calls on
+// different streams never share it. The block only ever grows; growing synchronises the device.
+// `hostSlot`, when requested, is a 64-byte pinned buffer used to bring scalar results back.
+Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot);
+void release_workspaces();
+
+// Counts kernel launches issued by this library since load (read by the benchmark).
+extern unsigned long long g_launches;
+inline void count_launch(int n = 1) { g_launches += n; }
+
+Status bad_arg(const std::string &msg);
+Status unsupported(const std::string &msg);
+Status unknown_op(const char *family, int opNum);
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool view_strides_multiple_of(const View &v, LL m) {
+    for (int i = 0; i < v.rank; i++) if (v.stride[i] % m != 0) return false;
+    return true;
+}
+inline LL ceil_div(LL a, LL b) { return (a + b - 1) / b; }
+
+}  // namespace nd4jb200
