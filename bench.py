@@ -1,0 +1,518 @@
+"""Benchmark of the legacy-op hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is the elementwise chain on float32 [16384, 4096]:
+    execBroadcast Add of a [4096] row vector  ->  execTransform Tanh  ->  execPairwiseTransform Multiply
+(x ~ N(0,1) seed 1, b ~ N(0,1) seed 2, y ~ U(0,1) seed 3). The headline value is array elements
+pushed through the chain per second, summed over all GPUs (each rank owns its own arrays: weak
+scaling, no data-path collective). Besides the contract keys the JSON line carries the roofline
+of the dominant kernel, a CPU baseline (the reference's own OpenMP loops on a bounded sample),
+the end-to-end number through host buffers, and a `families` table with the achieved HBM GB/s of
+the other op families at their configured sizes.
+
+With --impl reference the reference's CPU implementation (oracle/_ref) is timed instead.
+Under torchrun every rank runs the GPU arm; rank 0 prints the line.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS = 16384, 4096
+ELEMS = ROWS * COLS
+# algorithmic bytes per launch: operands read once + result written once
+BYTES = {"broadcast_add": 2 * ELEMS * 4 + COLS * 4, "transform_tanh": 2 * ELEMS * 4, "pairwise_mul": 3 * ELEMS * 4}
+METRIC = "elementwise chain throughput (broadcast Add -> Tanh -> pairwise Multiply, f32 [16384,4096])"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("hbm_gbs", 6650.0), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6.65 TB/s"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(rows):
+    x = np.random.default_rng(1).standard_normal((rows, COLS), dtype=np.float32)
+    b = np.random.default_rng(2).standard_normal(COLS, dtype=np.float32)
+    y = np.random.default_rng(3).random((rows, COLS), dtype=np.float32)
+    return x, b, y
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_chain(rows, repeats, threads=None):
+    """Times the reference's CPU loops on `rows` rows of the workload. Returns (Gelem/s, cores)."""
+    from oracle import reference
+    from libnd4j_b200 import shape as S
+    ref = reference.Reference()
+    if threads:
+        ref.set_threads(threads)
+    cores = ref.threads()
+    x, b, y = make_inputs(rows)
+    xi, bi = S.shape_info([rows, COLS]), S.shape_info([1, COLS])
+    xf, yf = x.ravel(), y.ravel()
+    t1, t2, t3 = (np.empty(rows * COLS, np.float32) for _ in range(3))
+    best = None
+    for _ in range(repeats + 1):   # first pass warms pages and the OpenMP pool
+        t0 = time.perf_counter()
+        ref.broadcast(0, xf, xi, b, bi, t1, xi, [1])
+        ref.transform(15, t1, xi, t2, xi)
+        ref.pairwise(6, t2, xi, yf, xi, t3, xi)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return rows * COLS / best / 1e9, cores, best
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import reference
+    if not reference.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libnd4jref.so was not built"}))
+        return
+    rows = 2048   # bounded sample: 1/8 of the rows, same row width
+    from libnd4j_b200 import shape as S
+    ref = reference.Reference()
+    cores = ref.threads()
+    x, b, y = make_inputs(rows)
+    xi, bi = S.shape_info([rows, COLS]), S.shape_info([1, COLS])
+    xf, yf = x.ravel(), y.ravel()
+    t1, t2, t3 = (np.empty(rows * COLS, np.float32) for _ in range(3))
+
+    def step():
+        ref.broadcast(0, xf, xi, b, bi, t1, xi, [1])
+        ref.transform(15, t1, xi, t2, xi)
+        ref.pairwise(6, t2, xi, yf, xi, t3, xi)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = rows * COLS / dt / 1e9
+    sample = "%d of %d rows per step, reference CPU loops (OpenMP), %d threads" % (rows, ROWS, cores)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "elementwise chain f32 [16384,4096] (sampled: %d rows)" % rows},
+        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+class Calls:
+    """Pre-marshalled C-ABI calls so that the per-launch host cost is one ctypes call."""
+
+    def __init__(self, ops, stream):
+        self.lib = ops.lib
+        self.stream = ctypes.c_void_p(stream)
+        self.keep = []
+
+    def longs(self, a):
+        arr = np.ascontiguousarray(a, dtype=np.int64)
+        self.keep.append(arr)
+        return arr.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong))
+
+    def ints(self, a):
+        arr = np.ascontiguousarray(a, dtype=np.int32)
+        self.keep.append(arr)
+        return arr.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+
+    @staticmethod
+    def p(t):
+        return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+    def check(self, code):
+        if code != 0:
+            raise RuntimeError(self.lib.nd4jb200_last_error().decode())
+
+
+def time_loop(torch, stream, fn, iters):
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(iters):
+        fn()
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop) / iters
+
+
+def family_table(torch, ops, calls, stream, peak, quick):
+    """Achieved HBM GB/s of the other op families at their configured sizes (algorithmic bytes /
+    CUDA-event time, inputs larger than L2 or L2 flushed by the rotation of buffers)."""
+    from libnd4j_b200 import shape as S
+    lib, st, P = calls.lib, calls.stream, calls.p
+    out = {}
+    dev = torch.device("cuda")
+
+    def record(name, nbytes, elems, fn, iters=20):
+        for _ in range(3):
+            fn()
+        ms = time_loop(torch, stream, fn, iters)
+        out[name] = {"ms": round(ms, 5), "GBps": round(nbytes / ms / 1e6, 1), "frac_of_measured_peak": round(nbytes / ms / 1e6 / peak, 3),
+                     "Gelem_s": round(elems / ms / 1e6, 2)}
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    # reduce Sum along dimension 1, [8192,4096]; several input copies rotate so L2 never holds the input
+    xs = [torch.empty(8192, 4096, device=dev).uniform_(-1, 1, generator=g) for _ in range(3)]
+    z = torch.zeros(8192, device=dev)
+    xi, zi, d1 = calls.longs(S.shape_info([8192, 4096])), calls.longs(S.shape_info([8192, 1])), calls.ints([1])
+    k = [0]
+
+    def f():
+        k[0] = (k[0] + 1) % 3
+        calls.check(lib.nd4jb200_exec_reduce(st, 0, 1, P(xs[k[0]]), xi, None, P(z), zi, d1, 1))
+    record("reduce_sum_dim1_8192x4096", 134250496, 8192 * 4096, f)
+    z0 = torch.zeros(4096, device=dev)
+    zi0, d0 = calls.longs(S.shape_info([1, 4096])), calls.ints([0])
+
+    def f():
+        k[0] = (k[0] + 1) % 3
+        calls.check(lib.nd4jb200_exec_reduce(st, 0, 1, P(xs[k[0]]), xi, None, P(z0), zi0, d0, 1))
+    record("reduce_sum_dim0_8192x4096", 134234112, 8192 * 4096, f)
+    del xs
+    # index reduce IMax dim 1 and summary-stats variance dim 0 on [65536,1024] with 16 levels
+    lv = torch.randint(0, 16, (65536, 1024), device=dev, generator=g).float() / 8 - 1
+    xi3 = calls.longs(S.shape_info([65536, 1024]))
+    zr, zc = torch.zeros(65536, device=dev), torch.zeros(1024, device=dev)
+    zir, zic = calls.longs(S.shape_info([65536, 1])), calls.longs(S.shape_info([1, 1024]))
+    record("indexreduce_imax_dim1_65536x1024", 268697600, 65536 * 1024,
+           lambda: calls.check(lib.nd4jb200_exec_index_reduce(st, 0, 0, P(lv), xi3, None, P(zr), zir, d1, 1)))
+    record("summarystats_variance_dim0_65536x1024", 268439552, 65536 * 1024,
+           lambda: calls.check(lib.nd4jb200_exec_summary_stats(st, 0, 0, P(lv), xi3, None, P(zc), zic, d0, 1, 1)))
+    del lv
+    # reduce3 cosine / euclidean on [32768,512] pairs, c-order and stride-2 f-order column views, f32 and f16
+    for dt, code, name in ((torch.float32, 0, "f32"), (torch.float16, 2, "f16")):
+        es = 4 if code == 0 else 2
+        nb = 2 * 32768 * 512 * es + 32768 * es
+        xa = [torch.randn(32768, 1024, device=dev, generator=g).to(dt) for _ in range(4)]
+        ya = [torch.randn(32768, 1024, device=dev, generator=g).to(dt) for _ in range(4)]
+        zz = torch.zeros(32768, device=dev, dtype=dt)
+        ci = calls.longs(S.shape_info([32768, 512]))
+        vi = calls.longs(S.shape_info([32768, 512], "f", [1, 65536], ews=-1))
+        zi4 = calls.longs(S.shape_info([32768, 1]))
+        for op, opname in ((2, "cosine"), (1, "euclidean")):
+            for info, lay in ((ci, "corder"), (vi, "fview")):
+                def f(op=op, info=info):
+                    k[0] = (k[0] + 1) % 4
+                    calls.check(lib.nd4jb200_exec_reduce3(st, code, op, P(xa[k[0]]), info, None, P(ya[k[0]]), info, P(zz), zi4, d1, 1))
+                record("reduce3_%s_%s_%s_32768x512" % (opname, lay, name), nb, 32768 * 512, f)
+        del xa, ya
+    # scalar family: x * 1.5 on the chain-sized array
+    xs_ = torch.randn(ELEMS, device=dev, generator=g)
+    zs_ = torch.empty_like(xs_)
+    si = calls.longs(S.shape_info([ROWS, COLS]))
+    record("scalar_mul_16384x4096", 2 * ELEMS * 4, ELEMS,
+           lambda: calls.check(lib.nd4jb200_exec_scalar(st, 0, 2, P(xs_), si, P(zs_), si, ctypes.c_double(1.5), None)))
+    del xs_, zs_
+    # random family: 2^30 outputs (2^26 when quick), table of 100000 words, seed 119
+    n = 1 << (26 if quick else 30)
+    state = ops.initRandom([None, stream.cuda_stream], 119, 100000, None)
+    zbuf = torch.empty(n, device=dev)
+    zin = calls.longs(S.shape_info([1, n]))
+    e01 = torch.tensor([0.0, 1.0], device=dev)
+    e03 = torch.tensor([0.3], device=dev)
+    e05 = torch.tensor([0.5], device=dev)
+    xr = torch.ones(n, device=dev)
+    sp = ctypes.c_void_p(state)
+    record("random_uniform_2p%d" % (26 if quick else 30), 4 * n, n,
+           lambda: calls.check(lib.nd4jb200_exec_random(st, 0, 0, sp, P(zbuf), zin, P(e01))), iters=3)
+    record("random_gaussian_2p%d" % (26 if quick else 30), 4 * n, n,
+           lambda: calls.check(lib.nd4jb200_exec_random_xy(st, 0, 6, sp, P(zbuf), zin, P(zbuf), zin, P(zbuf), zin, P(e01))), iters=3)
+    record("random_bernoulli_2p%d" % (26 if quick else 30), 4 * n, n,
+           lambda: calls.check(lib.nd4jb200_exec_random(st, 0, 7, sp, P(zbuf), zin, P(e03))), iters=3)
+    record("random_dropout_inverted_2p%d" % (26 if quick else 30), 8 * n, n,
+           lambda: calls.check(lib.nd4jb200_exec_random_x(st, 0, 2, sp, P(xr), zin, P(zbuf), zin, P(e05))), iters=3)
+    del xr
+    # whole-array Sum of 2^31 (2^27 when quick) floats drawn U(-1,1) on the device
+    n2 = 1 << (27 if quick else 31)
+    big = torch.empty(n2, device=dev)
+    chunk = 1 << 26
+    ci2 = calls.longs(S.shape_info([1, chunk]))
+    em1 = torch.tensor([-1.0, 1.0], device=dev)
+    for off in range(0, n2, chunk):
+        calls.check(lib.nd4jb200_exec_random(st, 0, 0, sp, P(big[off:off + chunk]), ci2, P(em1)))
+    bi2 = calls.longs(S.shape_info([1, n2]))
+    res = ctypes.c_double()
+    record("reduce_scalar_sum_2p%d" % (27 if quick else 31), 4 * n2, n2,
+           lambda: calls.check(lib.nd4jb200_exec_reduce_scalar(st, 0, 1, P(big), bi2, None, ctypes.byref(res))), iters=5)
+    ops.destroyRandom(state)
+    return out
+
+
+def run_ours(args):
+    import torch
+    from libnd4j_b200 import shape as S
+    from libnd4j_b200.native_ops import NativeOps
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ops = NativeOps()
+    stream = torch.cuda.Stream()
+    calls = Calls(ops, stream.cuda_stream)
+    lib, st, P = calls.lib, calls.stream, calls.p
+    peak, peak_src = measured_peaks()
+
+    x, b, y = make_inputs(ROWS)
+    hx, hb, hy = (torch.from_numpy(a).pin_memory() for a in (x, b, y))
+    hz = torch.empty(ELEMS, dtype=torch.float32).pin_memory()
+    with torch.cuda.stream(stream):
+        dx, db, dy = hx.cuda(non_blocking=True), hb.cuda(non_blocking=True), hy.cuda(non_blocking=True)
+        t1, t2, dz = (torch.empty(ROWS, COLS, device="cuda") for _ in range(3))
+    stream.synchronize()
+    xi, bi, d1 = calls.longs(S.shape_info([ROWS, COLS])), calls.longs(S.shape_info([1, COLS])), calls.ints([1])
+
+    def k_broadcast():
+        calls.check(lib.nd4jb200_exec_broadcast(st, 0, 0, P(dx), xi, P(db), bi, P(t1), xi, d1, 1))
+
+    def k_tanh():
+        calls.check(lib.nd4jb200_exec_transform(st, 0, 15, P(t1), xi, P(t2), xi, None))
+
+    def k_mul():
+        calls.check(lib.nd4jb200_exec_pairwise(st, 0, 6, P(t2), xi, P(dy), xi, P(dz), xi, None))
+
+    def step():
+        k_broadcast()
+        k_tanh()
+        k_mul()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = ops.launchCount()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(args.steps):
+        step()
+    stop.record(stream)
+    barrier()
+    launches = ops.launchCount() - launches0
+    ms_step = start.elapsed_time(stop) / args.steps
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms_step], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item())
+    value = world * ELEMS / ms_step / 1e6   # Gelem/s over all ranks
+
+    # per-kernel durations, each timed alone on the launch stream over the same buffers
+    per = {}
+    for name, fn in (("broadcast_add", k_broadcast), ("transform_tanh", k_tanh), ("pairwise_mul", k_mul)):
+        for _ in range(3):
+            fn()
+        per[name] = time_loop(torch, stream, fn, max(args.steps, 20))
+    dom = max(per, key=lambda n: per[n])
+    achieved = BYTES[dom] / per[dom] / 1e6
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                "per_kernel_ms": {k: round(v, 5) for k, v in per.items()},
+                "per_kernel_GBps": {k: round(BYTES[k] / v / 1e6, 1) for k, v in per.items()},
+                "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as f:
+            roofline["traffic"] = json.load(f).get(dom)
+
+    # end to end through host buffers: H2D of x, b, y, the chain, D2H of the result
+    def e2e_step():
+        ops.memcpyAsync(dx, hx.data_ptr(), ELEMS * 4, 1, stream.cuda_stream)
+        ops.memcpyAsync(db, hb.data_ptr(), COLS * 4, 1, stream.cuda_stream)
+        ops.memcpyAsync(dy, hy.data_ptr(), ELEMS * 4, 1, stream.cuda_stream)
+        step()
+        ops.memcpyAsync(hz.data_ptr(), dz, ELEMS * 4, 2, stream.cuda_stream)
+
+    e2e_step()
+    barrier()
+    e2e_iters = max(2, min(args.steps, 5))
+    e2e_ms = time_loop(torch, stream, e2e_step, e2e_iters)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": round(world * ELEMS / e2e_ms / 1e6, 3), "unit": "Gelem/s", "ms_per_step": round(e2e_ms, 3),
+           "h2d_bytes_per_step": 2 * ELEMS * 4 + COLS * 4, "d2h_bytes_per_step": ELEMS * 4}
+
+    families = None
+    if world == 1 and not args.no_families:
+        with torch.cuda.stream(stream):
+            del dx, dy, t1, t2, dz
+            torch.cuda.empty_cache()
+            families = family_table(torch, ops, calls, stream, peak, args.quick)
+    elif world > 1:
+        families = sharded_families(torch, dist, ops, calls, stream, world, rank, args.quick)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import reference
+        if reference.available():
+            rows = 2048
+            gel, cores, secs = cpu_reference_chain(rows, repeats=2)
+            cpu = {"value": round(gel, 4), "unit": "Gelem/s", "cores": cores, "kind": "reference",
+                   "sample": "%d of %d rows (same row width), best of 2 after one warm-up pass, %.1f ms" % (rows, ROWS, secs * 1e3)}
+        else:
+            cpu = {"value": None, "unit": "Gelem/s", "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": round(value, 3), "unit": "Gelem/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "elementwise chain f32 [16384,4096]: execBroadcast Add(dim 1) -> execTransform Tanh -> "
+                                   "execPairwiseTransform Multiply", "l2": "inputs larger than L2 (3 x 268 MB streamed per step)",
+                       "sharding": "one independent chain per GPU"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "families": families,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def sharded_families(torch, dist, ops, calls, stream, world, rank, quick):
+    """N > 1: the two sharded workloads. Random generation is offset-sharded with global indices
+    and needs no exchange; the whole-array Sum reduces each shard locally and combines the
+    per-GPU partials with one NCCL all-reduce (the only collective on this path)."""
+    from libnd4j_b200 import shape as S
+    lib, st, P = calls.lib, calls.stream, calls.p
+    dev = torch.device("cuda")
+    out = {}
+    n = 1 << (26 if quick else 30)
+    per = n // world
+    state = ops.initRandom([None, stream.cuda_stream], 119, 100000, None)
+    sp = ctypes.c_void_p(state)
+    z = torch.empty(per, device=dev)
+    e01 = torch.tensor([0.0, 1.0], device=dev)
+
+    def timed(fn, iters):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = time_loop(torch, stream, fn, iters)
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = timed(lambda: calls.check(lib.nd4jb200_exec_random_range(st, 0, 0, 0, sp, None, None, P(z), P(e01),
+                                                                  rank * per, per, n)), 3)
+    out["random_uniform_sharded"] = {"ms": round(ms, 4), "Gelem_s": round(n / ms / 1e6, 2), "elements": n}
+    n2 = 1 << (27 if quick else 31)
+    per2 = n2 // world
+    big = torch.empty(per2, device=dev)
+    chunk = min(per2, 1 << 26)
+    em1 = torch.tensor([-1.0, 1.0], device=dev)
+    for off in range(0, per2, chunk):
+        calls.check(lib.nd4jb200_exec_random_range(st, 0, 0, 0, sp, None, None, P(big[off:off + chunk]), P(em1),
+                                                   rank * per2 + off, chunk, n2))
+    bi2 = calls.longs(S.shape_info([1, per2]))
+    res = ctypes.c_double()
+    total = torch.zeros(1, device=dev, dtype=torch.float64)
+
+    def reduce_step():
+        calls.check(lib.nd4jb200_exec_reduce_scalar(st, 0, 1, P(big), bi2, None, ctypes.byref(res)))
+        total[0] = res.value
+        with torch.cuda.stream(stream):
+            dist.all_reduce(total)
+
+    ms = timed(reduce_step, 5)
+    out["reduce_scalar_sum_sharded_allreduce"] = {"ms": round(ms, 4), "Gelem_s": round(n2 / ms / 1e6, 2),
+                                                  "GBps": round(4 * n2 / ms / 1e6, 1), "elements": n2,
+                                                  "sum": float(total.item())}
+    ops.destroyRandom(state)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--quick", action="store_true", help="smaller sizes for the families table")
+    ap.add_argument("--no-families", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

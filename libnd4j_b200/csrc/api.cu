@@ -89,12 +89,15 @@ Status setup_reduction(const void *x, const Nd4jLong *xShapeInfo, const void *y,
     LL zLen = -1;
     if (zShapeInfo) { ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &s->z)); zLen = s->z.length; }
     ND_TRY(make_tad_plan(s->x, dimension, dimensionLength, &s->call.xPlan));
+    if (y) ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &s->y));
+    // reduce3 with a short x: x is one TAD that meets every TAD of y
+    const bool xIsOneTad = y && s->x.length < s->y.length && zLen != 1 && !forceWhole;
     // a single result means "whole array", whatever the dimension list says
     // (include/loops/cpu/reduce.cpp:108-111, include/loops/cpu/indexreduce.cpp:135-138)
-    if (forceWhole || zLen == 1 || s->call.xPlan.numTads == 1)
+    if (!xIsOneTad && (forceWhole || zLen == 1 || s->call.xPlan.numTads == 1))
         ND_TRY(make_tad_plan(s->x, nullptr, 0, &s->call.xPlan));
-    s->scalarResult = s->call.xPlan.whole;
-    if (zLen >= 0 && !forceWhole && zLen != s->call.xPlan.numTads) {
+    s->scalarResult = s->call.xPlan.whole && !xIsOneTad;
+    if (zLen >= 0 && !forceWhole && !xIsOneTad && zLen != s->call.xPlan.numTads) {
         std::ostringstream os;
         os << "result holds " << zLen << " elements but the dimension list yields " << s->call.xPlan.numTads << " TADs";
         return bad_arg(os.str());
@@ -102,7 +105,6 @@ Status setup_reduction(const void *x, const Nd4jLong *xShapeInfo, const void *y,
     s->call.x = x;
     s->call.finishLen = s->call.xPlan.tadLen;
     if (y) {
-        ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &s->y));
         TadPlan &xp = s->call.xPlan, &yp = s->call.yPlan;
         if (s->scalarResult) {
             if (s->x.length != s->y.length) return bad_arg("reduce3 over whole arrays needs x and y of equal length");
@@ -125,6 +127,7 @@ Status setup_reduction(const void *x, const Nd4jLong *xShapeInfo, const void *y,
             ND_TRY(make_tad_plan(s->x, nullptr, 0, &xp));
             xp.numTads = yp.numTads;
             s->call.finishLen = xp.tadLen;
+            if (zLen >= 0 && zLen != yp.numTads) return bad_arg("result length does not match the number of y TADs");
         }
         s->call.y = y;
     }

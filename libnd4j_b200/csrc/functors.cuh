@@ -35,6 +35,60 @@ template <class C> ND_D C rel_err(C a, C b) {
     return absv(a - b) / (absv(a) + absv(b));
 }
 
+// tanh for float with error well below one ulp, so that results stay within 2 ulp of the host
+// libm the reference calls (templatemath.h:847). |x| < 0.55: odd minimax polynomial. Otherwise
+// tanh = 1 - 2/(e^{2|x|} + 1) with e^{2|x|} = 2^n (1 + s), where s and the denominator are
+// carried as unevaluated float pairs (hi + lo) and the reciprocal's residual is folded into the
+// last subtraction, leaving a single rounding.
+ND_D float tanh_accurate(float x) {
+    const float ax = fabsf(x);
+    float t;
+    if (ax < 0.55f) {
+        const float z = ax * ax;
+        float p = -0.000966387638993646f;
+        p = fmaf(p, z, 0.0034055003387174483f);
+        p = fmaf(p, z, -0.008826388520025496f);
+        p = fmaf(p, z, 0.02186568778676557f);
+        p = fmaf(p, z, -0.053968065636603224f);
+        p = fmaf(p, z, 0.13333332981667803f);
+        p = fmaf(p, z, -0.3333333333225883f);
+        t = fmaf(ax * z, p, ax);
+    } else {
+        const float y = fminf(ax + ax, 40.0f);
+        const float n = rintf(y * 1.4426950408889634f);
+        const float rh = fmaf(-n, 0.693145751953125f, y);          // exact: ln2 split with a short high part
+        const float rl = -n * 1.42860682030941723212e-6f;
+        const float r = rh + rl;
+        const float rerr = (rh - r) + rl;
+        float q = 0.0001989928507603579f;
+        q = fmaf(q, r, 0.0013933650354159414f);
+        q = fmaf(q, r, 0.008333298469720569f);
+        q = fmaf(q, r, 0.04166646491457965f);
+        q = fmaf(q, r, 0.16666666719031667f);
+        q = fmaf(q, r, 0.5000000013468379f);
+        const float p = (r * r) * q;                                  // e^r - 1 - r
+        const float sh = r + p;
+        float sl = p - (sh - r);
+        sl += fmaf(rerr, r, rerr);
+        const float twoN = __int_as_float(((int) n + 127) << 23);
+        const float b = twoN * sh;                                    // exact scaling
+        const float a = twoN + 1.0f;
+        const float dh = a + b;                                       // e^{2|x|} + 1, high part
+        const float dl = fmaf(twoN, sl, b - (dh - a));                // and what the sum dropped
+        const float r0 = __frcp_rn(dh);
+        float e = fmaf(-dh, r0, 1.0f);
+        e = fmaf(-dl, r0, e);                                         // 1 - d * r0
+        const float two = r0 + r0;
+        const float uh = 1.0f - two;
+        const float ul = (1.0f - uh) - two;
+        t = uh + fmaf(-two, e, ul);
+    }
+    t = copysignf(t, x);
+    return x != x ? x : t;
+}
+template <class C> ND_D C tanhv(C x) { return tanh(x); }
+template <> ND_D float tanhv<float>(float x) { return tanh_accurate(x); }
+
 // The 14 comparison modes shared by MatchCondition, CompareAndSet, CompareAndReplace and the
 // First/LastIndex reductions (ops.h:1534-1602). Returns <0 for an unknown mode.
 template <class C> ND_D int condition(C v, C compare, C eps, int mode) {
@@ -85,7 +139,7 @@ ND_UNARY(Sign, 0, return C((x > C(0)) - (x < C(0)));)
 ND_UNARY(Sin, 0, return sin(x);)
 ND_UNARY(SoftPlus, 0, return log(C(1) + exp(x));)
 ND_UNARY(Sqrt, 0, return sqrt(x);)
-ND_UNARY(Tanh, 0, return tanh(x);)
+ND_UNARY(Tanh, 0, return tanhv(x);)
 ND_UNARY(ACos, 0, return acos(x);)
 ND_UNARY(ASin, 0, return asin(x);)
 ND_UNARY(ATan, 0, return atan(x);)
@@ -93,7 +147,7 @@ ND_UNARY(HardTanh, 0, return x < C(-1) ? C(-1) : (x > C(1) ? C(1) : x);)
 ND_UNARY(SoftSign, 0, return x / (C(1) + absv(x));)
 ND_UNARY(ELU, 0, return x >= C(0) ? x : exp(x) - C(1);)
 ND_UNARY(ELUDerivative, 0, return x >= C(0) ? C(1) : exp(x);)
-ND_UNARY(TanhDerivative, 0, C t = tanh(x); return C(1) - t * t;)
+ND_UNARY(TanhDerivative, 0, C t = tanhv(x); return C(1) - t * t;)
 ND_UNARY(TimesOneMinus, 0, return x * (C(1) - x);)
 ND_UNARY(HardTanhDerivative, 0, return (x >= C(-1) && x <= C(1)) ? C(1) : C(0);)
 ND_UNARY(Ones, 0, return C(1);)
@@ -122,21 +176,21 @@ ND_UNARY(HardSigmoid, 0, return minv(C(1), maxv(C(0), C(0.2f) * x + C(0.5f)));)
 ND_UNARY(HardSigmoidDerivative, 0, return (x < C(-2.5f) || x > C(2.5f)) ? C(0) : C(0.2f);)
 ND_UNARY(RationalTanh, 0,
          C d = (C(2) / C(3)) * x;
-         C t = sgn(d) * (C(1) - (C(1) / (C(1) + absv(d) + pow(d, C(2)) + C(1.41645f) * pow(d, C(4)))));
+         C d2 = d * d; C t = sgn(d) * (C(1) - (C(1) / (C(1) + absv(d) + d2 + C(1.41645f) * (d2 * d2))));
          return C(1.7159f) * t;)
 ND_UNARY(RationalTanhDerivative, 0,
          C d = (C(2) / C(3)) * x;
-         C a = C(1) + absv(d) + pow(d, C(2)) + C(1.41645f) * pow(d, C(4));
-         C t = (C(1) + sgn(d) * (C(2) * d + C(4) * C(1.41645f) * pow(d, C(3)))) / (a * a);
+         C d2 = d * d; C a = C(1) + absv(d) + d2 + C(1.41645f) * (d2 * d2);
+         C t = (C(1) + sgn(d) * (C(2) * d + C(4) * C(1.41645f) * (d2 * d))) / (a * a);
          return C(1.7159f) * (C(2) / C(3)) * t;)
 ND_UNARY(LogX, 1, return log(x) / log(p[0]);)
 ND_UNARY(Not, 1, return x == p[0] ? C(1) : C(0);)
-ND_UNARY(RectifiedTanh, 0, return maxv(C(0), tanh(x));)
-ND_UNARY(RectifiedTanhDerivative, 0, if (x > C(0)) { C t = tanh(x); return C(1) - t * t; } return C(0);)
+ND_UNARY(RectifiedTanh, 0, return maxv(C(0), tanhv(x));)
+ND_UNARY(RectifiedTanhDerivative, 0, if (x > C(0)) { C t = tanhv(x); return C(1) - t * t; } return C(0);)
 ND_UNARY(Sinh, 0, return sinh(x);)
 ND_UNARY(Cosh, 0, return cosh(x);)
 ND_UNARY(Tan, 0, return tan(x);)
-ND_UNARY(TanDerivative, 0, C c = cos(x); return C(1) / pow(c, C(2));)
+ND_UNARY(TanDerivative, 0, C c = cos(x); return C(1) / (c * c);)
 ND_UNARY(SELU, 0,
          return x > C(0) ? C(ND_SELU_LAMBDA) * x
                          : C(ND_SELU_LAMBDA) * (C(ND_SELU_ALPHA) * exp(x) - C(ND_SELU_ALPHA));)
@@ -149,7 +203,7 @@ ND_UNARY(ClipByValue, 2, return x > p[1] ? p[1] : (x < p[0] ? p[0] : x);)
 ND_UNARY(Swish, 0, return x * sigmoid(x);)
 ND_UNARY(SwishDerivative, 0,
          C ex = pow(C(ND_E), x);
-         return C((double(ex) * (double(x) + double(ex) + 1.)) / double(pow(C(double(ex) + 1.), C(2))));)
+         C e1 = C(double(ex) + 1.); return C((double(ex) * (double(x) + double(ex) + 1.)) / double(e1 * e1));)
 ND_UNARY(RSqrt, 0, return C(1) / sqrt(x);)
 ND_UNARY(Log1p, 0, return log(C(1) + x);)
 ND_UNARY(Erf, 0, return erf(x);)
@@ -158,8 +212,8 @@ ND_UNARY(IsNan, 0, return isnanv(x) ? C(1) : C(0);)
 ND_UNARY(IsFinite, 0, return isfinite(x) ? C(1) : C(0);)
 ND_UNARY(ACosh, 0, return acosh(x);)
 ND_UNARY(ACoshDerivative, 0, return C(1) / (sqrt(x - C(1)) * sqrt(x + C(1)));)
-ND_UNARY(ASinh, 0, return log(sqrt(pow(x, C(2)) + C(1)) + x);)
-ND_UNARY(ASinhDerivative, 0, return C(1) / sqrt(pow(x, C(2)) + C(1));)
+ND_UNARY(ASinh, 0, return log(sqrt(x * x + C(1)) + x);)
+ND_UNARY(ASinhDerivative, 0, return C(1) / sqrt(x * x + C(1));)
 ND_UNARY(SinhDerivative, 0, return cosh(x);)
 ND_UNARY(Rint, 0, return rint(x);)
 ND_UNARY(LogSigmoid, 0, return log(sigmoid(x));)
@@ -169,7 +223,7 @@ ND_UNARY(Expm1, 0, return exp(x) - C(1);)
 ND_UNARY(PowDerivativeT, 1, return p[0] * pow(x, p[0] - C(1));)
 ND_UNARY(ATanh, 0, return atanh(x);)
 ND_UNARY(Reciprocal, 0, return C(1) / x;)
-ND_UNARY(Sqr, 0, return pow(x, C(2));)
+ND_UNARY(Sqr, 0, return x * x;)
 ND_UNARY(RELU6, 1, C r = x < p[0] ? p[0] : x; return r < C(6) ? r : C(6);)
 
 // opNum -> functor. Composite transforms (Col2Im 36, Im2col 37, SoftMax 38, SoftMaxDerivative
@@ -222,7 +276,7 @@ ND_BINARY(Max, 0, return maxv(x, y);)
 ND_BINARY(Min, 0, return minv(x, y);)
 ND_BINARY(BAMax, 0, return absv(x) > absv(y) ? x : y;)   // broadcast form keeps the sign (ops.h 2-arg op)
 ND_BINARY(BAMin, 0, return absv(x) < absv(y) ? x : y;)
-ND_BINARY(SquaredSubtract, 0, return pow(x - y, C(2));)
+ND_BINARY(SquaredSubtract, 0, C d = x - y; return d * d;)
 ND_BINARY(FloorMod, 0,
           C m = fmod(x, y);
           return ((x < C(0)) == (y < C(0))) ? m : fmod(m + y, y);)
@@ -309,9 +363,9 @@ ND_REDUCE(RNorm2, 0, C(0), return x * x;, return a + b;, return sqrt(r);)
 ND_REDUCE(RNormMax, 0, C(0), return absv(x);, return maxv(a, b);, return r;)
 ND_REDUCE(RProd, 0, C(1), return x;, return a * b;, return r;)
 ND_REDUCE(RVariance, 2, C(0), C d = x - p[0]; return d * d;, return a + b;,
-          return (r - (pow(p[1], C(2)) / C((int) n))) / C(n - 1);)
+          return (r - ((p[1] * p[1]) / C((int) n))) / C(n - 1);)
 ND_REDUCE(RStandardDeviation, 2, C(0), C d = x - p[0]; return d * d;, return a + b;,
-          return sqrt((r - (pow(p[1], C(2)) / C((int) n))) / C(n - 1));)
+          return sqrt((r - ((p[1] * p[1]) / C((int) n))) / C(n - 1));)
 ND_REDUCE(RASum, 0, C(0), return absv(x);, return a + b;, return absv(r);)
 ND_REDUCE(RMatchCondition, 3, C(0), int c = condition(x, p[0], p[1], (int) p[2]); return c < 0 ? x : C(c);,
           return a + b;, return r;)
@@ -319,8 +373,8 @@ ND_REDUCE(RAMax, 0, C(0), return absv(x);, return maxv(a, b);, return absv(r);)
 ND_REDUCE(RAMin, 0, ND_INF(C), return absv(x);, return minv(a, b);, return absv(r);)
 ND_REDUCE(RAMean, 0, C(0), return absv(x);, return a + b;, return absv(r) / C((int) n);)
 ND_REDUCE(REntropy, 0, C(0), return x * log(x);, return a + b;, return r;)
-ND_REDUCE(RLogEntropy, 0, C(0), return log(pow(x, C(2)));, return a + b;, return r;)
-ND_REDUCE(RShannonEntropy, 0, C(0), C s = pow(x, C(2)); return s * log(s);, return a + b;, return -r;)
+ND_REDUCE(RLogEntropy, 0, C(0), return log(x * x);, return a + b;, return r;)
+ND_REDUCE(RShannonEntropy, 0, C(0), C s = x * x; return s * log(s);, return a + b;, return -r;)
 ND_REDUCE(RAny, 0, C(0), return x;, return a + b;, return r > C(0) ? C(1) : C(0);)
 ND_REDUCE(RAll, 0, C(1), return x;, return a * b;, return r > C(0) ? C(1) : C(0);)
 ND_REDUCE(RCountNonZero, 0, C(0), return x == C(0) ? C(0) : C(1);, return a + b;, return r;)

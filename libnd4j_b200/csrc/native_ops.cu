@@ -1,0 +1,294 @@
+// The reference-facing C++ surface: NativeOps members with the reference's signatures
+// (include/NativeOps.h), each a thin forwarder to the C ABI. The only logic here is recovering
+// HOST copies of the shapeInfo / dimension arguments, which the reference's CUDA build receives
+// as device pointers plus host copies in extraPointers.
+#include "../../include/NativeOps.h"
+#include <cuda_runtime.h>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace {
+
+std::mutex g_mu;
+std::map<const void *, std::vector<Nd4jLong> > g_shapeCache;
+std::map<std::pair<const void *, int>, std::vector<int> > g_dimCache;
+
+[[noreturn]] void fail(const char *where) {
+    throw std::runtime_error(std::string(where) + ": " + nd4jb200_last_error());
+}
+inline void check(int status, const char *where) { if (status != 0) fail(where); }
+
+inline void *stream_of(Nd4jPointer *extra) { return extra ? extra[1] : nullptr; }
+
+bool is_device_pointer(const void *p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return attr.type == cudaMemoryTypeDevice;
+}
+
+// Host view of a shapeInfo: the copy in extraPointers[slot] when the caller provided one,
+// otherwise the argument itself if it is host memory, otherwise a cached download.
+const Nd4jLong *host_info(Nd4jPointer *extra, int slot, const Nd4jLong *arg) {
+    if (extra && slot >= 0 && extra[slot]) return static_cast<const Nd4jLong *>(extra[slot]);
+    if (arg == nullptr) return nullptr;
+    if (!is_device_pointer(arg)) return arg;
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_shapeCache.find(arg);
+    if (it != g_shapeCache.end()) return it->second.data();
+    Nd4jLong rank = 0;
+    if (cudaMemcpy(&rank, arg, sizeof(Nd4jLong), cudaMemcpyDeviceToHost) != cudaSuccess || rank < 0 || rank > 32)
+        throw std::runtime_error("could not read shapeInfo from the device");
+    std::vector<Nd4jLong> v(2 * rank + 4);
+    if (cudaMemcpy(v.data(), arg, sizeof(Nd4jLong) * v.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
+        throw std::runtime_error("could not read shapeInfo from the device");
+    return g_shapeCache.emplace(arg, std::move(v)).first->second.data();
+}
+
+const int *host_dims(const int *dimension, int n) {
+    if (dimension == nullptr || n <= 0) return nullptr;
+    if (!is_device_pointer(dimension)) return dimension;
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto key = std::make_pair(static_cast<const void *>(dimension), n);
+    auto it = g_dimCache.find(key);
+    if (it != g_dimCache.end()) return it->second.data();
+    std::vector<int> v(n);
+    if (cudaMemcpy(v.data(), dimension, sizeof(int) * n, cudaMemcpyDeviceToHost) != cudaSuccess)
+        throw std::runtime_error("could not read the dimension array from the device");
+    return g_dimCache.emplace(key, std::move(v)).first->second.data();
+}
+
+template <class T> struct TypeCode;
+template <> struct TypeCode<float> { static constexpr int v = ND4JB200_FLOAT; };
+template <> struct TypeCode<double> { static constexpr int v = ND4JB200_DOUBLE; };
+template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; };
+
+}  // namespace
+
+#define X_INFO host_info(extraPointers, 0, xShapeInfo)
+#define Y_INFO host_info(extraPointers, 7, yShapeInfo)
+#define Z_INFO(arg) host_info(extraPointers, 8, arg)
+#define STREAM stream_of(extraPointers)
+
+#define ND4JB200_DEFINE_FAMILIES(T, S, R)                                                                              \
+    R NativeOps::execIndexReduceScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,          \
+                                          T *extraParams) {                                                           \
+        double out = 0;                                                                                                \
+        check(nd4jb200_exec_index_reduce_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, &out),         \
+              "execIndexReduceScalar" #S);                                                                             \
+        return (R) out;                                                                                                \
+    }                                                                                                                  \
+    void NativeOps::execIndexReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,             \
+                                       T *extraParams, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,    \
+                                       int dimensionLength) {                                                         \
+        check(nd4jb200_exec_index_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,               \
+                                         Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),        \
+                                         dimensionLength), "execIndexReduce" #S);                                      \
+    }                                                                                                                  \
+    void NativeOps::execBroadcast##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *y,         \
+                                     Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfo, int *dimension,      \
+                                     int dimensionLength) {                                                           \
+        check(nd4jb200_exec_broadcast(STREAM, TypeCode<T>::v, opNum, x, X_INFO, y, Y_INFO, result,                    \
+                                      Z_INFO(resultShapeInfo), host_dims(dimension, dimensionLength),                 \
+                                      dimensionLength), "execBroadcast" #S);                                           \
+    }                                                                                                                  \
+    void NativeOps::execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong xStride, T *y,    \
+                                             Nd4jLong yStride, T *result, Nd4jLong resultStride, T *extraParams,      \
+                                             Nd4jLong n) {                                                            \
+        check(nd4jb200_exec_pairwise_strided(STREAM, TypeCode<T>::v, opNum, dx, xStride, y, yStride, result,          \
+                                             resultStride, extraParams, n), "execPairwiseTransform" #S);               \
+    }                                                                                                                  \
+    void NativeOps::execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong *xShapeInfo,      \
+                                             T *y, Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfo,        \
+                                             T *extraParams) {                                                        \
+        check(nd4jb200_exec_pairwise(STREAM, TypeCode<T>::v, opNum, dx, X_INFO, y, Y_INFO, result,                    \
+                                     Z_INFO(resultShapeInfo), extraParams), "execPairwiseTransform" #S);               \
+    }                                                                                                                  \
+    void NativeOps::execReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParams,  \
+                                  T *result, Nd4jLong *resultShapeInfo) {                                             \
+        check(nd4jb200_exec_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,                     \
+                                   Z_INFO(resultShapeInfo), nullptr, 0), "execReduce" #S);                             \
+    }                                                                                                                  \
+    void NativeOps::execReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParams,  \
+                                  T *result, Nd4jLong *resultShapeInfo, int *dimension, int dimensionLength) {        \
+        check(nd4jb200_exec_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,                     \
+                                   Z_INFO(resultShapeInfo), host_dims(dimension, dimensionLength), dimensionLength),  \
+              "execReduce" #S);                                                                                        \
+    }                                                                                                                  \
+    R NativeOps::execReduceScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,               \
+                                     T *extraParams) {                                                                \
+        double out = 0;                                                                                                \
+        check(nd4jb200_exec_reduce_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, &out),               \
+              "execReduceScalar" #S);                                                                                  \
+        return (R) out;                                                                                                \
+    }                                                                                                                  \
+    void NativeOps::execReduce3##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,                 \
+                                   T *extraParamsVals, T *y, Nd4jLong *yShapeInfo, T *result,                         \
+                                   Nd4jLong *resultShapeInfo) {                                                       \
+        check(nd4jb200_exec_reduce3(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO, result,     \
+                                    Z_INFO(resultShapeInfo), nullptr, 0), "execReduce3" #S);                           \
+    }                                                                                                                  \
+    R NativeOps::execReduce3Scalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,              \
+                                      T *extraParamsVals, T *y, Nd4jLong *yShapeInfo) {                               \
+        double out = 0;                                                                                                \
+        check(nd4jb200_exec_reduce3_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO,      \
+                                           &out), "execReduce3Scalar" #S);                                             \
+        return (R) out;                                                                                                \
+    }                                                                                                                  \
+    void NativeOps::execReduce3##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,                 \
+                                   T *extraParamsVals, T *y, Nd4jLong *yShapeInfo, T *result,                         \
+                                   Nd4jLong *resultShapeInfoBuffer, int *dimension, int dimensionLength) {            \
+        check(nd4jb200_exec_reduce3(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO, result,     \
+                                    Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),             \
+                                    dimensionLength), "execReduce3" #S);                                               \
+    }                                                                                                                  \
+    void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,            \
+                                  Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension,                   \
+                                  int dimensionLength) {                                                              \
+        check(nd4jb200_exec_scalar_along_dimension(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, z,          \
+                                                   Z_INFO(zShapeInfo), scalars,                                       \
+                                                   host_dims(dimension, dimensionLength), dimensionLength),           \
+              "execScalar" #S);                                                                                        \
+    }                                                                                                                  \
+    R NativeOps::execSummaryStatsScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,         \
+                                           T *extraParams, bool biasCorrected) {                                      \
+        double out = 0;                                                                                                \
+        check(nd4jb200_exec_summary_stats_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams,               \
+                                                 biasCorrected ? 1 : 0, &out), "execSummaryStatsScalar" #S);           \
+        return (R) out;                                                                                                \
+    }                                                                                                                  \
+    void NativeOps::execSummaryStats##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,            \
+                                        T *extraParams, T *result, Nd4jLong *resultShapeInfo, bool biasCorrected) {   \
+        check(nd4jb200_exec_summary_stats(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,              \
+                                          Z_INFO(resultShapeInfo), nullptr, 0, biasCorrected ? 1 : 0),                \
+              "execSummaryStats" #S);                                                                                  \
+    }                                                                                                                  \
+    void NativeOps::execSummaryStats##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,            \
+                                        T *extraParams, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,   \
+                                        int dimensionLength, bool biasCorrected) {                                    \
+        check(nd4jb200_exec_summary_stats(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,              \
+                                          Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),       \
+                                          dimensionLength, biasCorrected ? 1 : 0), "execSummaryStats" #S);             \
+    }                                                                                                                  \
+    void NativeOps::execTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong xStride, T *result,       \
+                                     Nd4jLong resultStride, T *extraParams, Nd4jLong n) {                             \
+        check(nd4jb200_exec_transform_strided(STREAM, TypeCode<T>::v, opNum, dx, xStride, result, resultStride,       \
+                                              extraParams, n), "execTransform" #S);                                    \
+    }                                                                                                                  \
+    void NativeOps::execTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong *xShapeInfo, T *result,   \
+                                     Nd4jLong *resultShapeInfo, T *extraParams) {                                     \
+        check(nd4jb200_exec_transform(STREAM, TypeCode<T>::v, opNum, dx, X_INFO, result, Z_INFO(resultShapeInfo),     \
+                                      extraParams), "execTransform" #S);                                               \
+    }                                                                                                                  \
+    void NativeOps::execRandom##S(Nd4jPointer *extraPointers, int opNum, Nd4jPointer state, T *z,                     \
+                                  Nd4jLong *zShapeBuffer, T *extraArguments) {                                        \
+        check(nd4jb200_exec_random(STREAM, TypeCode<T>::v, opNum, state, z, host_info(extraPointers, 0, zShapeBuffer),\
+                                   extraArguments), "execRandom" #S);                                                  \
+    }                                                                                                                  \
+    void NativeOps::execRandom##S(Nd4jPointer *extraPointers, int opNum, Nd4jPointer state, T *x,                     \
+                                  Nd4jLong *xShapeBuffer, T *y, Nd4jLong *yShapeBuffer, T *z,                         \
+                                  Nd4jLong *zShapeBuffer, T *extraArguments) {                                        \
+        check(nd4jb200_exec_random_xy(STREAM, TypeCode<T>::v, opNum, state, x, host_info(nullptr, -1, xShapeBuffer),  \
+                                      y, host_info(nullptr, -1, yShapeBuffer), z,                                     \
+                                      host_info(nullptr, -1, zShapeBuffer), extraArguments), "execRandom" #S);         \
+    }                                                                                                                  \
+    void NativeOps::execRandom##S(Nd4jPointer *extraPointers, int opNum, Nd4jPointer state, T *x,                     \
+                                  Nd4jLong *xShapeBuffer, T *z, Nd4jLong *zShapeBuffer, T *extraArguments) {          \
+        check(nd4jb200_exec_random_x(STREAM, TypeCode<T>::v, opNum, state, x, host_info(nullptr, -1, xShapeBuffer),   \
+                                     z, host_info(nullptr, -1, zShapeBuffer), extraArguments), "execRandom" #S);       \
+    }
+
+ND4JB200_DEFINE_FAMILIES(double, Double, double)
+ND4JB200_DEFINE_FAMILIES(float, Float, float)
+ND4JB200_DEFINE_FAMILIES(float16, Half, float)
+
+#define ND4JB200_DEFINE_SCALAR(T, S, ST)                                                                               \
+    void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong xStride, T *result,           \
+                                  Nd4jLong resultStride, ST scalar, T *extraParams, Nd4jLong n) {                     \
+        check(nd4jb200_exec_scalar_strided(STREAM, TypeCode<T>::v, opNum, x, xStride, result, resultStride,           \
+                                           (double) scalar, extraParams, n), "execScalar" #S);                         \
+    }                                                                                                                  \
+    void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *result,       \
+                                  Nd4jLong *resultShapeInfo, ST scalar, T *extraParams) {                             \
+        check(nd4jb200_exec_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, result, Z_INFO(resultShapeInfo),         \
+                                   (double) scalar, extraParams), "execScalar" #S);                                    \
+    }
+ND4JB200_DEFINE_SCALAR(double, Double, double)
+ND4JB200_DEFINE_SCALAR(float, Float, float)
+ND4JB200_DEFINE_SCALAR(float16, Half, float)
+
+Nd4jPointer NativeOps::initRandom(Nd4jPointer *extraPointers, long seed, long bufferSize, Nd4jPointer ptrToBuffer) {
+    Nd4jPointer state = nd4jb200_init_random(stream_of(extraPointers), seed, bufferSize,
+                                             extraPointers ? extraPointers[0] : nullptr, ptrToBuffer);
+    if (!state) fail("initRandom");
+    return state;
+}
+void NativeOps::refreshBuffer(Nd4jPointer *extraPointers, long seed, Nd4jPointer ptrRandom) {
+    check(nd4jb200_refresh_buffer(stream_of(extraPointers), seed, ptrRandom), "refreshBuffer");
+}
+void NativeOps::reSeedBuffer(Nd4jPointer *extraPointers, long seed, Nd4jPointer ptrRandom) {
+    check(nd4jb200_reseed_buffer(seed, ptrRandom), "reSeedBuffer");
+}
+void NativeOps::destroyRandom(Nd4jPointer ptrRandom) { nd4jb200_destroy_random(ptrRandom); }
+
+void NativeOps::tadOnlyShapeInfo(Nd4jLong *xShapeInfo, int *dimension, int dimensionLength, Nd4jLong *targetBuffer,
+                                 Nd4jLong *offsetsBuffer) {
+    check(nd4jb200_tad_only_shape_info(xShapeInfo, dimension, dimensionLength, targetBuffer, offsetsBuffer),
+          "tadOnlyShapeInfo");
+}
+
+static int device_of(Nd4jPointer p) { return (int) (Nd4jLong) p; }
+
+void NativeOps::initializeDevicesAndFunctions() {}
+Nd4jPointer NativeOps::mallocHost(Nd4jLong memorySize, int) { return nd4jb200_malloc_host(memorySize); }
+Nd4jPointer NativeOps::mallocDevice(Nd4jLong memorySize, Nd4jPointer, int) { return nd4jb200_malloc_device(memorySize); }
+int NativeOps::freeHost(Nd4jPointer pointer) { return nd4jb200_free_host(pointer) == 0 ? 1 : 0; }
+int NativeOps::freeDevice(Nd4jPointer pointer, Nd4jPointer) { return nd4jb200_free_device(pointer) == 0 ? 1 : 0; }
+Nd4jPointer NativeOps::createContext() { return nullptr; }
+Nd4jPointer NativeOps::createStream() {
+    Nd4jPointer s = nd4jb200_create_stream();
+    if (!s) fail("createStream");
+    return s;
+}
+Nd4jPointer NativeOps::createEvent() {
+    Nd4jPointer e = nd4jb200_create_event();
+    if (!e) fail("createEvent");
+    return e;
+}
+int NativeOps::registerEvent(Nd4jPointer event, Nd4jPointer stream) { check(nd4jb200_register_event(event, stream), "registerEvent"); return 1; }
+int NativeOps::destroyEvent(Nd4jPointer event) { check(nd4jb200_destroy_event(event), "destroyEvent"); return 1; }
+int NativeOps::setDevice(Nd4jPointer ptrToDeviceId) { check(nd4jb200_set_device(device_of(ptrToDeviceId)), "setDevice"); return 1; }
+int NativeOps::getDevice() { return nd4jb200_get_device(); }
+int NativeOps::streamSynchronize(Nd4jPointer stream) { check(nd4jb200_stream_synchronize(stream), "streamSynchronize"); return 1; }
+int NativeOps::eventSynchronize(Nd4jPointer event) { check(nd4jb200_event_synchronize(event), "eventSynchronize"); return 1; }
+Nd4jLong NativeOps::getDeviceFreeMemory(Nd4jPointer p) { return nd4jb200_device_free_memory(device_of(p)); }
+Nd4jLong NativeOps::getDeviceTotalMemory(Nd4jPointer p) { return nd4jb200_device_total_memory(device_of(p)); }
+int NativeOps::getDeviceMajor(Nd4jPointer p) { return nd4jb200_device_major(device_of(p)); }
+int NativeOps::getDeviceMinor(Nd4jPointer p) { return nd4jb200_device_minor(device_of(p)); }
+const char *NativeOps::getDeviceName(Nd4jPointer p) { return nd4jb200_device_name(device_of(p)); }
+int NativeOps::memcpy(Nd4jPointer dst, Nd4jPointer src, Nd4jLong size, int flags, Nd4jPointer) {
+    check(nd4jb200_memcpy(dst, src, size, flags), "memcpy"); return 1;
+}
+int NativeOps::memcpyAsync(Nd4jPointer dst, Nd4jPointer src, Nd4jLong size, int flags, Nd4jPointer reserved) {
+    check(nd4jb200_memcpy_async(dst, src, size, flags, reserved), "memcpyAsync"); return 1;
+}
+int NativeOps::memset(Nd4jPointer dst, int value, Nd4jLong size, int, Nd4jPointer) {
+    check(nd4jb200_memset_async(dst, value, size, nullptr), "memset");
+    check(nd4jb200_stream_synchronize(nullptr), "memset");
+    return 1;
+}
+int NativeOps::memsetAsync(Nd4jPointer dst, int value, Nd4jLong size, int, Nd4jPointer reserved) {
+    check(nd4jb200_memset_async(dst, value, size, reserved), "memsetAsync"); return 1;
+}
+int NativeOps::getAvailableDevices() { return nd4jb200_get_available_devices(); }
+// The reference's tuning knobs for its own launch heuristics and OpenMP loops have no effect on
+// these kernels; they are accepted so that callers need no change.
+void NativeOps::enableDebugMode(bool) {}
+void NativeOps::enableVerboseMode(bool) {}
+void NativeOps::setGridLimit(int) {}
+void NativeOps::setElementThreshold(int) {}
+void NativeOps::setTADThreshold(int) {}
+void NativeOps::setOmpNumThreads(int) {}
+void NativeOps::setOmpMinThreads(int) {}

@@ -1,0 +1,197 @@
+"""GPU parity of the random family against the reference's RandomBuffer / execRandom: uniform
+bits, Bernoulli and dropout masks bit-exact (including the wrap-around hash path, generations
+above 1 and re-seeded states); Gaussian / LogNormal within 1e-5 absolute because log/cos/sin
+come from different math libraries."""
+import numpy as np
+import pytest
+import torch
+
+from libnd4j_b200 import shape as S
+from libnd4j_b200.native_ops import FLOAT
+
+pytestmark = pytest.mark.gpu
+
+SEED, TABLE = 119, 100000   # fixture of the reference's RNGTests.cpp:22-34
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+@pytest.fixture()
+def pair(ops, real_ref):
+    st = ops.initRandom(None, SEED, TABLE, None)
+    rs, table = real_ref.init_random(SEED, TABLE)
+    yield st, rs, table
+    ops.destroyRandom(st)
+    real_ref.destroy_random(rs)
+
+
+def test_table_matches_reference(ops, real_ref, pair):
+    st, rs, table = pair
+    got = torch.zeros(TABLE, dtype=torch.int64, device="cuda")
+    ops.memcpy(got, ops.lib.nd4jb200_rng_device_table(st), TABLE * 8, 3)
+    np.testing.assert_array_equal(host(got).view(np.uint64), table)
+    # values printed by the reference for this fixture
+    assert table[0] == 7465776281147007380 and table[99999] == 2165072995135488967
+
+
+def run_both(ops, ref, st, rs, op, n, extra, x=None, y=None, dt=np.float32, name="Float", gaussian=False):
+    zi = S.shape_info([1, n])
+    z = np.zeros(n, dt)
+    dz = dev(z)
+    ex = np.array(extra, dtype=dt)
+    dex = dev(ex)
+    fn = getattr(ops, "execRandom" + name)
+    if gaussian:
+        fn(None, op, st, dz, zi, dz, zi, dz, zi, dex)
+        ref.random_xy(op, rs, z, zi, z, zi, z, zi, ex)
+    elif x is None:
+        fn(None, op, st, dz, zi, dex)
+        ref.random(op, rs, z, zi, ex)
+    elif y is None:
+        fn(None, op, st, dev(x), zi, dz, zi, dex)
+        ref.random_x(op, rs, x, zi, z, zi, ex)
+    else:
+        fn(None, op, st, dev(x), zi, dev(y), zi, dz, zi, dex)
+        ref.random_xy(op, rs, x, zi, y, zi, z, zi, ex)
+    return host(dz), z
+
+
+def test_sequence_of_calls_bit_exact(ops, real_ref, pair):
+    """Uniform -> Gaussian -> Bernoulli -> DropOutInverted -> DropOut -> AlphaDropOut ->
+    ProbablisticMerge -> Linspace -> Exponential on one evolving state; the call lengths make the
+    position wrap the 100000-entry table several times (generation > 1)."""
+    st, rs, _ = pair
+    rng = np.random.default_rng(7)
+    n = 70001
+    x = rng.standard_normal(n).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32)
+    g, r = run_both(ops, real_ref, st, rs, 0, n, [0, 1])
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 0, n, [-3, 5])
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 6, n, [0, 1], gaussian=True)
+    np.testing.assert_allclose(g, r, atol=1e-5, rtol=0)
+    g, r = run_both(ops, real_ref, st, rs, 7, n, [0.3])
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 2, n, [0.5], x=x)
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 1, n, [0.8], x=x)
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 12, n, [0.6, 1.1, -0.2, 1.7], x=x)
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 3, n, [0.4], x=x, y=y)
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 4, n, [2, 9])
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 13, n, [1.5])
+    np.testing.assert_allclose(g, r, rtol=1e-5, atol=1e-6)   # pow() of two math libraries
+    g, r = run_both(ops, real_ref, st, rs, 10, n, [0, 0.5], gaussian=True)
+    np.testing.assert_allclose(g, r, rtol=1e-5, atol=1e-6)
+    seed, pos, gen, amp, size = ops.rngState(st)
+    assert (pos, gen) == (real_ref.rng_position(rs), real_ref.rng_generation(rs))
+    assert gen > 1
+
+
+def test_reseed_and_refresh(ops, real_ref, pair):
+    st, rs, _ = pair
+    ops.reSeedBuffer(None, 4242, st)
+    real_ref.reseed(rs, 4242)
+    g, r = run_both(ops, real_ref, st, rs, 0, 5000, [0, 1])
+    np.testing.assert_array_equal(g, r)
+    ops.refreshBuffer(None, 77, st)
+    real_ref.refresh(rs, 77)
+    g, r = run_both(ops, real_ref, st, rs, 0, 250007, [0, 1])
+    np.testing.assert_array_equal(g, r)
+    ops.reSeedBuffer(None, -5, st)   # a negative amplifier becomes a huge unsigned multiplier
+    real_ref.reseed(rs, -5)
+    g, r = run_both(ops, real_ref, st, rs, 7, 1000, [0.5])
+    np.testing.assert_array_equal(g, r)
+
+
+@pytest.mark.parametrize("dt,name", [(np.float64, "Double"), (np.float16, "Half")])
+def test_other_types(ops, real_ref, pair, dt, name):
+    st, rs, _ = pair
+    g, r = run_both(ops, real_ref, st, rs, 0, 150001, [0, 1], dt=dt, name=name)
+    np.testing.assert_array_equal(g, r)
+    g, r = run_both(ops, real_ref, st, rs, 7, 1001, [0.25], dt=dt, name=name)
+    np.testing.assert_array_equal(g, r)
+
+
+def test_uniform_closed_interval_and_known_values(ops, pair):
+    st, _, _ = pair
+    dz = torch.zeros(8, device="cuda")
+    ops.execRandomFloat(None, 0, st, dz, S.shape_info([1, 8]), dev(np.array([0, 1], np.float32)))
+    # first uniforms of the reference for seed 119 / table 100000
+    np.testing.assert_array_equal(host(dz)[:4], np.array([0.404720545, 0.550942004, 0.127938554, 0.622450352], np.float32))
+    assert ops.rngState(st)[1] == 8
+
+
+def test_strided_output_uses_f_order_coordinates(ops, real_ref, pair):
+    """A non-linear output view is filled through f-order coordinates, which fixes which element
+    receives which draw (include/loops/cpu/random.cpp:175)."""
+    st, rs, _ = pair
+    shape = (6, 10)
+    parent = np.zeros((6, 20), np.float32)
+    info = S.shape_info(shape, "c", [20, 2], ews=-1)
+    want = parent.ravel().copy()
+    real_ref.random(0, rs, want, info, np.array([0, 1], np.float32))
+    dz = dev(parent.ravel())
+    ops.execRandomFloat(None, 0, st, dz, info, dev(np.array([0, 1], np.float32)))
+    np.testing.assert_array_equal(host(dz), want)
+
+
+def test_sharded_ranges_reassemble_the_full_call(ops, real_ref, pair):
+    """Offset-sharding: G independent range calls with global indices reproduce one full call
+    bit for bit (Gaussian within tolerance), and a single rewind matches the reference state."""
+    st, rs, _ = pair
+    n, G = 1 << 20, 8
+    zi = S.shape_info([1, n])
+    for op, extra, arity in ((0, [0, 1], 0), (7, [0.3], 0), (2, [0.5], 1), (6, [0, 1], 2)):
+        ex = np.array(extra, np.float32)
+        x = np.random.default_rng(op).standard_normal(n).astype(np.float32)
+        want = np.zeros(n, np.float32)
+        if arity == 0:
+            real_ref.random(op, rs, want, zi, ex)
+        elif arity == 1:
+            real_ref.random_x(op, rs, x, zi, want, zi, ex)
+        else:
+            real_ref.random_xy(op, rs, want, zi, want, zi, want, zi, ex)
+        dz = torch.zeros(n, device="cuda")
+        dx = dev(x)
+        per = n // G
+        for g in range(G):
+            zs = dz[g * per:(g + 1) * per]
+            xs = dx[g * per:(g + 1) * per] if arity == 1 else (zs if arity == 2 else None)
+            ys = zs if arity == 2 else None
+            ops.execRandomRange(FLOAT, None, op, arity, st, xs, ys, zs, dev(ex), g * per, per, n)
+        ops.rngRewind(st, n)
+        if op == 6:
+            np.testing.assert_allclose(host(dz), want, atol=1e-5, rtol=0)
+        else:
+            np.testing.assert_array_equal(host(dz), want)
+        assert ops.rngState(st)[1:3] == (real_ref.rng_position(rs), real_ref.rng_generation(rs))
+
+
+def test_large_uniform_properties(ops, pair):
+    """2^26 draws: mean/variance of U(0,1), every value inside the closed interval, and a
+    re-run from the same state reproduces the same bits."""
+    st, _, _ = pair
+    n = 1 << 26
+    zi = S.shape_info([1, n])
+    ex = dev(np.array([0, 1], np.float32))
+    state = ops.rngState(st)
+    a = torch.zeros(n, device="cuda")
+    ops.execRandomFloat(None, 0, st, a, zi, ex)
+    assert 0.0 <= float(a.min()) and float(a.max()) <= 1.0
+    assert abs(float(a.double().mean()) - 0.5) < 2e-4
+    assert abs(float(a.double().var()) - 1 / 12) < 2e-4
+    ops.rngSetState(st, *state[:4])
+    b = torch.zeros(n, device="cuda")
+    ops.execRandomFloat(None, 0, st, b, zi, ex)
+    assert torch.equal(a, b)
