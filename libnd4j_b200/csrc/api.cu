@@ -190,6 +190,9 @@ Status random_common(void *stream, int dtype, int opNum, int arity, RandomState 
     RngArgs a;
     a.g.table = s->devTable; a.g.size = s->size; a.g.position = s->position;
     a.g.generation = s->generation; a.g.seed = s->seed; a.g.amplifier = s->amplifier;
+    a.g.thrGeneration = s->generation ? 0xffffffffffffffffull / (unsigned long long) s->generation : 0ull;
+    a.g.thrAmplifier = s->amplifier ? 0xffffffffffffffffull / (unsigned long long) s->amplifier : 0ull;
+    a.chunk = 0;
     a.x = x; a.y = y; a.z = z; a.extra = extra;
     a.first = first; a.count = count; a.length = length;
     a.sx = a.sy = a.sz = 1; a.mode = 0; a.yIsZ = (y == z);

@@ -113,25 +113,37 @@ Status ND_S(summary_stats)(int opNum, const ReduceCall &c, cudaStream_t st) {
     }
 }
 #elif ND_FAMILY == 4
+// Dense launches give every CTA one contiguous chunk of indices (a multiple of `quantum`), enough
+// CTAs to fill the machine a few times over, so that the per-thread cursor set-up is amortised.
+static void plan_chunks(LL count, LL quantum, LL *chunk, LL *blocks) {
+    LL want = (LL) kNumSMs * 16;
+    LL maxBlocks = ceil_div(count, quantum);
+    if (want > maxBlocks) want = maxBlocks;
+    if (want < 1) want = 1;
+    *chunk = ceil_div(ceil_div(count, want), quantum) * quantum;
+    *blocks = ceil_div(count, *chunk);
+}
 template <int OP, int ARITY>
-static Status launch_random(const RngArgs &a, cudaStream_t st) {
+static Status launch_random(RngArgs a, cudaStream_t st) {
     if (a.count <= 0) return kOk;
     constexpr int V = Elem<ND_T>::kVec;
-    LL work = a.mode == 0 ? ceil_div(a.count, V) : a.count;
-    LL blocks = ceil_div(work, kRngBlock);
-    const LL cap = (LL) kNumSMs * 32;
-    if (blocks > cap) blocks = cap;
+    LL blocks;
+    if (a.mode == 0) plan_chunks(a.count, (LL) kRngBlock * V, &a.chunk, &blocks);
+    else {
+        blocks = ceil_div(a.count, kRngBlock);
+        const LL cap = (LL) kNumSMs * 32;
+        if (blocks > cap) blocks = cap;
+    }
     k_random<ND_T, OP, ARITY><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
     count_launch();
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
 template <bool LOGNORMAL>
-static Status launch_gaussian(const RngArgs &a, cudaStream_t st) {
+static Status launch_gaussian(RngArgs a, cudaStream_t st) {
     if (a.count <= 0) return kOk;
-    LL blocks = ceil_div(ceil_div(a.count, 2), kRngBlock);
-    const LL cap = (LL) kNumSMs * 32;
-    if (blocks > cap) blocks = cap;
+    LL blocks;
+    plan_chunks(a.count, 2 * (LL) kRngBlock, &a.chunk, &blocks);
     k_random_gaussian<ND_T, LOGNORMAL><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
     count_launch();
     ND_CUDA(cudaGetLastError());

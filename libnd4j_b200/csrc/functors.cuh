@@ -27,7 +27,6 @@ template <> ND_D float absv<float>(float x) { return fabsf(x); }
 template <class C> ND_D C maxv(C a, C b) { return a > b ? a : b; }   // nd4j_max: "a > b ? a : b"
 template <class C> ND_D C minv(C a, C b) { return a < b ? a : b; }   // nd4j_min: "a < b ? a : b"
 template <class C> ND_D C sgn(C x) { return x < C(0) ? C(-1) : (x > C(0) ? C(1) : C(0)); }
-template <class C> ND_D C sigmoid(C x) { return C(1) / (C(1) + exp(-x)); }
 template <class C> ND_D bool isnanv(C x) { return x != x; }
 template <class C> ND_D bool isinfv(C x) { return isinf(x); }
 template <class C> ND_D C rel_err(C a, C b) {
@@ -40,54 +39,96 @@ template <class C> ND_D C rel_err(C a, C b) {
 // tanh = 1 - 2/(e^{2|x|} + 1) with e^{2|x|} = 2^n (1 + s), where s and the denominator are
 // carried as unevaluated float pairs (hi + lo) and the reciprocal's residual is folded into the
 // last subtraction, leaving a single rounding.
+ND_D float rcp_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 ND_D float tanh_accurate(float x) {
     const float ax = fabsf(x);
-    float t;
-    if (ax < 0.55f) {
-        const float z = ax * ax;
-        float p = -0.000966387638993646f;
-        p = fmaf(p, z, 0.0034055003387174483f);
-        p = fmaf(p, z, -0.008826388520025496f);
-        p = fmaf(p, z, 0.02186568778676557f);
-        p = fmaf(p, z, -0.053968065636603224f);
-        p = fmaf(p, z, 0.13333332981667803f);
-        p = fmaf(p, z, -0.3333333333225883f);
-        t = fmaf(ax * z, p, ax);
-    } else {
-        const float y = fminf(ax + ax, 40.0f);
-        const float n = rintf(y * 1.4426950408889634f);
-        const float rh = fmaf(-n, 0.693145751953125f, y);          // exact: ln2 split with a short high part
-        const float rl = -n * 1.42860682030941723212e-6f;
-        const float r = rh + rl;
-        const float rerr = (rh - r) + rl;
-        float q = 0.0001989928507603579f;
-        q = fmaf(q, r, 0.0013933650354159414f);
-        q = fmaf(q, r, 0.008333298469720569f);
-        q = fmaf(q, r, 0.04166646491457965f);
-        q = fmaf(q, r, 0.16666666719031667f);
-        q = fmaf(q, r, 0.5000000013468379f);
-        const float p = (r * r) * q;                                  // e^r - 1 - r
-        const float sh = r + p;
-        float sl = p - (sh - r);
-        sl += fmaf(rerr, r, rerr);
-        const float twoN = __int_as_float(((int) n + 127) << 23);
-        const float b = twoN * sh;                                    // exact scaling
-        const float a = twoN + 1.0f;
-        const float dh = a + b;                                       // e^{2|x|} + 1, high part
-        const float dl = fmaf(twoN, sl, b - (dh - a));                // and what the sum dropped
-        const float r0 = __frcp_rn(dh);
-        float e = fmaf(-dh, r0, 1.0f);
-        e = fmaf(-dl, r0, e);                                         // 1 - d * r0
-        const float two = r0 + r0;
-        const float uh = 1.0f - two;
-        const float ul = (1.0f - uh) - two;
-        t = uh + fmaf(-two, e, ul);
-    }
+    // small arguments: odd polynomial
+    const float z = ax * ax;
+    float ps = -0.000966387638993646f;
+    ps = fmaf(ps, z, 0.0034055003387174483f);
+    ps = fmaf(ps, z, -0.008826388520025496f);
+    ps = fmaf(ps, z, 0.02186568778676557f);
+    ps = fmaf(ps, z, -0.053968065636603224f);
+    ps = fmaf(ps, z, 0.13333332981667803f);
+    ps = fmaf(ps, z, -0.3333333333225883f);
+    const float ts = fmaf(ax * z, ps, ax);
+    // everything else: 1 - 2 / (2^n (1 + s) + 1); both chains are straight-line code so that the
+    // compiler can interleave them (most warps hold arguments of both kinds anyway)
+    const float y = ax + ax;
+    const float magic = 12582912.0f;                                  // 1.5 * 2^23: adding it rounds to an integer
+    const float nb = fmaf(y, 1.4426950408889634f, magic);
+    const float n = nb - magic;
+    const float rh = fmaf(-n, 0.693145751953125f, y);                 // exact: ln2 split with a short high part
+    const float rl = -n * 1.42860682030941723212e-6f;
+    const float r = rh + rl;
+    const float rerr = (rh - r) + rl;
+    float q = 0.0001989928507603579f;
+    q = fmaf(q, r, 0.0013933650354159414f);
+    q = fmaf(q, r, 0.008333298469720569f);
+    q = fmaf(q, r, 0.04166646491457965f);
+    q = fmaf(q, r, 0.16666666719031667f);
+    q = fmaf(q, r, 0.5000000013468379f);
+    const float p = (r * r) * q;                                      // e^r - 1 - r
+    const float sh = r + p;
+    float sl = p - (sh - r);
+    sl += fmaf(rerr, r, rerr);
+    // the integer n sits in the low mantissa bits of nb: move it into the exponent field
+    const float twoN = __int_as_float((__float_as_int(nb) << 23) + 0x3f800000);
+    const float b = twoN * sh;                                        // exact scaling
+    const float a = twoN + 1.0f;
+    const float dh = a + b;                                           // e^{2|x|} + 1, high part
+    const float dl = fmaf(twoN, sl, b - (dh - a));                    // and what the sum dropped
+    const float r0 = rcp_fast(dh);
+    float e = fmaf(-dh, r0, 1.0f);
+    e = fmaf(-dl, r0, e);                                             // 1 - d * r0, folded in below
+    const float two = r0 + r0;
+    const float uh = 1.0f - two;
+    const float ul = (1.0f - uh) - two;
+    const float tb = uh + fmaf(-two, e, ul);
+    float t = ax < 0.55f ? ts : tb;
+    t = ax > 9.1f ? 1.0f : t;                                         // also covers exponents that left the range
     t = copysignf(t, x);
     return x != x ? x : t;
 }
+// exp for float with error close to half an ulp (the host libm's expf is nearly correctly
+// rounded, the CUDA library's is within 2 ulp): same range reduction and (hi, lo) bookkeeping as
+// tanh_accurate, with the scaling by 2^n split in two so that subnormal results round once more.
+ND_D float exp_accurate(float x) {
+    if (!(x < 88.72284f)) return x == x ? CUDART_INF_F : x;
+    if (x < -103.972f) return 0.0f;
+    const float n = rintf(x * 1.4426950408889634f);
+    const float rh = fmaf(-n, 0.693145751953125f, x);
+    const float rl = -n * 1.42860682030941723212e-6f;
+    const float r = rh + rl;
+    const float rerr = (rh - r) + rl;
+    float q = 0.0001989928507603579f;
+    q = fmaf(q, r, 0.0013933650354159414f);
+    q = fmaf(q, r, 0.008333298469720569f);
+    q = fmaf(q, r, 0.04166646491457965f);
+    q = fmaf(q, r, 0.16666666719031667f);
+    q = fmaf(q, r, 0.5000000013468379f);
+    const float p = (r * r) * q;
+    const float sh = r + p;
+    float sl = p - (sh - r);
+    sl += fmaf(rerr, r, rerr);
+    const float t = 1.0f + sh;
+    const float e = (1.0f - t) + sh;
+    float res = t + (e + sl);
+    const int ni = (int) n, a = ni / 2, b = ni - a;
+    res *= __int_as_float((a + 127) << 23);
+    res *= __int_as_float((b + 127) << 23);
+    return res;
+}
+template <class C> ND_D C expv(C x) { return exp(x); }
+template <> ND_D float expv<float>(float x) { return exp_accurate(x); }
+
 template <class C> ND_D C tanhv(C x) { return tanh(x); }
 template <> ND_D float tanhv<float>(float x) { return tanh_accurate(x); }
+template <class C> ND_D C sigmoid(C x) { return C(1) / (C(1) + expv(-x)); }
 
 // The 14 comparison modes shared by MatchCondition, CompareAndSet, CompareAndReplace and the
 // First/LastIndex reductions (ops.h:1534-1602). Returns <0 for an unknown mode.
@@ -123,7 +164,7 @@ template <class C> ND_D int condition(C v, C compare, C eps, int mode) {
 ND_UNARY(Abs, 0, return absv(x);)
 ND_UNARY(Ceiling, 0, return ceil(x);)
 ND_UNARY(Cosine, 0, return cos(x);)
-ND_UNARY(Exp, 0, return exp(x);)
+ND_UNARY(Exp, 0, return expv(x);)
 ND_UNARY(Floor, 0, return floor(x);)
 ND_UNARY(Log, 0, return log(x);)
 ND_UNARY(Neg, 0, return -x;)
@@ -132,12 +173,12 @@ ND_UNARY(Round, 0, return round(x);)
 ND_UNARY(SetRange, 2,
          C lo = p[0], hi = p[1];
          if (x >= lo && x <= hi) return x;
-         if (lo == C(0) && hi == C(1)) { C v = C(1) / (C(1) + exp(-x)); return floor(v * (hi - lo)) + lo; }
+         if (lo == C(0) && hi == C(1)) { C v = C(1) / (C(1) + expv(-x)); return floor(v * (hi - lo)) + lo; }
          return floor(x * (hi - lo)) + lo;)
 ND_UNARY(Sigmoid, 0, return sigmoid(x);)
 ND_UNARY(Sign, 0, return C((x > C(0)) - (x < C(0)));)
 ND_UNARY(Sin, 0, return sin(x);)
-ND_UNARY(SoftPlus, 0, return log(C(1) + exp(x));)
+ND_UNARY(SoftPlus, 0, return log(C(1) + expv(x));)
 ND_UNARY(Sqrt, 0, return sqrt(x);)
 ND_UNARY(Tanh, 0, return tanhv(x);)
 ND_UNARY(ACos, 0, return acos(x);)
@@ -145,8 +186,8 @@ ND_UNARY(ASin, 0, return asin(x);)
 ND_UNARY(ATan, 0, return atan(x);)
 ND_UNARY(HardTanh, 0, return x < C(-1) ? C(-1) : (x > C(1) ? C(1) : x);)
 ND_UNARY(SoftSign, 0, return x / (C(1) + absv(x));)
-ND_UNARY(ELU, 0, return x >= C(0) ? x : exp(x) - C(1);)
-ND_UNARY(ELUDerivative, 0, return x >= C(0) ? C(1) : exp(x);)
+ND_UNARY(ELU, 0, return x >= C(0) ? x : expv(x) - C(1);)
+ND_UNARY(ELUDerivative, 0, return x >= C(0) ? C(1) : expv(x);)
 ND_UNARY(TanhDerivative, 0, C t = tanhv(x); return C(1) - t * t;)
 ND_UNARY(TimesOneMinus, 0, return x * (C(1) - x);)
 ND_UNARY(HardTanhDerivative, 0, return (x >= C(-1) && x <= C(1)) ? C(1) : C(0);)
@@ -193,9 +234,9 @@ ND_UNARY(Tan, 0, return tan(x);)
 ND_UNARY(TanDerivative, 0, C c = cos(x); return C(1) / (c * c);)
 ND_UNARY(SELU, 0,
          return x > C(0) ? C(ND_SELU_LAMBDA) * x
-                         : C(ND_SELU_LAMBDA) * (C(ND_SELU_ALPHA) * exp(x) - C(ND_SELU_ALPHA));)
+                         : C(ND_SELU_LAMBDA) * (C(ND_SELU_ALPHA) * expv(x) - C(ND_SELU_ALPHA));)
 ND_UNARY(SELUDerivative, 0,
-         return x > C(0) ? C(ND_SELU_LAMBDA) : C(ND_SELU_ALPHA) * C(ND_SELU_LAMBDA) * exp(x);)
+         return x > C(0) ? C(ND_SELU_LAMBDA) : C(ND_SELU_ALPHA) * C(ND_SELU_LAMBDA) * expv(x);)
 ND_UNARY(MatchConditionT, 3,
          int r = condition(x, p[0], p[1], (int) p[2]);
          return r < 0 ? x : C(r);)
@@ -219,7 +260,7 @@ ND_UNARY(Rint, 0, return rint(x);)
 ND_UNARY(LogSigmoid, 0, return log(sigmoid(x));)
 ND_UNARY(LogSigmoidDerivative, 0, C ex = pow(C(ND_E), x); return C(1) / (ex + C(1));)
 ND_UNARY(Erfc, 0, return erfc(x);)
-ND_UNARY(Expm1, 0, return exp(x) - C(1);)
+ND_UNARY(Expm1, 0, return expv(x) - C(1);)
 ND_UNARY(PowDerivativeT, 1, return p[0] * pow(x, p[0] - C(1));)
 ND_UNARY(ATanh, 0, return atanh(x);)
 ND_UNARY(Reciprocal, 0, return C(1) / x;)
@@ -308,9 +349,9 @@ ND_BINARY(BinaryRelativeError, 1, return rel_err(x, y) > p[0] ? C(1) : C(0);)
 ND_BINARY(BinaryMinimumAbsoluteRelativeError, 2,
           return rel_err(x, y) > p[0] ? (absv(x - y) < p[1] ? C(0) : C(1)) : C(0);)
 ND_BINARY(PowDerivativeB, 0, return y * pow(x, y - C(1));)
-ND_BINARY(LogPoisonLoss, 0, return exp(y) - x * y;)
+ND_BINARY(LogPoisonLoss, 0, return expv(y) - x * y;)
 ND_BINARY(LogPoisonLossFull, 0,
-          return exp(y) - x * y + (x * log(x) - x + C(0.5) * log(C(2.0 * 3.14159265358979323846) * x));)
+          return expv(y) - x * y + (x * log(x) - x + C(0.5) * log(C(2.0 * 3.14159265358979323846) * x));)
 
 #define ND_PAIRWISE_TABLE(X)                                                                       \
     X(0, Add) X(1, Copy) X(2, Divide) X(3, EqualTo) X(4, GreaterThan) X(5, LessThan)               \

@@ -91,17 +91,22 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
             if (a.mode == 0) {
                 LL j = j0 + (LL) lane * V;
                 const LL step = (LL) g * V;
-                // two packs in flight per operand before any dependent arithmetic
-                for (; j + step < j1; j += 2 * step) {
-                    Pack<T> xa = load_pack(xb + j), xc = load_pack(xb + j + step);
-                    Pack<T> ya, yc;
-                    if (P::kInputs == 2) { ya = load_pack(yb + j); yc = load_pack(yb + j + step); }
+                // U packs per operand are requested before any dependent arithmetic, so that every
+                // lane keeps 64 bytes (or 2 x 32 with two operands) in flight
+                constexpr int U = P::kInputs == 2 ? 2 : 4;
+                for (; j + (U - 1) * step < j1; j += U * step) {
+                    Pack<T> xv[U], yv[U];
 #pragma unroll
-                    for (int k = 0; k < V; k++)
-                        P::accum(s, Elem<T>::to_c(xa.v[k]), P::kInputs == 2 ? Elem<T>::to_c(ya.v[k]) : C(0), j + k, p);
+                    for (int u = 0; u < U; u++) {
+                        xv[u] = load_pack(xb + j + u * step);
+                        if (P::kInputs == 2) yv[u] = load_pack(yb + j + u * step);
+                    }
 #pragma unroll
-                    for (int k = 0; k < V; k++)
-                        P::accum(s, Elem<T>::to_c(xc.v[k]), P::kInputs == 2 ? Elem<T>::to_c(yc.v[k]) : C(0), j + step + k, p);
+                    for (int u = 0; u < U; u++)
+#pragma unroll
+                        for (int k = 0; k < V; k++)
+                            P::accum(s, Elem<T>::to_c(xv[u].v[k]), P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[k]) : C(0),
+                                     j + u * step + k, p);
                 }
                 for (; j < j1; j += step) {
                     Pack<T> xa = load_pack(xb + j);
@@ -147,65 +152,89 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
     }
 }
 
-// blockDim = (32, 8). blockIdx.x enumerates (hi, tile of 32 consecutive TADs); blockIdx.y is the
-// row split.
+// blockDim = (32, 8). blockIdx.x enumerates (hi, tile of 32 * W consecutive TADs); blockIdx.y is
+// the row split. W = 1, or the 128-bit pack width when the TAD bases allow aligned vector loads:
+// a thread then owns W neighbouring TADs and a warp reads 512 contiguous bytes per row.
 constexpr int kColRows = 8;
+constexpr int kColUnroll = 4;
 
-template <class T, class P>
+template <class T, class P, bool VEC>
 __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs a) {
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
+    constexpr int W = VEC ? Elem<T>::kVec : 1;
     C p[P::kParams ? P::kParams : 1];
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     const T *ax = static_cast<const T *>(a.x);
     const T *ay = static_cast<const T *>(a.y);
     T *az = static_cast<T *>(a.z);
 
-    const LL tilesPerHi = (a.colLo + 31) / 32;
+    const LL tilesPerHi = (a.colLo + 32 * W - 1) / (32 * W);
     const LL hi = blockIdx.x / tilesPerHi;
     const LL tile = blockIdx.x - hi * tilesPerHi;
-    const LL lo = tile * 32 + threadIdx.x;
-    const bool active = lo < a.colLo;
+    const LL lo = (tile * 32 + threadIdx.x) * W;
+    const bool active = lo < a.colLo;          // colLo is a multiple of W on the vector path
     const LL r = hi * a.colLo + lo;
 
-    State s;
-    P::init(s);
+    State s[W];
+#pragma unroll
+    for (int w = 0; w < W; w++) P::init(s[w]);
     if (active) {
         const T *xb = ax + view_offset(a.xOuterHi, hi) + lo;
         const T *yb = P::kInputs == 2 ? ay + view_offset(a.yOuterHi, hi) + lo : nullptr;
         const LL step = (LL) gridDim.y * kColRows;
         LL j = (LL) blockIdx.y * kColRows + threadIdx.y;
-        // four independent rows in flight per thread
-        for (; j + 3 * step < a.tadLen; j += 4 * step) {
-            C x0 = Elem<T>::load(xb + j * a.colStrideX);
-            C x1 = Elem<T>::load(xb + (j + step) * a.colStrideX);
-            C x2 = Elem<T>::load(xb + (j + 2 * step) * a.colStrideX);
-            C x3 = Elem<T>::load(xb + (j + 3 * step) * a.colStrideX);
-            C y0 = C(0), y1 = C(0), y2 = C(0), y3 = C(0);
-            if (P::kInputs == 2) {
-                y0 = Elem<T>::load(yb + j * a.colStrideY);
-                y1 = Elem<T>::load(yb + (j + step) * a.colStrideY);
-                y2 = Elem<T>::load(yb + (j + 2 * step) * a.colStrideY);
-                y3 = Elem<T>::load(yb + (j + 3 * step) * a.colStrideY);
+        for (; j + (kColUnroll - 1) * step < a.tadLen; j += kColUnroll * step) {
+            if (VEC) {
+                Pack<T> xv[kColUnroll], yv[kColUnroll];
+#pragma unroll
+                for (int u = 0; u < kColUnroll; u++) {
+                    xv[u] = load_pack(xb + (j + u * step) * a.colStrideX);
+                    if (P::kInputs == 2) yv[u] = load_pack(yb + (j + u * step) * a.colStrideY);
+                }
+#pragma unroll
+                for (int u = 0; u < kColUnroll; u++)
+#pragma unroll
+                    for (int w = 0; w < W; w++)
+                        P::accum(s[w], Elem<T>::to_c(xv[u].v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0),
+                                 j + u * step, p);
+            } else {
+                C xv[kColUnroll], yv[kColUnroll];
+#pragma unroll
+                for (int u = 0; u < kColUnroll; u++) {
+                    xv[u] = Elem<T>::load(xb + (j + u * step) * a.colStrideX);
+                    yv[u] = P::kInputs == 2 ? Elem<T>::load(yb + (j + u * step) * a.colStrideY) : C(0);
+                }
+#pragma unroll
+                for (int u = 0; u < kColUnroll; u++) P::accum(s[0], xv[u], yv[u], j + u * step, p);
             }
-            P::accum(s, x0, y0, j, p);
-            P::accum(s, x1, y1, j + step, p);
-            P::accum(s, x2, y2, j + 2 * step, p);
-            P::accum(s, x3, y3, j + 3 * step, p);
         }
         for (; j < a.tadLen; j += step) {
-            C xv = Elem<T>::load(xb + j * a.colStrideX);
-            C yv = P::kInputs == 2 ? Elem<T>::load(yb + j * a.colStrideY) : C(0);
-            P::accum(s, xv, yv, j, p);
+            if (VEC) {
+                Pack<T> xv = load_pack(xb + j * a.colStrideX), yv;
+                if (P::kInputs == 2) yv = load_pack(yb + j * a.colStrideY);
+#pragma unroll
+                for (int w = 0; w < W; w++)
+                    P::accum(s[w], Elem<T>::to_c(xv.v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv.v[w]) : C(0), j, p);
+            } else {
+                C xv = Elem<T>::load(xb + j * a.colStrideX);
+                C yv = P::kInputs == 2 ? Elem<T>::load(yb + j * a.colStrideY) : C(0);
+                P::accum(s[0], xv, yv, j, p);
+            }
         }
     }
     __shared__ State rows[kColRows][32];
-    rows[threadIdx.y][threadIdx.x] = s;
-    __syncthreads();
-    if (threadIdx.y == 0 && active) {
-        for (int k = 1; k < kColRows; k++) P::merge(s, rows[k][threadIdx.x]);
-        if (a.splits == 1) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
-        else reinterpret_cast<State *>(a.partials)[r * a.splits + blockIdx.y] = s;
+#pragma unroll
+    for (int w = 0; w < W; w++) {
+        if (w) __syncthreads();
+        rows[threadIdx.y][threadIdx.x] = s[w];
+        __syncthreads();
+        if (threadIdx.y == 0 && active) {
+            State m = s[w];
+            for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][threadIdx.x]);
+            if (a.splits == 1) az[r + w] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+            else reinterpret_cast<State *>(a.partials)[(r + w) * a.splits + blockIdx.y] = m;
+        }
     }
 }
 

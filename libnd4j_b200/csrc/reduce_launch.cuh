@@ -60,9 +60,12 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         a.xOuterHi = xo; a.xOuterHi.rank = xo.rank - 1;
         a.yOuterHi = yo; a.yOuterHi.rank = yo.rank - 1;
         const LL hiCount = a.numTads / a.colLo;
-        const LL tiles = hiCount * ceil_div(a.colLo, 32);
+        // 128-bit loads across neighbouring TADs need every TAD row to start on a 16-byte boundary
+        bool vec = a.colLo % V == 0 && aligned16(a.x) && a.colStrideX % V == 0 && view_strides_multiple_of(a.xOuterHi, V);
+        if (two) vec = vec && aligned16(a.y) && a.colStrideY % V == 0 && view_strides_multiple_of(a.yOuterHi, V);
+        const LL tiles = hiCount * ceil_div(a.colLo, 32 * (vec ? V : 1));
         LL splits = ceil_div((LL) kNumSMs * 8, tiles);
-        const LL maxSplits = a.tadLen / (kColRows * 8);   // at least 8 rows per thread
+        const LL maxSplits = a.tadLen / (kColRows * 2 * kColUnroll);   // at least two unrolled trips per thread
         if (splits > maxSplits) splits = maxSplits;
         if (splits < 1) splits = 1;
         if (splits > 4096) splits = 4096;
@@ -72,7 +75,8 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
             a.partials = static_cast<char *>(ws) + 256;
         }
         dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
-        k_reduce_cols<T, P><<<grid, block, 0, stream>>>(a);
+        if (vec) k_reduce_cols<T, P, true><<<grid, block, 0, stream>>>(a);
+        else k_reduce_cols<T, P, false><<<grid, block, 0, stream>>>(a);
         count_launch();
     } else {
         if (xUnit && yUnit) {
@@ -83,7 +87,10 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
             a.mode = rank1 ? 1 : 2;
         }
         const LL perLane = a.mode == 0 ? V : 1;
-        if (a.tadLen * (LL) sizeof(T) >= 8192) a.group = kBlock;
+        // a warp per TAD needs no barrier; a whole CTA per TAD only pays off for long TADs or when
+        // there are too few TADs to fill the machine with warps
+        const LL tadBytes = a.tadLen * (LL) sizeof(T);
+        if (tadBytes > 262144 || (tadBytes >= 8192 && a.numTads < 4096)) a.group = kBlock;
         else {
             int g = 1;
             while (g < 32 && (LL) g * perLane * 4 < a.tadLen) g <<= 1;

@@ -108,6 +108,12 @@ def test_transform_other_types(ops, real_ref, dt, name, op):
     want = real_ref.transform(op, x, info, np.empty_like(x), info, ex)
     dz = dev(np.zeros(n, dt))
     getattr(ops, "execTransform" + name)(None, op, dev(x), info, dz, info, None if ex is None else dev(ex))
+    if dt == np.float16 and op == 51:
+        # HardSigmoid: the reference rounds the constant 0.2 and every intermediate to half, the
+        # GPU rounds once at the end; near the zero crossing that is many ulps of a tiny result
+        # but at most two half-ulps of the intermediates (magnitude 0.5)
+        assert np.abs(host(dz).astype(np.float64) - want.astype(np.float64)).max() <= 2 * 2.0 ** -11
+        return
     d = ulp_distance(host(dz), want)
     # the reference rounds to half after every operation of a composite functor, the GPU once
     assert d.max() <= (3 if dt == np.float16 else 2), d.max()
