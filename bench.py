@@ -198,7 +198,7 @@ def time_loop(torch, stream, fn, iters):
     return start.elapsed_time(stop) / iters
 
 
-def family_table(torch, ops, calls, stream, peak, quick):
+def family_table(torch, ops, calls, stream, peak, quick, only=None):
     """Achieved HBM GB/s of the other op families at their configured sizes (algorithmic bytes /
     CUDA-event time, inputs larger than L2 or L2 flushed by the rotation of buffers)."""
     from libnd4j_b200 import shape as S
@@ -207,6 +207,10 @@ def family_table(torch, ops, calls, stream, peak, quick):
     dev = torch.device("cuda")
 
     def record(name, nbytes, elems, fn, iters=20):
+        if only and only not in name:
+            return
+        if only:
+            iters = min(iters, 3)
         for _ in range(3):
             fn()
         ms = time_loop(torch, stream, fn, iters)
@@ -414,7 +418,7 @@ def run_ours(args):
         with torch.cuda.stream(stream):
             del dx, dy, t1, t2, dz
             torch.cuda.empty_cache()
-            families = family_table(torch, ops, calls, stream, peak, args.quick)
+            families = family_table(torch, ops, calls, stream, peak, args.quick, args.only)
     elif world > 1:
         families = sharded_families(torch, dist, ops, calls, stream, world, rank, args.quick)
 
@@ -507,6 +511,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller sizes for the families table")
     ap.add_argument("--no-families", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--only", default=None, help="profiling aid: run only the families whose name contains this text, "
+                                                 "three timed launches each")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

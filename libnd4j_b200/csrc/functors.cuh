@@ -36,9 +36,14 @@ template <class C> ND_D C rel_err(C a, C b) {
 
 // tanh for float with error well below one ulp, so that results stay within 2 ulp of the host
 // libm the reference calls (templatemath.h:847). |x| < 0.55: odd minimax polynomial. Otherwise
-// tanh = 1 - 2/(e^{2|x|} + 1) with e^{2|x|} = 2^n (1 + s), where s and the denominator are
-// carried as unevaluated float pairs (hi + lo) and the reciprocal's residual is folded into the
-// last subtraction, leaving a single rounding.
+// |x| = k/16 + d with |d| <= 1/32, and
+//     tanh(k/16 + d) = T + (1 - T^2) tanh(d) / (1 + T tanh(d)),   T = tanh(k/16),
+// where T comes from a 139-entry table as an unevaluated float pair and the second term is at
+// most 0.03, so its rounding errors are a small fraction of an ulp of the result. Both chains are
+// straight-line code (most warps hold arguments of both kinds anyway).
+static __device__ const float4 kTanhTable[139] = {
+#include "tanh_table.inc"
+};
 ND_D float rcp_fast(float x) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -46,7 +51,6 @@ ND_D float rcp_fast(float x) {
 }
 ND_D float tanh_accurate(float x) {
     const float ax = fabsf(x);
-    // small arguments: odd polynomial
     const float z = ax * ax;
     float ps = -0.000966387638993646f;
     ps = fmaf(ps, z, 0.0034055003387174483f);
@@ -56,41 +60,18 @@ ND_D float tanh_accurate(float x) {
     ps = fmaf(ps, z, 0.13333332981667803f);
     ps = fmaf(ps, z, -0.3333333333225883f);
     const float ts = fmaf(ax * z, ps, ax);
-    // everything else: 1 - 2 / (2^n (1 + s) + 1); both chains are straight-line code so that the
-    // compiler can interleave them (most warps hold arguments of both kinds anyway)
-    const float y = ax + ax;
-    const float magic = 12582912.0f;                                  // 1.5 * 2^23: adding it rounds to an integer
-    const float nb = fmaf(y, 1.4426950408889634f, magic);
-    const float n = nb - magic;
-    const float rh = fmaf(-n, 0.693145751953125f, y);                 // exact: ln2 split with a short high part
-    const float rl = -n * 1.42860682030941723212e-6f;
-    const float r = rh + rl;
-    const float rerr = (rh - r) + rl;
-    float q = 0.0001989928507603579f;
-    q = fmaf(q, r, 0.0013933650354159414f);
-    q = fmaf(q, r, 0.008333298469720569f);
-    q = fmaf(q, r, 0.04166646491457965f);
-    q = fmaf(q, r, 0.16666666719031667f);
-    q = fmaf(q, r, 0.5000000013468379f);
-    const float p = (r * r) * q;                                      // e^r - 1 - r
-    const float sh = r + p;
-    float sl = p - (sh - r);
-    sl += fmaf(rerr, r, rerr);
-    // the integer n sits in the low mantissa bits of nb: move it into the exponent field
-    const float twoN = __int_as_float((__float_as_int(nb) << 23) + 0x3f800000);
-    const float b = twoN * sh;                                        // exact scaling
-    const float a = twoN + 1.0f;
-    const float dh = a + b;                                           // e^{2|x|} + 1, high part
-    const float dl = fmaf(twoN, sl, b - (dh - a));                    // and what the sum dropped
-    const float r0 = rcp_fast(dh);
-    float e = fmaf(-dh, r0, 1.0f);
-    e = fmaf(-dl, r0, e);                                             // 1 - d * r0, folded in below
-    const float two = r0 + r0;
-    const float uh = 1.0f - two;
-    const float ul = (1.0f - uh) - two;
-    const float tb = uh + fmaf(-two, e, ul);
+    // k = round(16 |x|) limited to the table; adding 1.5 * 2^23 leaves k in the low mantissa bits
+    const float magic = 12582912.0f;
+    const float kb = fmaf(fminf(fmaxf(ax, 0.5f), 9.125f), 16.0f, magic);
+    const float kf = kb - magic;
+    const float4 e = __ldg(&kTanhTable[(__float_as_int(kb) & 0xff) - 8]);   // {T hi, T lo, 1 - T^2, 0}
+    const float d = fmaf(-kf, 0.0625f, ax);                                  // exact
+    const float d2 = d * d;
+    const float td = fmaf(d * d2, fmaf(0.13333333f, d2, -0.33333334f), d);   // tanh(d), |d| <= 1/32
+    const float corr = (e.z * td) * rcp_fast(fmaf(e.x, td, 1.0f));
+    const float tb = e.x + (e.y + corr);
     float t = ax < 0.55f ? ts : tb;
-    t = ax > 9.1f ? 1.0f : t;                                         // also covers exponents that left the range
+    t = ax > 9.1f ? 1.0f : t;
     t = copysignf(t, x);
     return x != x ? x : t;
 }
@@ -212,7 +193,7 @@ ND_UNARY(CompareAndSetT, 4,
 ND_UNARY(ReplaceNans, 1, return isnanv(x) ? p[0] : x;)
 ND_UNARY(StabilizeFP16, 0, return x <= C(0) ? C(0.001) : x;)
 ND_UNARY(Cube, 0, return x * x * x;)
-ND_UNARY(CubeDerivative, 0, return C(3) * x * x;)
+ND_UNARY(CubeDerivative, 0, return C(3) * (x * x);)   // the reference build squares first
 ND_UNARY(HardSigmoid, 0, return minv(C(1), maxv(C(0), C(0.2f) * x + C(0.5f)));)
 ND_UNARY(HardSigmoidDerivative, 0, return (x < C(-2.5f) || x > C(2.5f)) ? C(0) : C(0.2f);)
 ND_UNARY(RationalTanh, 0,

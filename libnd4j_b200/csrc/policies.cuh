@@ -15,6 +15,10 @@ template <class Op, class C> struct Reduce {
     static constexpr int kParams = Op::kParams;
     ND_D static void init(State &s) { s.v = Op::template identity<C>(); }
     ND_D static void accum(State &s, C x, C, LL, const C *p) { s.v = Op::template combine<C>(s.v, Op::template map<C>(x, p)); }
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+#pragma unroll
+        for (int i = 0; i < N; i++) accum(s, x[i], y[i], j0 + i * jstep, p);
+    }
     ND_D static void merge(State &s, const State &o) { s.v = Op::template combine<C>(s.v, o.v); }
     ND_D static C finish(const State &s, LL n, const C *p) { return Op::template post<C>(s.v, n, p); }
 };
@@ -31,6 +35,10 @@ template <class C> struct LogSumExp {
         if (x > s.m) { s.s = s.s * exp(s.m - x) + C(1); s.m = x; }
         else if (x == s.m) s.s += C(1);      // also covers +-inf without producing inf-inf
         else s.s += exp(x - s.m);
+    }
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+#pragma unroll
+        for (int i = 0; i < N; i++) accum(s, x[i], y[i], j0 + i * jstep, p);
     }
     ND_D static void merge(State &s, const State &o) {
         if (o.s == C(0)) return;
@@ -62,6 +70,10 @@ template <int kind, class C> struct Reduce3 {
             s.acc += same ? C(0) : C(1);
         } else if (kind == 6) { s.e0 += minv(x, y); s.e1 += maxv(x, y); }
         else s.acc += (x == y) ? C(0) : C(1);
+    }
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+#pragma unroll
+        for (int i = 0; i < N; i++) accum(s, x[i], y[i], j0 + i * jstep, p);
     }
     ND_D static void merge(State &s, const State &o) { s.acc += o.acc; s.e0 += o.e0; s.e1 += o.e1; }
     ND_D static C finish(const State &s, LL n, const C *) {
@@ -96,6 +108,21 @@ template <int kind, class C> struct IndexExtreme {
         C v = (kind >= 2) ? absv(x) : x;
         if (better(v, j, s.v, s.i)) { s.v = v; s.i = j; }
     }
+    // a run of ascending indices needs no tie-break: the first strictly better element wins, and
+    // only the winner of the run is compared (with the index tie-break) against the state
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+        C best = (kind >= 2) ? absv(x[0]) : x[0];
+        int at = 0;
+#pragma unroll
+        for (int i = 1; i < N; i++) {
+            C v = (kind >= 2) ? absv(x[i]) : x[i];
+            bool b = (kind == 0 || kind == 2) ? v > best : v < best;
+            best = b ? v : best;
+            at = b ? i : at;
+        }
+        LL j = j0 + at * jstep;
+        if (better(best, j, s.v, s.i)) { s.v = best; s.i = j; }
+    }
     ND_D static void merge(State &s, const State &o) { if (better(o.v, o.i, s.v, s.i)) { s.v = o.v; s.i = o.i; } }
     ND_D static C finish(const State &s, LL, const C *) { return C(s.i); }
 };
@@ -117,6 +144,10 @@ template <int kind, class C> struct IndexMatch {
         bool hit = c < 0 ? (x != C(0)) : (c != 0);
         if (hit) take(s, j);
     }
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+#pragma unroll
+        for (int i = 0; i < N; i++) accum(s, x[i], y[i], j0 + i * jstep, p);
+    }
     ND_D static void merge(State &s, const State &o) { if (o.i >= 0) take(s, o.i); }
     ND_D static C finish(const State &s, LL, const C *) { return C(s.i); }
 };
@@ -126,7 +157,7 @@ template <int kind, class C> struct IndexMatch {
 // Here each thread keeps double sums of (x - k) and (x - k)^2 around a pivot k taken from its
 // own data (3 flops per element), and partial states are re-centred when merged; the moments
 // come out of the same fp64 arithmetic class as the reference's.
-// kind: 0 variance, 1 standard deviation. p[0] carries biasCorrected (0/1), set by the host.
+// kind: 0 variance, 1 standard deviation.
 template <int kind, class C> struct Stats {
     struct State { double n, s1, s2, k; };
     static constexpr int kInputs = 1;
@@ -137,6 +168,17 @@ template <int kind, class C> struct Stats {
         if (s.n == 0) s.k = v;
         double d = v - s.k;
         s.n += 1.0; s.s1 += d; s.s2 += d * d;
+    }
+    // N elements at once: their offsets from the pivot are summed in the element's own compute
+    // type first (N is at most 8, so this adds a few units in the last place of a short sum) and
+    // only the two short sums enter the double accumulators
+    template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
+        if (s.n == 0) s.k = (double) x[0];
+        const C k = (C) s.k;
+        C a = C(0), b = C(0);
+#pragma unroll
+        for (int i = 0; i < N; i++) { C d = x[i] - k; a += d; b += d * d; }
+        s.n += (double) N; s.s1 += (double) a; s.s2 += (double) b;
     }
     ND_D static void merge(State &s, const State &o) {
         if (o.n == 0) return;

@@ -10,17 +10,20 @@
 //              walks one TAD segment with 128-bit loads when alignment allows.
 //   across-TAD (k_reduce_cols): consecutive TADs are adjacent in memory and a TAD's own
 //              elements are far apart (column reductions of row-major arrays, row reductions of
-//              f-order views). 32 lanes read 32 neighbouring TADs per row; 8 row-lanes per CTA
-//              and `splits` CTAs share the rows of one TAD tile.
+//              f-order views). 32 lanes read neighbouring TADs per row (128-bit loads when the
+//              rows are 16-byte aligned); 8 row-lanes per CTA and `splits` CTAs share the rows of
+//              one TAD tile.
 //
 // A TAD may be cut into `splits` segments handled by different groups/CTAs; each writes its
 // partial state to a scratch array and k_reduce_finalize merges the partials of a TAD in
-// segment order. All merges (lanes, warps, segments) happen in an order fixed by indices, never
-// by arrival, so a call is bit-reproducible run to run.
+// an order fixed by the segment numbers. All merges (lanes, warps, segments) happen in an order
+// fixed by indices, never by arrival, so a call is bit-reproducible run to run.
 //
 // Policy concept (see policies.cuh):
 //   typedef State;  static constexpr int kInputs (1|2), kParams;
 //   init(State&);  accum(State&, C x, C y, LL j, const C* p);  merge(State&, const State&);
+//   accum_many<N>(State&, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C* p)
+//       folds N elements with indices j0, j0 + jstep, ... (ascending) in one go;
 //   C finish(const State&, LL n, const C* p);
 #pragma once
 #include "device_utils.cuh"
@@ -47,6 +50,19 @@ struct ReduceArgs {
 };
 
 constexpr int kBlock = 256;
+
+template <class T, class P, int N>
+ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, LL j0,
+                    const typename Elem<T>::C *p) {
+    typedef typename Elem<T>::C C;
+    C xa[N], ya[N];
+#pragma unroll
+    for (int k = 0; k < N; k++) {
+        xa[k] = Elem<T>::to_c(xv.v[k]);
+        ya[k] = P::kInputs == 2 ? Elem<T>::to_c(yv.v[k]) : C(0);
+    }
+    P::template accum_many<N>(s, xa, ya, j0, 1, p);
+}
 
 template <class T, class P>
 __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
@@ -102,19 +118,13 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
                         if (P::kInputs == 2) yv[u] = load_pack(yb + j + u * step);
                     }
 #pragma unroll
-                    for (int u = 0; u < U; u++)
-#pragma unroll
-                        for (int k = 0; k < V; k++)
-                            P::accum(s, Elem<T>::to_c(xv[u].v[k]), P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[k]) : C(0),
-                                     j + u * step + k, p);
+                    for (int u = 0; u < U; u++) fold_pack<T, P, V>(s, xv[u], yv[u], j + u * step, p);
                 }
                 for (; j < j1; j += step) {
                     Pack<T> xa = load_pack(xb + j);
                     Pack<T> ya;
                     if (P::kInputs == 2) ya = load_pack(yb + j);
-#pragma unroll
-                    for (int k = 0; k < V; k++)
-                        P::accum(s, Elem<T>::to_c(xa.v[k]), P::kInputs == 2 ? Elem<T>::to_c(ya.v[k]) : C(0), j + k, p);
+                    fold_pack<T, P, V>(s, xa, ya, j, p);
                 }
             } else if (a.mode == 1) {
                 const LL sx = a.xInner.rank ? a.xInner.stride[0] : 0;
@@ -193,20 +203,23 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
                     if (P::kInputs == 2) yv[u] = load_pack(yb + (j + u * step) * a.colStrideY);
                 }
 #pragma unroll
-                for (int u = 0; u < kColUnroll; u++)
+                for (int w = 0; w < W; w++) {
+                    C xa[kColUnroll], ya[kColUnroll];
 #pragma unroll
-                    for (int w = 0; w < W; w++)
-                        P::accum(s[w], Elem<T>::to_c(xv[u].v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0),
-                                 j + u * step, p);
+                    for (int u = 0; u < kColUnroll; u++) {
+                        xa[u] = Elem<T>::to_c(xv[u].v[w]);
+                        ya[u] = P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0);
+                    }
+                    P::template accum_many<kColUnroll>(s[w], xa, ya, j, step, p);
+                }
             } else {
-                C xv[kColUnroll], yv[kColUnroll];
+                C xa[kColUnroll], ya[kColUnroll];
 #pragma unroll
                 for (int u = 0; u < kColUnroll; u++) {
-                    xv[u] = Elem<T>::load(xb + (j + u * step) * a.colStrideX);
-                    yv[u] = P::kInputs == 2 ? Elem<T>::load(yb + (j + u * step) * a.colStrideY) : C(0);
+                    xa[u] = Elem<T>::load(xb + (j + u * step) * a.colStrideX);
+                    ya[u] = P::kInputs == 2 ? Elem<T>::load(yb + (j + u * step) * a.colStrideY) : C(0);
                 }
-#pragma unroll
-                for (int u = 0; u < kColUnroll; u++) P::accum(s[0], xv[u], yv[u], j + u * step, p);
+                P::template accum_many<kColUnroll>(s[0], xa, ya, j, step, p);
             }
         }
         for (; j < a.tadLen; j += step) {
@@ -238,7 +251,8 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
     }
 }
 
-// One thread per TAD merges that TAD's `splits` partial states in segment order.
+// One warp per TAD: lane l folds the partial states l, l + 32, ... of that TAD in ascending
+// order (coalesced reads), then the 32 lane results are merged by the fixed butterfly.
 template <class T, class P>
 __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) {
     typedef typename Elem<T>::C C;
@@ -247,10 +261,14 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     T *az = static_cast<T *>(a.z);
     const State *parts = reinterpret_cast<const State *>(a.partials);
-    for (LL r = (LL) blockIdx.x * kBlock + threadIdx.x; r < a.numTads; r += (LL) gridDim.x * kBlock) {
-        State s = parts[r * a.splits];
-        for (int k = 1; k < a.splits; k++) P::merge(s, parts[r * a.splits + k]);
-        az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+    const int lane = threadIdx.x & 31;
+    const LL warpsTotal = (LL) gridDim.x * (kBlock / 32);
+    for (LL r = (LL) blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); r < a.numTads; r += warpsTotal) {
+        State s;
+        P::init(s);
+        for (int k = lane; k < a.splits; k += 32) P::merge(s, parts[r * a.splits + k]);
+        group_merge<P>(s, 32);
+        if (lane == 0) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
     }
 }
 

@@ -118,8 +118,8 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         count_launch();
     }
     if (a.splits > 1) {
-        LL blocks = ceil_div(a.numTads, kBlock);
-        if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+        LL blocks = ceil_div(a.numTads, kBlock / 32);   // one warp per TAD
+        if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
         k_reduce_finalize<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
         count_launch();
     }

@@ -107,7 +107,7 @@ static float transform_f32(int op, float x, const float *p) {
         case 46: return isnan(x) ? p[0] : x;
         case 47: return x <= 0.0f ? 0.001f : x;
         case 49: return x * x * x;
-        case 50: return 3.0f * x * x;
+        case 50: return 3.0f * (x * x);   /* the reference build (associative-math) squares first */
         case 51: { float v = 0.2f * x + 0.5f; v = v > 0.0f ? v : 0.0f; return v < 1.0f ? v : 1.0f; }
         case 52: return (x < -2.5f || x > 2.5f) ? 0.0f : 0.2f;
         case 53: {
