@@ -193,7 +193,7 @@ ND_UNARY(CompareAndSetT, 4,
 ND_UNARY(ReplaceNans, 1, return isnanv(x) ? p[0] : x;)
 ND_UNARY(StabilizeFP16, 0, return x <= C(0) ? C(0.001) : x;)
 ND_UNARY(Cube, 0, return x * x * x;)
-ND_UNARY(CubeDerivative, 0, return C(3) * (x * x);)   // the reference build squares first
+ND_UNARY(CubeDerivative, 0, return C(3) * x * x;)
 ND_UNARY(HardSigmoid, 0, return minv(C(1), maxv(C(0), C(0.2f) * x + C(0.5f)));)
 ND_UNARY(HardSigmoidDerivative, 0, return (x < C(-2.5f) || x > C(2.5f)) ? C(0) : C(0.2f);)
 ND_UNARY(RationalTanh, 0,

@@ -56,7 +56,10 @@ CANCELLING = {13: (4, 1.0), 21: (2, 1.0), 22: (2, 0.0), 23: (4, 1.0), 29: (4, 0.
               61: (2, 0.0), 62: (4, 1.0), 67: (4, 1.7581), 68: (4, 0.0), 75: (8, 1.0), 88: (4, 1.0), 91: (2, 1.0),
               84: (4, 1.0), 85: (4, 0.0), 66: (8, 0.0), 77: (2, 1.0), 74: (4, 0.0), 89: (4, 0.0), 10: (2, 0.0),
               7: (4, 0.0), 92: (8, 0.0), 55: (4, 0.0), 63: (4, 0.0), 64: (4, 0.0), 65: (4, 0.0), 90: (8, 0.0),
-              82: (4, 0.0), 93: (4, 0.0)}
+              82: (4, 0.0), 93: (4, 0.0),
+              # 3*x*x: the reference's associative-math build groups the product differently in its
+              # single-thread and OpenMP code paths, so either grouping is two roundings away at most
+              50: (2, 0.0)}
 
 
 def ulps_at(got, want, floor):

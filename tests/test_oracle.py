@@ -43,6 +43,9 @@ def test_port_matches_golden(port, gold, name, case):
         assert (np.abs(got.astype(np.float64) - want) / np.spacing(scale)).max() <= 4
         if case["op"] in (2, 3, 5, 12, 15, 16, 17, 18, 63, 64, 65, 78, 86, 90):   # a single libm call
             assert ulp_distance(got, want).max() <= 1
+    elif fam == "transform" and case["op"] == 50:
+        # 3*x*x is grouped differently by the reference's single-thread and OpenMP code paths
+        assert ulp_distance(got, want).max() <= 2
     elif fam == "scalar" and case["op"] == 3:
         # x / scalar: the reference's reciprocal-math build multiplies by a hoisted 1/scalar
         assert ulp_distance(got, want).max() <= 1
