@@ -49,6 +49,19 @@ int nd4jb200_exec_reduce(void *stream, int dtype, int opNum, const void *x, cons
 int nd4jb200_exec_reduce_scalar(void *stream, int dtype, int opNum, const void *x,
                                 const Nd4jLong *xShapeInfo, const void *extraParams, double *result);
 
+/* Whole-array reduction that allocates nothing. It has no counterpart in the reference: the
+ * reference's CUDA build takes its reduction scratch from the caller (extraPointers[4]), this
+ * library normally allocates its own. Callers that cannot allocate on the device - code running
+ * inside a pool that owns all device memory, loops that must not trigger a device-wide
+ * synchronisation, processes without allocation rights - use this form instead: partial states
+ * live in a fixed 64 KiB device array inside the library and the result is written to `z`, a
+ * DEVICE location for one element of the call's type (asynchronous on `stream`).
+ * Arrays longer than 2^27 elements are refused with ND4JB200_ETOOLARGE. Calls on one device
+ * share the array, so calls that overlap on the GPU must be ordered by the caller. The first
+ * call on each device looks up the array's address and should precede any stream capture. */
+int nd4jb200_exec_reduce_scalar_noalloc(void *stream, int dtype, int opNum, const void *x,
+                                        const Nd4jLong *xShapeInfo, const void *extraParams, void *z);
+
 /* ---- indexreduce: NativeOps::execIndexReduce* (blas/NativeOps.h:576-602;
  *      blas/cuda/NativeOps.cu:1699-1781). Indices are written in the element type, as in the
  *      reference (include/loops/cpu/indexreduce.cpp:206,223). ---------------------------------- */
