@@ -40,8 +40,8 @@ Status fetch_scalar(cudaStream_t st, int dtype, const void *dev, void *hostSlot,
 }
 
 // Scratch large enough for the partial states of any single-TAD (whole array) reduction:
-// at most kTargetThreads segments of the largest state (32 bytes), plus the 256-byte result slot.
-constexpr size_t kScalarWorkspace = 256 + 32 * (size_t) kTargetThreads + 4096;
+// at most kTargetThreads segments of the largest state (32 bytes), plus the result slot and counter region.
+constexpr size_t kScalarWorkspace = 256 + kCounterSlots * sizeof(unsigned) + 32 * (size_t) kTargetThreads + 4096;
 
 bool same_shape(const ShapeDesc &a, const ShapeDesc &b) {
     if (a.rank != b.rank) return false;

@@ -113,6 +113,7 @@ extern "C" int nd4jb200_exec_reduce_scalar_noalloc(void *stream, int dtype, int 
     ReduceArgs a;
     a.x = x; a.y = nullptr; a.extra = extraParams; a.z = z;
     a.partials = scratch;
+    a.counters = nullptr;   // partials are merged by the separate finalize launch
     a.numTads = 1;
     a.tadLen = xd.length;
     a.xOuter = plan.outer; a.xInner = plan.inner;

@@ -7,20 +7,23 @@
 //
 //   along-TAD  (k_reduce_tads): consecutive elements of one TAD are (close to) adjacent in
 //              memory. A group of g threads (1..32 lanes of a warp, or a whole 256-thread CTA)
-//              walks one TAD segment with 128-bit loads when alignment allows.
+//              walks one TAD segment with 128-bit loads when alignment allows, 128 bytes in
+//              flight per thread.
 //   across-TAD (k_reduce_cols): consecutive TADs are adjacent in memory and a TAD's own
 //              elements are far apart (column reductions of row-major arrays, row reductions of
-//              f-order views). 32 lanes read neighbouring TADs per row (128-bit loads when the
-//              rows are 16-byte aligned); 8 row-lanes per CTA and `splits` CTAs share the rows of
-//              one TAD tile.
+//              f-order views). 32 lanes read neighbouring TADs per row (vector loads when the
+//              rows are aligned); 8 row-lanes per CTA and `splits` CTAs share the rows of one
+//              TAD tile.
 //
 // A TAD may be cut into `splits` segments handled by different groups/CTAs; each writes its
-// partial state to a scratch array and k_reduce_finalize merges the partials of a TAD in
-// an order fixed by the segment numbers. All merges (lanes, warps, segments) happen in an order
-// fixed by indices, never by arrival, so a call is bit-reproducible run to run.
+// partial state to a scratch array. The partials of a TAD are merged in an order fixed by the
+// segment numbers, either by the group that completes the TAD last (arrival counters; nobody
+// waits on anybody: a group that is not last simply leaves) or by the separate k_reduce_finalize
+// launch. All merges (lanes, warps, segments) happen in an order fixed by indices, never by
+// arrival, so a call is bit-reproducible run to run.
 //
 // Policy concept (see policies.cuh):
-//   typedef State;  static constexpr int kInputs (1|2), kParams;
+//   typedef State;  static constexpr int kInputs (1|2), kParams, kColBytes;
 //   init(State&);  accum(State&, C x, C y, LL j, const C* p);  merge(State&, const State&);
 //   accum_many<N>(State&, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C* p)
 //       folds N elements with indices j0, j0 + jstep, ... (ascending) in one go;
@@ -36,6 +39,9 @@ struct ReduceArgs {
     const void *extra;   // device extra parameters or null
     void *z;             // one result per TAD, written densely
     void *partials;      // scratch for split TADs: State[numTads * splits]
+    unsigned *counters;  // one zeroed arrival counter per TAD (along-TAD) or TAD tile (across-TAD): when set,
+                         // the group that completes a TAD last merges its partials inside the same launch
+                         // and re-zeroes the counter; when null the partials are left for k_reduce_finalize
     LL numTads;
     LL tadLen;
     View xOuter, xInner;
@@ -51,6 +57,16 @@ struct ReduceArgs {
 
 constexpr int kBlock = 256;
 
+// Partial states written by other SMs during this launch are read through L2.
+template <class S> ND_D S load_state_cg(const S *p) {
+    S r;
+    const unsigned *src = reinterpret_cast<const unsigned *>(p);
+    unsigned *dst = reinterpret_cast<unsigned *>(&r);
+#pragma unroll
+    for (int w = 0; w < (int) (sizeof(S) / 4); w++) dst[w] = __ldcg(src + w);
+    return r;
+}
+
 template <class T, class P, int N>
 ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, LL j0,
                     const typename Elem<T>::C *p) {
@@ -62,6 +78,20 @@ ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, 
         ya[k] = P::kInputs == 2 ? Elem<T>::to_c(yv.v[k]) : C(0);
     }
     P::template accum_many<N>(s, xa, ya, j0, 1, p);
+}
+
+// W consecutive elements (W * sizeof(T) is 2, 4, 8 or 16 bytes) moved as one transaction.
+template <class T, int W> struct alignas(W * sizeof(T)) Vec {
+    T v[W];
+};
+template <class T, int W> ND_D Vec<T, W> load_vec(const T *p) {
+    Vec<T, W> r;
+    constexpr int B = W * (int) sizeof(T);
+    if (B == 16) *reinterpret_cast<uint4 *>(&r) = __ldg(reinterpret_cast<const uint4 *>(p));
+    else if (B == 8) *reinterpret_cast<uint2 *>(&r) = __ldg(reinterpret_cast<const uint2 *>(p));
+    else if (B == 4) *reinterpret_cast<unsigned *>(&r) = __ldg(reinterpret_cast<const unsigned *>(p));
+    else *reinterpret_cast<unsigned short *>(&r) = __ldg(reinterpret_cast<const unsigned short *>(p));
+    return r;
 }
 
 template <class T, class P>
@@ -79,11 +109,15 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
     const int groupsPerBlock = kBlock / g;
     const int lane = threadIdx.x % g;
     const LL totalSegs = a.numTads * a.splits;
-    const LL segLen = (a.tadLen + a.splits - 1) / a.splits;
     // segments start on a vector boundary so the 128-bit path stays aligned
-    const LL segLenAligned = (segLen + V - 1) / V * V;
+    LL segLenAligned = a.tadLen;
+    if (a.splits > 1) {
+        const LL segLen = (a.tadLen + a.splits - 1) / a.splits;
+        segLenAligned = (segLen + V - 1) / V * V;
+    }
 
     __shared__ State warpStates[kBlock / 32];
+    __shared__ int lastFlag;
 
     for (LL seg = (LL) blockIdx.x * groupsPerBlock + threadIdx.x / g; ; seg += (LL) gridDim.x * groupsPerBlock) {
         // a warp- or CTA-wide group leaves as a whole (seg is uniform across it)
@@ -95,10 +129,12 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
 
         State s;
         P::init(s);
-        LL r = 0, sp = 0;
+        LL r = seg, sp = 0;
         if (active) {
-            r = seg / a.splits;
-            sp = seg - r * a.splits;
+            if (a.splits > 1) {     // the 64-bit division is only paid by split TADs
+                r = seg / a.splits;
+                sp = seg - r * a.splits;
+            }
             const LL j0 = sp * segLenAligned;
             LL j1 = j0 + segLenAligned;
             if (j1 > a.tadLen) j1 = a.tadLen;
@@ -108,8 +144,8 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
                 LL j = j0 + (LL) lane * V;
                 const LL step = (LL) g * V;
                 // U packs per operand are requested before any dependent arithmetic, so that every
-                // lane keeps 64 bytes (or 2 x 32 with two operands) in flight
-                constexpr int U = P::kInputs == 2 ? 2 : 4;
+                // lane keeps 128 bytes in flight (8 x 16 with one operand, 2 x 4 x 16 with two)
+                constexpr int U = P::kInputs == 2 ? 4 : 8;
                 for (; j + (U - 1) * step < j1; j += U * step) {
                     Pack<T> xv[U], yv[U];
 #pragma unroll
@@ -119,6 +155,13 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
                     }
 #pragma unroll
                     for (int u = 0; u < U; u++) fold_pack<T, P, V>(s, xv[u], yv[u], j + u * step, p);
+                }
+                for (; j + step < j1; j += 2 * step) {
+                    Pack<T> xa = load_pack(xb + j), xc = load_pack(xb + j + step);
+                    Pack<T> ya, yc;
+                    if (P::kInputs == 2) { ya = load_pack(yb + j); yc = load_pack(yb + j + step); }
+                    fold_pack<T, P, V>(s, xa, ya, j, p);
+                    fold_pack<T, P, V>(s, xc, yc, j + step, p);
                 }
                 for (; j < j1; j += step) {
                     Pack<T> xa = load_pack(xb + j);
@@ -155,24 +198,64 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
             }
             __syncthreads();
         }
-        if (active && lane == 0) {
-            if (a.splits == 1) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
-            else reinterpret_cast<State *>(a.partials)[seg] = s;
+        if (a.splits == 1) {
+            if (active && lane == 0) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+            continue;
         }
+        State *parts = reinterpret_cast<State *>(a.partials);
+        if (a.counters == nullptr) {
+            if (active && lane == 0) parts[seg] = s;
+            continue;
+        }
+        // publish the partial, then find out whether this group completed the TAD
+        int last = 0;
+        if (active && lane == 0) {
+            parts[seg] = s;
+            __threadfence();
+            last = atomicAdd(&a.counters[r], 1u) == (unsigned) (a.splits - 1);
+            if (last) a.counters[r] = 0u;
+        }
+        if (g == kBlock) {
+            if (threadIdx.x == 0) lastFlag = last;
+            __syncthreads();
+            last = lastFlag;
+        } else if (g > 1) {
+            last = __shfl_sync(0xffffffffu, last, (threadIdx.x & 31) / g * g);
+        }
+        State m;
+        P::init(m);
+        if (last) {
+            __threadfence();
+            for (int k = lane; k < a.splits; k += g) P::merge(m, load_state_cg(parts + r * a.splits + k));
+        }
+        if (g > 1) group_merge<P>(m, g < 32 ? g : 32);
+        if (g == kBlock) {
+            const int w = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) warpStates[w] = m;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                m = warpStates[0];
+                for (int k = 1; k < kBlock / 32; k++) P::merge(m, warpStates[k]);
+            }
+            __syncthreads();
+        }
+        if (last && lane == 0) az[r] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
     }
 }
 
 // blockDim = (32, 8). blockIdx.x enumerates (hi, tile of 32 * W consecutive TADs); blockIdx.y is
-// the row split. W = 1, or the 128-bit pack width when the TAD bases allow aligned vector loads:
-// a thread then owns W neighbouring TADs and a warp reads 512 contiguous bytes per row.
+// the row split. W = 1, or a vector width chosen by the launcher when the TAD bases allow aligned
+// vector loads: a thread then owns W neighbouring TADs and a warp reads 32 * W contiguous elements
+// per row. R rows per operand are in flight per thread.
 constexpr int kColRows = 8;
-constexpr int kColUnroll = 4;
 
-template <class T, class P, bool VEC>
+template <class P> struct ColUnroll { static constexpr int v = P::kInputs == 2 ? 4 : 8; };
+
+template <class T, class P, int W>
 __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs a) {
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
-    constexpr int W = VEC ? Elem<T>::kVec : 1;
+    constexpr int R = ColUnroll<P>::v;
     C p[P::kParams ? P::kParams : 1];
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     const T *ax = static_cast<const T *>(a.x);
@@ -194,49 +277,35 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
         const T *yb = P::kInputs == 2 ? ay + view_offset(a.yOuterHi, hi) + lo : nullptr;
         const LL step = (LL) gridDim.y * kColRows;
         LL j = (LL) blockIdx.y * kColRows + threadIdx.y;
-        for (; j + (kColUnroll - 1) * step < a.tadLen; j += kColUnroll * step) {
-            if (VEC) {
-                Pack<T> xv[kColUnroll], yv[kColUnroll];
+        for (; j + (R - 1) * step < a.tadLen; j += R * step) {
+            Vec<T, W> xv[R], yv[R];
 #pragma unroll
-                for (int u = 0; u < kColUnroll; u++) {
-                    xv[u] = load_pack(xb + (j + u * step) * a.colStrideX);
-                    if (P::kInputs == 2) yv[u] = load_pack(yb + (j + u * step) * a.colStrideY);
+            for (int u = 0; u < R; u++) {
+                xv[u] = load_vec<T, W>(xb + (j + u * step) * a.colStrideX);
+                if (P::kInputs == 2) yv[u] = load_vec<T, W>(yb + (j + u * step) * a.colStrideY);
+            }
+#pragma unroll
+            for (int w = 0; w < W; w++) {
+                C xa[R], ya[R];
+#pragma unroll
+                for (int u = 0; u < R; u++) {
+                    xa[u] = Elem<T>::to_c(xv[u].v[w]);
+                    ya[u] = P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0);
                 }
-#pragma unroll
-                for (int w = 0; w < W; w++) {
-                    C xa[kColUnroll], ya[kColUnroll];
-#pragma unroll
-                    for (int u = 0; u < kColUnroll; u++) {
-                        xa[u] = Elem<T>::to_c(xv[u].v[w]);
-                        ya[u] = P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0);
-                    }
-                    P::template accum_many<kColUnroll>(s[w], xa, ya, j, step, p);
-                }
-            } else {
-                C xa[kColUnroll], ya[kColUnroll];
-#pragma unroll
-                for (int u = 0; u < kColUnroll; u++) {
-                    xa[u] = Elem<T>::load(xb + (j + u * step) * a.colStrideX);
-                    ya[u] = P::kInputs == 2 ? Elem<T>::load(yb + (j + u * step) * a.colStrideY) : C(0);
-                }
-                P::template accum_many<kColUnroll>(s[0], xa, ya, j, step, p);
+                P::template accum_many<R>(s[w], xa, ya, j, step, p);
             }
         }
         for (; j < a.tadLen; j += step) {
-            if (VEC) {
-                Pack<T> xv = load_pack(xb + j * a.colStrideX), yv;
-                if (P::kInputs == 2) yv = load_pack(yb + j * a.colStrideY);
+            Vec<T, W> xv = load_vec<T, W>(xb + j * a.colStrideX), yv;
+            if (P::kInputs == 2) yv = load_vec<T, W>(yb + j * a.colStrideY);
 #pragma unroll
-                for (int w = 0; w < W; w++)
-                    P::accum(s[w], Elem<T>::to_c(xv.v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv.v[w]) : C(0), j, p);
-            } else {
-                C xv = Elem<T>::load(xb + j * a.colStrideX);
-                C yv = P::kInputs == 2 ? Elem<T>::load(yb + j * a.colStrideY) : C(0);
-                P::accum(s[0], xv, yv, j, p);
-            }
+            for (int w = 0; w < W; w++)
+                P::accum(s[w], Elem<T>::to_c(xv.v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv.v[w]) : C(0), j, p);
         }
     }
     __shared__ State rows[kColRows][32];
+    __shared__ int lastFlag;
+    State *parts = reinterpret_cast<State *>(a.partials);
 #pragma unroll
     for (int w = 0; w < W; w++) {
         if (w) __syncthreads();
@@ -246,7 +315,33 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
             State m = s[w];
             for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][threadIdx.x]);
             if (a.splits == 1) az[r + w] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
-            else reinterpret_cast<State *>(a.partials)[(r + w) * a.splits + blockIdx.y] = m;
+            else parts[(r + w) * a.splits + blockIdx.y] = m;
+        }
+    }
+    if (a.splits == 1 || a.counters == nullptr) return;
+    // the CTA that completes this TAD tile last merges the tile's partials (nobody waits)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+        const int last = atomicAdd(&a.counters[blockIdx.x], 1u) == (unsigned) (a.splits - 1);
+        if (last) a.counters[blockIdx.x] = 0u;
+        lastFlag = last;
+    }
+    __syncthreads();
+    if (!lastFlag) return;
+    __threadfence();
+#pragma unroll
+    for (int w = 0; w < W; w++) {
+        State m;
+        P::init(m);
+        if (active)
+            for (int k = threadIdx.y; k < a.splits; k += kColRows) P::merge(m, load_state_cg(parts + (r + w) * a.splits + k));
+        __syncthreads();
+        rows[threadIdx.y][threadIdx.x] = m;
+        __syncthreads();
+        if (threadIdx.y == 0 && active) {
+            for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][threadIdx.x]);
+            az[r + w] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
         }
     }
 }

@@ -17,6 +17,25 @@ struct ReduceCall {
     LL finishLen = 0;            // n handed to the policy's finish()
 };
 
+// Workspace layout: [256-byte result slot][kCounterSlots arrival counters][partial states]. The
+// counter region is never used for anything else; the workspace is zero-filled when it is
+// allocated and every launch re-zeroes the counters it used. Merging inside the launch pays off
+// when a TAD has few segments; with many segments per TAD only a few CTAs would do all the
+// merging, so those cases (and calls that need more counters than the region holds) leave the
+// partials to the separate, fully parallel finalize launch.
+constexpr size_t kCounterSlots = 65536;
+constexpr int kMaxInKernelMerge = 32;
+template <class State>
+Status split_scratch(cudaStream_t stream, ReduceArgs &a, size_t counters) {
+    const size_t counterBytes = kCounterSlots * sizeof(unsigned);
+    void *ws = nullptr;
+    ND_TRY(workspace(stream, 256 + counterBytes + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
+    a.counters = (a.splits <= kMaxInKernelMerge && counters <= kCounterSlots)
+                     ? reinterpret_cast<unsigned *>(static_cast<char *>(ws) + 256) : nullptr;
+    a.partials = static_cast<char *>(ws) + 256 + counterBytes;
+    return kOk;
+}
+
 // Enough resident threads to cover HBM latency on every SM.
 constexpr LL kTargetThreads = (LL) kNumSMs * 2048;
 
@@ -30,6 +49,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     ReduceArgs a;
     a.x = c.x; a.y = c.y; a.extra = c.extra; a.z = c.z;
     a.partials = nullptr;
+    a.counters = nullptr;
     a.numTads = c.xPlan.numTads;
     a.tadLen = c.xPlan.tadLen;
     a.xOuter = c.xPlan.outer; a.xInner = c.xPlan.inner;
@@ -52,7 +72,6 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         for (int d = 0; cols && d < xo.rank; d++) cols = yo.shape[d] == xo.shape[d];
     }
 
-    void *ws = nullptr;
     if (cols) {
         a.colLo = xo.shape[xo.rank - 1];
         a.colStrideX = xi.stride[0];
@@ -60,23 +79,24 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         a.xOuterHi = xo; a.xOuterHi.rank = xo.rank - 1;
         a.yOuterHi = yo; a.yOuterHi.rank = yo.rank - 1;
         const LL hiCount = a.numTads / a.colLo;
-        // 128-bit loads across neighbouring TADs need every TAD row to start on a 16-byte boundary
-        bool vec = a.colLo % V == 0 && aligned16(a.x) && a.colStrideX % V == 0 && view_strides_multiple_of(a.xOuterHi, V);
-        if (two) vec = vec && aligned16(a.y) && a.colStrideY % V == 0 && view_strides_multiple_of(a.yOuterHi, V);
-        const LL tiles = hiCount * ceil_div(a.colLo, 32 * (vec ? V : 1));
+        // vector loads across neighbouring TADs need every TAD row to start on a vector boundary
+        constexpr int W = P::kColBytes / (int) sizeof(T) > 0 ? P::kColBytes / (int) sizeof(T) : 1;
+        constexpr size_t WB = (size_t) W * sizeof(T);
+        bool vec = W > 1 && a.colLo % W == 0 && reinterpret_cast<uintptr_t>(a.x) % WB == 0 && a.colStrideX % W == 0 &&
+                   view_strides_multiple_of(a.xOuterHi, W);
+        if (two) vec = vec && reinterpret_cast<uintptr_t>(a.y) % WB == 0 && a.colStrideY % W == 0 &&
+                       view_strides_multiple_of(a.yOuterHi, W);
+        const LL tiles = hiCount * ceil_div(a.colLo, 32 * (vec ? W : 1));
         LL splits = ceil_div((LL) kNumSMs * 8, tiles);
-        const LL maxSplits = a.tadLen / (kColRows * 2 * kColUnroll);   // at least two unrolled trips per thread
+        const LL maxSplits = a.tadLen / (kColRows * 2 * ColUnroll<P>::v);   // at least two unrolled trips per thread
         if (splits > maxSplits) splits = maxSplits;
         if (splits < 1) splits = 1;
         if (splits > 4096) splits = 4096;
         a.splits = (int) splits;
-        if (a.splits > 1) {
-            ND_TRY(workspace(stream, 256 + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
-            a.partials = static_cast<char *>(ws) + 256;
-        }
+        if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) tiles));
         dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
-        if (vec) k_reduce_cols<T, P, true><<<grid, block, 0, stream>>>(a);
-        else k_reduce_cols<T, P, false><<<grid, block, 0, stream>>>(a);
+        if (vec) k_reduce_cols<T, P, W><<<grid, block, 0, stream>>>(a);
+        else k_reduce_cols<T, P, 1><<<grid, block, 0, stream>>>(a);
         count_launch();
     } else {
         if (xUnit && yUnit) {
@@ -106,10 +126,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
             if (splits < 1) splits = 1;
         }
         a.splits = (int) splits;
-        if (a.splits > 1) {
-            ND_TRY(workspace(stream, 256 + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
-            a.partials = static_cast<char *>(ws) + 256;
-        }
+        if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) a.numTads));
         const LL totalSegs = a.numTads * a.splits;
         LL blocks = ceil_div(totalSegs, kBlock / a.group);
         const LL cap = (LL) kNumSMs * 64;
@@ -117,7 +134,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         k_reduce_tads<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
         count_launch();
     }
-    if (a.splits > 1) {
+    if (a.splits > 1 && a.counters == nullptr) {
         LL blocks = ceil_div(a.numTads, kBlock / 32);   // one warp per TAD
         if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
         k_reduce_finalize<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);

@@ -43,6 +43,8 @@ Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot)
             b.dev = nullptr; b.cap = 0;
         }
         ND_CUDA(cudaMalloc(&b.dev, want));
+        // arrival counters live in this block and must start at zero
+        ND_CUDA(cudaMemset(b.dev, 0, want));
         b.cap = want;
     }
     if (hostSlot && !b.host) ND_CUDA(cudaMallocHost(&b.host, 64));
