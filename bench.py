@@ -219,7 +219,7 @@ def time_graph(torch, stream, fn, iters, replays=5):
     return start.elapsed_time(stop) / (iters * replays)
 
 
-def family_table(torch, ops, calls, stream, peak, quick, only=None):
+def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=False):
     """Achieved HBM GB/s of the other op families at their configured sizes (algorithmic bytes /
     CUDA-event time, inputs larger than L2 or L2 flushed by the rotation of buffers)."""
     from libnd4j_b200 import shape as S
@@ -228,13 +228,13 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None):
     dev = torch.device("cuda")
 
     def record(name, nbytes, elems, fn, iters=20, graph=True):
-        if only and only not in name:
+        if only and not any(part in name for part in only.split(",")):
             return
-        if only:
+        if profile:
             iters = min(iters, 3)
         for _ in range(3):
             fn()
-        ms = time_graph(torch, stream, fn, iters) if (graph and not only) else time_loop(torch, stream, fn, iters)
+        ms = time_graph(torch, stream, fn, iters) if (graph and not profile) else time_loop(torch, stream, fn, iters)
         out[name] = {"ms": round(ms, 5), "GBps": round(nbytes / ms / 1e6, 1), "frac_of_measured_peak": round(nbytes / ms / 1e6 / peak, 3),
                      "Gelem_s": round(elems / ms / 1e6, 2)}
 
@@ -347,6 +347,9 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     calls = Calls(ops, stream.cuda_stream)
     lib, st, P = calls.lib, calls.stream, calls.p
+    for kv in args.tune:
+        key, value = kv.split("=")
+        calls.check(lib.nd4jb200_set_tuning(int(key), ctypes.c_longlong(int(value))))
     peak, peak_src = measured_peaks()
 
     x, b, y = make_inputs(ROWS)
@@ -440,7 +443,7 @@ def run_ours(args):
         with torch.cuda.stream(stream):
             del dx, dy, t1, t2, dz
             torch.cuda.empty_cache()
-            families = family_table(torch, ops, calls, stream, peak, args.quick, args.only)
+            families = family_table(torch, ops, calls, stream, peak, args.quick, args.only, args.profile)
     elif world > 1:
         families = sharded_families(torch, dist, ops, calls, stream, world, rank, args.quick)
 
@@ -533,8 +536,10 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller sizes for the families table")
     ap.add_argument("--no-families", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--only", default=None, help="profiling aid: run only the families whose name contains this text, "
-                                                 "three timed launches each")
+    ap.add_argument("--only", default=None, help="run only the families whose name contains one of these comma-separated texts")
+    ap.add_argument("--profile", action="store_true", help="profiling aid: three plain timed launches per family, no graph")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a launch heuristic through nd4jb200_set_tuning (repeatable)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

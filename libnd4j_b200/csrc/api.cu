@@ -40,8 +40,10 @@ Status fetch_scalar(cudaStream_t st, int dtype, const void *dev, void *hostSlot,
 }
 
 // Scratch large enough for the partial states of any single-TAD (whole array) reduction:
-// at most kTargetThreads segments of the largest state (32 bytes), plus the result slot and counter region.
-constexpr size_t kScalarWorkspace = 256 + kCounterSlots * sizeof(unsigned) + 32 * (size_t) kTargetThreads + 4096;
+// at most kNumSMs * kMaxRowThreadsPerSm segments of the largest state (32 bytes), plus the result slot and
+// counter region.
+constexpr long long kMaxRowThreadsPerSm = 4096;
+constexpr size_t kScalarWorkspace = 256 + kCounterSlots * sizeof(unsigned) + 32 * (size_t) kNumSMs * kMaxRowThreadsPerSm + 4096;
 
 bool same_shape(const ShapeDesc &a, const ShapeDesc &b) {
     if (a.rank != b.rank) return false;
@@ -230,6 +232,15 @@ extern "C" {
 
 const char *nd4jb200_last_error(void) { return last_error(); }
 unsigned long long nd4jb200_launch_count(void) { return g_launches; }
+
+int nd4jb200_set_tuning(int key, long long value) {
+    if (key < 0 || key >= kTuneCount || value < 1 || (key == kTuneRowThreadsPerSm && value > kMaxRowThreadsPerSm)) {
+        set_error("nd4jb200_set_tuning: unknown key or value out of range");
+        return kBadArgument;
+    }
+    g_tuning[key] = value;
+    return kOk;
+}
 
 // ---------------------------------------------------------------------------------------------
 int nd4jb200_exec_reduce(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,

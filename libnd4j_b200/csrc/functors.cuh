@@ -24,6 +24,9 @@ namespace fn {
 
 template <class C> ND_D C absv(C x) { return x < C(0) ? -x : x; }
 template <> ND_D float absv<float>(float x) { return fabsf(x); }
+// a * b + c in one rounding; for accumulators whose tolerance is relative, not for elementwise results
+ND_D float fmav(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+ND_D double fmav(double a, double b, double c) { return __fma_rn(a, b, c); }
 template <class C> ND_D C maxv(C a, C b) { return a > b ? a : b; }   // nd4j_max: "a > b ? a : b"
 template <class C> ND_D C minv(C a, C b) { return a < b ? a : b; }   // nd4j_min: "a < b ? a : b"
 template <class C> ND_D C sgn(C x) { return x < C(0) ? C(-1) : (x > C(0) ? C(1) : C(0)); }

@@ -63,9 +63,9 @@ template <int kind, class C> struct Reduce3 {
     ND_D static void init(State &s) { s.acc = C(0); s.e0 = C(0); s.e1 = C(0); }
     ND_D static void accum(State &s, C x, C y, LL, const C *p) {
         if (kind == 0) s.acc += absv(x - y);
-        else if (kind == 1) { C d = x - y; s.acc += d * d; }
-        else if (kind == 2 || kind == 5) { s.acc += x * y; s.e0 += x * x; s.e1 += y * y; }
-        else if (kind == 3) s.acc += x * y;
+        else if (kind == 1) { C d = x - y; s.acc = fmav(d, d, s.acc); }
+        else if (kind == 2 || kind == 5) { s.acc = fmav(x, y, s.acc); s.e0 = fmav(x, x, s.e0); s.e1 = fmav(y, y, s.e1); }
+        else if (kind == 3) s.acc = fmav(x, y, s.acc);
         else if (kind == 4) {
             C eps = p[0];
             C diff = absv(x - y);
@@ -108,10 +108,12 @@ template <int kind, class C> struct IndexExtreme {
         if (kind == 0 || kind == 2) return a > b || (a == b && ia < ib);
         return a < b || (a == b && ia < ib);
     }
-    ND_D static void accum(State &s, C x, C, LL j, const C *) {
-        C v = (kind >= 2) ? absv(x) : x;
-        if (better(v, j, s.v, s.i)) { s.v = v; s.i = j; }
+    ND_D static void take(State &s, C v, LL j) {     // selects, not branches: lanes rarely agree
+        const bool b = better(v, j, s.v, s.i);
+        s.v = b ? v : s.v;
+        s.i = b ? j : s.i;
     }
+    ND_D static void accum(State &s, C x, C, LL j, const C *) { take(s, (kind >= 2) ? absv(x) : x, j); }
     // a run of ascending indices needs no tie-break: the first strictly better element wins, and
     // only the winner of the run is compared (with the index tie-break) against the state
     template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
@@ -124,10 +126,24 @@ template <int kind, class C> struct IndexExtreme {
             best = b ? v : best;
             at = b ? i : at;
         }
-        LL j = j0 + at * jstep;
-        if (better(best, j, s.v, s.i)) { s.v = best; s.i = j; }
+        take(s, best, j0 + at * jstep);
     }
-    ND_D static void merge(State &s, const State &o) { if (better(o.v, o.i, s.v, s.i)) { s.v = o.v; s.i = o.i; } }
+    // U packs of V consecutive elements, pack u starting at index j0 + u * ustep (ascending):
+    // one index computation and one tie-break for the whole tile
+    static constexpr bool kTile = true;
+    template <int U, int V> ND_D static void accum_tile(State &s, const C (&x)[U * V], LL j0, int ustep, const C *) {
+        C best = (kind >= 2) ? absv(x[0]) : x[0];
+        int at = 0;
+#pragma unroll
+        for (int i = 1; i < U * V; i++) {
+            C v = (kind >= 2) ? absv(x[i]) : x[i];
+            bool b = (kind == 0 || kind == 2) ? v > best : v < best;
+            best = b ? v : best;
+            at = b ? i : at;
+        }
+        take(s, best, j0 + ((at / V) * ustep + (at % V)));
+    }
+    ND_D static void merge(State &s, const State &o) { take(s, o.v, o.i); }
     ND_D static C finish(const State &s, LL, const C *) { return C(s.i); }
 };
 
@@ -176,14 +192,14 @@ template <int kind, class C> struct Stats {
         s.n += 1.0; s.s1 += d; s.s2 += d * d;
     }
     // N elements at once: their offsets from the pivot are summed in the element's own compute
-    // type first (N is at most 8, so this adds a few units in the last place of a short sum) and
+    // type first (N is at most 16, so this adds a few units in the last place of a short sum) and
     // only the two short sums enter the double accumulators
     template <int N> ND_D static void accum_many(State &s, const C (&x)[N], const C (&y)[N], LL j0, LL jstep, const C *p) {
         if (s.n == 0) s.k = (double) x[0];
         const C k = (C) s.k;
         C a = C(0), b = C(0);
 #pragma unroll
-        for (int i = 0; i < N; i++) { C d = x[i] - k; a += d; b += d * d; }
+        for (int i = 0; i < N; i++) { C d = x[i] - k; a += d; b = fmav(d, d, b); }
         s.n += (double) N; s.s1 += (double) a; s.s2 += (double) b;
     }
     ND_D static void merge(State &s, const State &o) {

@@ -48,6 +48,8 @@ struct ReduceArgs {
     View yOuter, yInner;
     int group;           // threads cooperating on one TAD segment (along-TAD kernel)
     int splits;          // segments per TAD
+    LL partTadStride;    // partial state of (TAD r, segment k) lives at partials[r * partTadStride + k * partSplitStride]
+    LL partSplitStride;
     int mode;            // along-TAD: 0 = unit-stride inner + 128-bit loads, 1 = rank-1 inner, 2 = general inner view
     LL colLo;            // across-TAD: extent of the contiguous outer axis
     LL colStrideX, colStrideY;   // across-TAD: element stride between consecutive elements of a TAD
@@ -79,6 +81,10 @@ ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, 
     }
     P::template accum_many<N>(s, xa, ya, j0, 1, p);
 }
+
+// Policies that can fold a whole tile of packs at once declare kTile (see pol::IndexExtreme).
+template <class P, class = void> struct HasTile { static constexpr bool value = false; };
+template <class P> struct HasTile<P, decltype((void) P::kTile)> { static constexpr bool value = true; };
 
 // W consecutive elements (W * sizeof(T) is 2, 4, 8 or 16 bytes) moved as one transaction.
 template <class T, int W> struct alignas(W * sizeof(T)) Vec {
@@ -153,21 +159,31 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
                         xv[u] = load_pack(xb + j + u * step);
                         if (P::kInputs == 2) yv[u] = load_pack(yb + j + u * step);
                     }
+                    if constexpr (HasTile<P>::value) {
+                        C xa[U * V];
 #pragma unroll
-                    for (int u = 0; u < U; u++) fold_pack<T, P, V>(s, xv[u], yv[u], j + u * step, p);
+                        for (int u = 0; u < U; u++)
+#pragma unroll
+                            for (int k = 0; k < V; k++) xa[u * V + k] = Elem<T>::to_c(xv[u].v[k]);
+                        P::template accum_tile<U, V>(s, xa, j, (int) step, p);
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < U; u++) fold_pack<T, P, V>(s, xv[u], yv[u], j + u * step, p);
+                    }
                 }
-                for (; j + step < j1; j += 2 * step) {
-                    Pack<T> xa = load_pack(xb + j), xc = load_pack(xb + j + step);
-                    Pack<T> ya, yc;
-                    if (P::kInputs == 2) { ya = load_pack(yb + j); yc = load_pack(yb + j + step); }
-                    fold_pack<T, P, V>(s, xa, ya, j, p);
-                    fold_pack<T, P, V>(s, xc, yc, j + step, p);
-                }
-                for (; j < j1; j += step) {
-                    Pack<T> xa = load_pack(xb + j);
-                    Pack<T> ya;
-                    if (P::kInputs == 2) ya = load_pack(yb + j);
-                    fold_pack<T, P, V>(s, xa, ya, j, p);
+                if (j < j1) {
+                    // last, partial trip of the segment: the loads are still issued together; packs
+                    // beyond the segment re-read the trip's first pack and are not folded
+                    Pack<T> xv[U], yv[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const LL ju = j + u * step < j1 ? j + u * step : j;
+                        xv[u] = load_pack(xb + ju);
+                        if (P::kInputs == 2) yv[u] = load_pack(yb + ju);
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (j + u * step < j1) fold_pack<T, P, V>(s, xv[u], yv[u], j + u * step, p);
                 }
             } else if (a.mode == 1) {
                 const LL sx = a.xInner.rank ? a.xInner.stride[0] : 0;
@@ -226,7 +242,7 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
         P::init(m);
         if (last) {
             __threadfence();
-            for (int k = lane; k < a.splits; k += g) P::merge(m, load_state_cg(parts + r * a.splits + k));
+            for (int k = lane; k < a.splits; k += g) P::merge(m, load_state_cg(parts + r * a.partTadStride + k));
         }
         if (g > 1) group_merge<P>(m, g < 32 ? g : 32);
         if (g == kBlock) {
@@ -249,13 +265,18 @@ __global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
 // per row. R rows per operand are in flight per thread.
 constexpr int kColRows = 8;
 
-template <class P> struct ColUnroll { static constexpr int v = P::kInputs == 2 ? 4 : 8; };
+// rows in flight per thread: 128 bytes over all operands, at most 8 rows
+template <class T, class P> struct ColUnroll {
+    static constexpr int kLane = P::kColBytes < (int) sizeof(T) ? (int) sizeof(T) : P::kColBytes;
+    static constexpr int kFull = 128 / (kLane * P::kInputs);
+    static constexpr int v = kFull > 8 ? 8 : kFull;
+};
 
 template <class T, class P, int W>
-__global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs a) {
+__global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceArgs a) {
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
-    constexpr int R = ColUnroll<P>::v;
+    constexpr int R = ColUnroll<T, P>::v;
     C p[P::kParams ? P::kParams : 1];
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     const T *ax = static_cast<const T *>(a.x);
@@ -295,34 +316,54 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
                 P::template accum_many<R>(s[w], xa, ya, j, step, p);
             }
         }
-        for (; j < a.tadLen; j += step) {
-            Vec<T, W> xv = load_vec<T, W>(xb + j * a.colStrideX), yv;
-            if (P::kInputs == 2) yv = load_vec<T, W>(yb + j * a.colStrideY);
+        if (j < a.tadLen) {
+            // last, partial trip: the loads are still issued together; rows beyond the TAD re-read
+            // the trip's first row and are not folded
+            Vec<T, W> xv[R], yv[R];
 #pragma unroll
-            for (int w = 0; w < W; w++)
-                P::accum(s[w], Elem<T>::to_c(xv.v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv.v[w]) : C(0), j, p);
+            for (int u = 0; u < R; u++) {
+                const LL ju = j + u * step < a.tadLen ? j + u * step : j;
+                xv[u] = load_vec<T, W>(xb + ju * a.colStrideX);
+                if (P::kInputs == 2) yv[u] = load_vec<T, W>(yb + ju * a.colStrideY);
+            }
+#pragma unroll
+            for (int u = 0; u < R; u++) {
+                if (j + u * step < a.tadLen) {
+#pragma unroll
+                    for (int w = 0; w < W; w++)
+                        P::accum(s[w], Elem<T>::to_c(xv[u].v[w]), P::kInputs == 2 ? Elem<T>::to_c(yv[u].v[w]) : C(0),
+                                 j + u * step, p);
+                }
+            }
         }
     }
-    __shared__ State rows[kColRows][32];
+    // The CTA's 8 row-lanes are merged through shared memory in one round: thread t of the CTA
+    // then owns TAD t of the tile (32 * W TADs), so partial states and results are written with
+    // consecutive threads on consecutive TADs. Partials of the across-TAD kernel are laid out
+    // [split][TAD] for that reason (a.partTadStride == 1).
+    constexpr int kTile = 32 * W;
+    __shared__ State rows[kColRows][kTile];
     __shared__ int lastFlag;
     State *parts = reinterpret_cast<State *>(a.partials);
 #pragma unroll
-    for (int w = 0; w < W; w++) {
-        if (w) __syncthreads();
-        rows[threadIdx.y][threadIdx.x] = s[w];
-        __syncthreads();
-        if (threadIdx.y == 0 && active) {
-            State m = s[w];
-            for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][threadIdx.x]);
-            if (a.splits == 1) az[r + w] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
-            else parts[(r + w) * a.splits + blockIdx.y] = m;
-        }
+    for (int w = 0; w < W; w++) rows[threadIdx.y][threadIdx.x * W + w] = s[w];
+    __syncthreads();
+    const int t = threadIdx.y * 32 + threadIdx.x;
+    const LL tlo = tile * kTile + t;
+    const bool owner = t < kTile && tlo < a.colLo;
+    const LL tr = hi * a.colLo + tlo;
+    if (owner) {
+        State m = rows[0][t];
+#pragma unroll
+        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
+        if (a.splits == 1) az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        else parts[(LL) blockIdx.y * a.partSplitStride + tr] = m;
     }
     if (a.splits == 1 || a.counters == nullptr) return;
     // the CTA that completes this TAD tile last merges the tile's partials (nobody waits)
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0 && threadIdx.y == 0) {
+    if (t == 0) {
         const int last = atomicAdd(&a.counters[blockIdx.x], 1u) == (unsigned) (a.splits - 1);
         if (last) a.counters[blockIdx.x] = 0u;
         lastFlag = last;
@@ -330,24 +371,40 @@ __global__ void __launch_bounds__(32 * kColRows) k_reduce_cols(const ReduceArgs 
     __syncthreads();
     if (!lastFlag) return;
     __threadfence();
-#pragma unroll
-    for (int w = 0; w < W; w++) {
+    // row-lane y folds segments y, y + 8, ... (ascending) of every TAD of the tile, then the
+    // owners fold the 8 row-lane results in ascending order
+    for (int c = threadIdx.x; c < kTile; c += 32) {
         State m;
         P::init(m);
-        if (active)
-            for (int k = threadIdx.y; k < a.splits; k += kColRows) P::merge(m, load_state_cg(parts + (r + w) * a.splits + k));
-        __syncthreads();
-        rows[threadIdx.y][threadIdx.x] = m;
-        __syncthreads();
-        if (threadIdx.y == 0 && active) {
-            for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][threadIdx.x]);
-            az[r + w] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        const LL clo = tile * kTile + c;
+        if (clo < a.colLo) {
+            const State *src = parts + hi * a.colLo + clo;
+            int k = threadIdx.y;
+            for (; k + 3 * kColRows < a.splits; k += 4 * kColRows) {
+                State q0 = load_state_cg(src + (LL) k * a.partSplitStride);
+                State q1 = load_state_cg(src + (LL) (k + kColRows) * a.partSplitStride);
+                State q2 = load_state_cg(src + (LL) (k + 2 * kColRows) * a.partSplitStride);
+                State q3 = load_state_cg(src + (LL) (k + 3 * kColRows) * a.partSplitStride);
+                P::merge(m, q0); P::merge(m, q1); P::merge(m, q2); P::merge(m, q3);
+            }
+            for (; k < a.splits; k += kColRows) P::merge(m, load_state_cg(src + (LL) k * a.partSplitStride));
         }
+        rows[threadIdx.y][c] = m;
+    }
+    __syncthreads();
+    if (owner) {
+        State m = rows[0][t];
+#pragma unroll
+        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
+        az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
     }
 }
 
-// One warp per TAD: lane l folds the partial states l, l + 32, ... of that TAD in ascending
-// order (coalesced reads), then the 32 lane results are merged by the fixed butterfly.
+// Separate merge pass for calls whose partials were not merged inside the reduction launch.
+// Layout [TAD][segment] (partSplitStride == 1): one warp per TAD, lane l folds segments l, l + 32,
+// ... in ascending order, then the 32 lane results are merged by the fixed butterfly.
+// Layout [segment][TAD] (partTadStride == 1): one thread per TAD folds its segments in ascending
+// order, four loads in flight. Both read the scratch coalesced.
 template <class T, class P>
 __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) {
     typedef typename Elem<T>::C C;
@@ -356,12 +413,28 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     T *az = static_cast<T *>(a.z);
     const State *parts = reinterpret_cast<const State *>(a.partials);
+    if (a.partSplitStride != 1) {
+        for (LL r = (LL) blockIdx.x * kBlock + threadIdx.x; r < a.numTads; r += (LL) gridDim.x * kBlock) {
+            State s;
+            P::init(s);
+            const State *src = parts + r * a.partTadStride;
+            int k = 0;
+            for (; k + 3 < a.splits; k += 4) {
+                State q0 = src[(LL) k * a.partSplitStride], q1 = src[(LL) (k + 1) * a.partSplitStride];
+                State q2 = src[(LL) (k + 2) * a.partSplitStride], q3 = src[(LL) (k + 3) * a.partSplitStride];
+                P::merge(s, q0); P::merge(s, q1); P::merge(s, q2); P::merge(s, q3);
+            }
+            for (; k < a.splits; k++) P::merge(s, src[(LL) k * a.partSplitStride]);
+            az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+        }
+        return;
+    }
     const int lane = threadIdx.x & 31;
     const LL warpsTotal = (LL) gridDim.x * (kBlock / 32);
     for (LL r = (LL) blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); r < a.numTads; r += warpsTotal) {
         State s;
         P::init(s);
-        for (int k = lane; k < a.splits; k += 32) P::merge(s, parts[r * a.splits + k]);
+        for (int k = lane; k < a.splits; k += 32) P::merge(s, parts[r * a.partTadStride + k]);
         group_merge<P>(s, 32);
         if (lane == 0) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
     }

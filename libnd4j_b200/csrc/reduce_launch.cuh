@@ -24,25 +24,24 @@ struct ReduceCall {
 // merging, so those cases (and calls that need more counters than the region holds) leave the
 // partials to the separate, fully parallel finalize launch.
 constexpr size_t kCounterSlots = 65536;
-constexpr int kMaxInKernelMerge = 32;
 template <class State>
 Status split_scratch(cudaStream_t stream, ReduceArgs &a, size_t counters) {
     const size_t counterBytes = kCounterSlots * sizeof(unsigned);
     void *ws = nullptr;
     ND_TRY(workspace(stream, 256 + counterBytes + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
-    a.counters = (a.splits <= kMaxInKernelMerge && counters <= kCounterSlots)
+    a.counters = (a.splits <= g_tuning[kTuneMaxInKernelMerge] && counters <= kCounterSlots)
                      ? reinterpret_cast<unsigned *>(static_cast<char *>(ws) + 256) : nullptr;
     a.partials = static_cast<char *>(ws) + 256 + counterBytes;
     return kOk;
 }
 
-// Enough resident threads to cover HBM latency on every SM.
-constexpr LL kTargetThreads = (LL) kNumSMs * 2048;
 
 template <class T, class P>
 Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     typedef typename P::State State;
     constexpr int V = Elem<T>::kVec;
+    // enough resident threads to cover HBM latency on every SM
+    const LL kTargetThreads = (LL) kNumSMs * g_tuning[kTuneRowThreadsPerSm];
     const bool two = P::kInputs == 2;
     if (c.xPlan.numTads <= 0 || c.xPlan.tadLen < 0) return kOk;
 
@@ -57,6 +56,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     a.yInner = two ? c.yPlan.inner : c.xPlan.inner;
     a.finishLen = c.finishLen;
     a.splits = 1; a.group = 32; a.mode = 2;
+    a.partTadStride = 1; a.partSplitStride = 1;
     a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;
     a.xOuterHi = a.xOuter; a.yOuterHi = a.yOuter;
 
@@ -87,12 +87,13 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         if (two) vec = vec && reinterpret_cast<uintptr_t>(a.y) % WB == 0 && a.colStrideY % W == 0 &&
                        view_strides_multiple_of(a.yOuterHi, W);
         const LL tiles = hiCount * ceil_div(a.colLo, 32 * (vec ? W : 1));
-        LL splits = ceil_div((LL) kNumSMs * 8, tiles);
-        const LL maxSplits = a.tadLen / (kColRows * 2 * ColUnroll<P>::v);   // at least two unrolled trips per thread
+        LL splits = ceil_div((LL) kNumSMs * g_tuning[kTuneColCtasPerSm], tiles);
+        const LL maxSplits = a.tadLen / (kColRows * 2 * ColUnroll<T, P>::v);   // at least two unrolled trips per thread
         if (splits > maxSplits) splits = maxSplits;
         if (splits < 1) splits = 1;
         if (splits > 4096) splits = 4096;
         a.splits = (int) splits;
+        a.partTadStride = 1; a.partSplitStride = a.numTads;
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) tiles));
         dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
         if (vec) k_reduce_cols<T, P, W><<<grid, block, 0, stream>>>(a);
@@ -126,6 +127,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
             if (splits < 1) splits = 1;
         }
         a.splits = (int) splits;
+        a.partTadStride = a.splits; a.partSplitStride = 1;
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) a.numTads));
         const LL totalSegs = a.numTads * a.splits;
         LL blocks = ceil_div(totalSegs, kBlock / a.group);
@@ -135,7 +137,8 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         count_launch();
     }
     if (a.splits > 1 && a.counters == nullptr) {
-        LL blocks = ceil_div(a.numTads, kBlock / 32);   // one warp per TAD
+        LL blocks = a.partSplitStride == 1 ? ceil_div(a.numTads, kBlock / 32)    // one warp per TAD
+                                           : ceil_div(a.numTads, kBlock);         // one thread per TAD
         if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
         k_reduce_finalize<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
         count_launch();

@@ -31,6 +31,10 @@ void release_workspaces();
 extern unsigned long long g_launches;
 inline void count_launch(int n = 1) { g_launches += n; }
 
+// Launch heuristics that may be overridden at run time (nd4jb200_set_tuning); defaults in runtime.cu.
+enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneCount = 3 };
+extern long long g_tuning[kTuneCount];
+
 Status bad_arg(const std::string &msg);
 Status unsupported(const std::string &msg);
 Status unknown_op(const char *family, int opNum);

@@ -73,6 +73,7 @@ def load_library(path=None):
     sig = {
         "nd4jb200_last_error": (ctypes.c_char_p, []),
         "nd4jb200_launch_count": (ctypes.c_ulonglong, []),
+        "nd4jb200_set_tuning": (ctypes.c_int, [ctypes.c_int, ctypes.c_longlong]),
         "nd4jb200_exec_reduce": (i, [vp, i, i, vp, llp, vp, vp, llp, ip, i]),
         "nd4jb200_exec_reduce_scalar": (i, [vp, i, i, vp, llp, vp, dp]),
         "nd4jb200_exec_index_reduce": (i, [vp, i, i, vp, llp, vp, vp, llp, ip, i]),
