@@ -42,7 +42,9 @@ unsigned long long nd4jb200_launch_count(void);
 /* Launch heuristics (no counterpart in the reference). key 0: CTAs per SM the across-TAD reduction
  * kernel aims for when it cuts TADs into segments (default 3); key 1: resident threads per SM the
  * along-TAD reduction kernel aims for (default 1024); key 2: most segments per TAD that are still
- * merged inside the reduction launch instead of by a separate pass (default 32). Results do not
+ * merged inside the reduction launch instead of by a separate pass (default 32); key 3: 1 (default)
+ * launches kernels with programmatic stream serialisation so that a kernel's launch overlaps the
+ * tail of the previous kernel on the stream, 0 launches them plainly. Results do not
  * depend on these values beyond the summation order of floating-point reductions. */
 int nd4jb200_set_tuning(int key, long long value);
 

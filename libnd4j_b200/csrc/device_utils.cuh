@@ -70,6 +70,14 @@ template <class S> ND_D S shfl_xor_state(const S &s, int mask) {
     return r;
 }
 
+// First statement of every kernel: allow the stream's next kernel to be scheduled early, then wait
+// until the previous kernel has completed and its memory operations are visible. Both are no-ops
+// for a kernel launched without programmatic stream serialisation.
+ND_D void grid_dependency_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // Butterfly merge across `width` adjacent lanes (width a power of two <= 32). Every lane of the
 // group ends with the same merged state; the merge order is fixed by the lane ids, so results
 // do not depend on scheduling.

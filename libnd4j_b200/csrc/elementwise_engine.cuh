@@ -38,6 +38,7 @@ template <class Op, int ARITY, class C> ND_D C ew_apply(C x, C y, C sc, const C 
 }
 template <class T, class Op, int ARITY>
 __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     constexpr int V = Elem<T>::kVec;
     const T *ax = static_cast<const T *>(a.x);
@@ -104,8 +105,7 @@ Status run_elementwise(EwArgs a, cudaStream_t stream) {
     const LL cap = (LL) kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    k_elementwise<T, Op, ARITY><<<(unsigned) blocks, kEwBlock, 0, stream>>>(a);
-    count_launch();
+    launch_kernel(k_elementwise<T, Op, ARITY>, dim3((unsigned) blocks), dim3(kEwBlock), stream, a);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
@@ -125,6 +125,7 @@ struct BcArgs {
 // PER_TAD false: z_tad[f] = f(x_tad[f], y[f]);  true: z_tad[f] = f(x_tad[f], y[r], p)
 template <class T, class Op, bool PER_TAD>
 __global__ void __launch_bounds__(kEwBlock) k_broadcast(const BcArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     constexpr int V = Elem<T>::kVec;
     const T *ax = static_cast<const T *>(a.x);
@@ -190,14 +191,13 @@ Status run_broadcast(BcArgs a, cudaStream_t stream) {
         a.rowsPerBlock = ceil_div(a.numTads, rowChunks);
         rowChunks = ceil_div(a.numTads, a.rowsPerBlock);
         dim3 grid((unsigned) colBlocks, (unsigned) rowChunks);
-        k_broadcast<T, Op, PER_TAD><<<grid, kEwBlock, 0, stream>>>(a);
+        launch_kernel(k_broadcast<T, Op, PER_TAD>, grid, dim3(kEwBlock), stream, a);
     } else {
         LL blocks = ceil_div(a.numTads * a.tadLen, kEwBlock);
         const LL cap = (LL) kNumSMs * 16;
         if (blocks > cap) blocks = cap;
-        k_broadcast<T, Op, PER_TAD><<<(unsigned) blocks, kEwBlock, 0, stream>>>(a);
+        launch_kernel(k_broadcast<T, Op, PER_TAD>, dim3((unsigned) blocks), dim3(kEwBlock), stream, a);
     }
-    count_launch();
     ND_CUDA(cudaGetLastError());
     return kOk;
 }

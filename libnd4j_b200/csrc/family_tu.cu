@@ -134,8 +134,7 @@ static Status launch_random(RngArgs a, cudaStream_t st) {
         const LL cap = (LL) kNumSMs * 32;
         if (blocks > cap) blocks = cap;
     }
-    k_random<ND_T, OP, ARITY><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
-    count_launch();
+    launch_kernel(k_random<ND_T, OP, ARITY>, dim3((unsigned) blocks), dim3(kRngBlock), st, a);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
@@ -144,8 +143,7 @@ static Status launch_gaussian(RngArgs a, cudaStream_t st) {
     if (a.count <= 0) return kOk;
     LL blocks;
     plan_chunks(a.count, 2 * (LL) kRngBlock, &a.chunk, &blocks);
-    k_random_gaussian<ND_T, LOGNORMAL><<<(unsigned) blocks, kRngBlock, 0, st>>>(a);
-    count_launch();
+    launch_kernel(k_random_gaussian<ND_T, LOGNORMAL>, dim3((unsigned) blocks), dim3(kRngBlock), st, a);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }

@@ -64,12 +64,10 @@ template <class T, class P>
 Status launch(ReduceArgs a, cudaStream_t stream) {
     static_assert(sizeof(typename P::State) <= kStateBytes, "state does not fit a scratch slot");
     if (a.splits == 1) {
-        k_reduce_tads<T, P><<<1, kBlock, 0, stream>>>(a);
-        count_launch();
+        launch_kernel(k_reduce_tads<T, P>, dim3(1), dim3(kBlock), stream, a);
     } else {
-        k_reduce_tads<T, P><<<(unsigned) a.splits, kBlock, 0, stream>>>(a);
-        k_reduce_finalize<T, P><<<1, kBlock, 0, stream>>>(a);
-        count_launch(2);
+        launch_kernel(k_reduce_tads<T, P>, dim3((unsigned) a.splits), dim3(kBlock), stream, a);
+        launch_kernel(k_reduce_finalize<T, P>, dim3(1), dim3(kBlock), stream, a);
     }
     ND_CUDA(cudaGetLastError());
     return kOk;

@@ -60,6 +60,8 @@ template <int kind, class C> struct Reduce3 {
     static constexpr int kInputs = 2;
     static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = kind == 4 ? 1 : 0;   // EqualsWithEps: p[0] = eps
+    // the cosine kinds convert and multiply 16 half values per pack pair: 80 registers instead of 64
+    static constexpr int kHalfRowCtas = (kind == 2 || kind == 5 || kind == 6) ? 3 : 4;
     ND_D static void init(State &s) { s.acc = C(0); s.e0 = C(0); s.e1 = C(0); }
     ND_D static void accum(State &s, C x, C y, LL, const C *p) {
         if (kind == 0) s.acc += absv(x - y);

@@ -86,6 +86,11 @@ ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, 
 template <class P, class = void> struct HasTile { static constexpr bool value = false; };
 template <class P> struct HasTile<P, decltype((void) P::kTile)> { static constexpr bool value = true; };
 
+// CTAs per SM the along-TAD kernel is compiled for. A budget of 64 registers lets the compiler keep
+// all loads of a trip in flight; a policy may name another budget for half precision (kHalfRowCtas).
+template <class T, class P, class = void> struct RowBudget { static constexpr int v = 4; };
+template <class P> struct RowBudget<__half, P, decltype((void) P::kHalfRowCtas)> { static constexpr int v = P::kHalfRowCtas; };
+
 // W consecutive elements (W * sizeof(T) is 2, 4, 8 or 16 bytes) moved as one transaction.
 template <class T, int W> struct alignas(W * sizeof(T)) Vec {
     T v[W];
@@ -101,7 +106,8 @@ template <class T, int W> ND_D Vec<T, W> load_vec(const T *p) {
 }
 
 template <class T, class P>
-__global__ void __launch_bounds__(kBlock) k_reduce_tads(const ReduceArgs a) {
+__global__ void __launch_bounds__(kBlock, RowBudget<T, P>::v) k_reduce_tads(const ReduceArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
     constexpr int V = Elem<T>::kVec;
@@ -274,6 +280,7 @@ template <class T, class P> struct ColUnroll {
 
 template <class T, class P, int W>
 __global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
     constexpr int R = ColUnroll<T, P>::v;
@@ -407,6 +414,7 @@ __global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceAr
 // order, four loads in flight. Both read the scratch coalesced.
 template <class T, class P>
 __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     typedef typename P::State State;
     C p[P::kParams ? P::kParams : 1];

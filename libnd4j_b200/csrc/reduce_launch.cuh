@@ -96,9 +96,8 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         a.partTadStride = 1; a.partSplitStride = a.numTads;
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) tiles));
         dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
-        if (vec) k_reduce_cols<T, P, W><<<grid, block, 0, stream>>>(a);
-        else k_reduce_cols<T, P, 1><<<grid, block, 0, stream>>>(a);
-        count_launch();
+        if (vec) launch_kernel(k_reduce_cols<T, P, W>, grid, block, stream, a);
+        else launch_kernel(k_reduce_cols<T, P, 1>, grid, block, stream, a);
     } else {
         if (xUnit && yUnit) {
             bool vec = a.tadLen % V == 0 && aligned16(a.x) && view_strides_multiple_of(xo, V);
@@ -133,15 +132,13 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         LL blocks = ceil_div(totalSegs, kBlock / a.group);
         const LL cap = (LL) kNumSMs * 64;
         if (blocks > cap) blocks = cap;
-        k_reduce_tads<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
-        count_launch();
+        launch_kernel(k_reduce_tads<T, P>, dim3((unsigned) blocks), dim3(kBlock), stream, a);
     }
     if (a.splits > 1 && a.counters == nullptr) {
         LL blocks = a.partSplitStride == 1 ? ceil_div(a.numTads, kBlock / 32)    // one warp per TAD
                                            : ceil_div(a.numTads, kBlock);         // one thread per TAD
         if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
-        k_reduce_finalize<T, P><<<(unsigned) blocks, kBlock, 0, stream>>>(a);
-        count_launch();
+        launch_kernel(k_reduce_finalize<T, P>, dim3((unsigned) blocks), dim3(kBlock), stream, a);
     }
     ND_CUDA(cudaGetLastError());
     return kOk;

@@ -222,6 +222,7 @@ constexpr int kRngBlock = 256;
 
 template <class T, int OP, int ARITY>
 __global__ void __launch_bounds__(kRngBlock) k_random(const RngArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     constexpr int V = Elem<T>::kVec;
     constexpr bool kDraw = RngNeedsDraw<OP, ARITY>::v;
@@ -289,6 +290,7 @@ __global__ void __launch_bounds__(kRngBlock) k_random(const RngArgs a) {
 // CTA b owns the pairs of indices [b * chunk, (b + 1) * chunk) (chunk is even).
 template <class T, bool LOGNORMAL>
 __global__ void __launch_bounds__(kRngBlock) k_random_gaussian(const RngArgs a) {
+    grid_dependency_sync();
     typedef typename Elem<T>::C C;
     const T *ay = static_cast<const T *>(a.y);
     T *az = static_cast<T *>(a.z);

@@ -32,8 +32,29 @@ extern unsigned long long g_launches;
 inline void count_launch(int n = 1) { g_launches += n; }
 
 // Launch heuristics that may be overridden at run time (nd4jb200_set_tuning); defaults in runtime.cu.
-enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneCount = 3 };
+enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneCount = 4 };
 extern long long g_tuning[kTuneCount];
+
+// Every kernel of the library starts with grid_dependency_sync() (device_utils.cuh): it lets the
+// next kernel of the stream be scheduled while this one drains and then waits for the previous
+// kernel's memory operations. Launching with programmatic stream serialisation turns that on, so
+// that launch latency and the kernel prologue overlap the predecessor's tail; ordering of all
+// global memory accesses between consecutive kernels stays that of a plain stream.
+template <class... KArgs, class... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_tuning[kTuneOverlapLaunch] ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
+    count_launch();
+}
 
 Status bad_arg(const std::string &msg);
 Status unsupported(const std::string &msg);
