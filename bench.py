@@ -51,29 +51,44 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index = index
-        self.lines = []
+        self.lines = []          # (arrival time, csv line)
         self.proc = None
+        self.window = [None, None]
 
     def start(self):
+        """Starts nvidia-smi and waits (up to 3 s) for its first sample, so that the sampler is
+        already running when the timed region begins."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
+            t0 = time.monotonic()
+            while not self.lines and time.monotonic() - t0 < 3.0:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
+
+    def mark_begin(self):
+        self.window[0] = time.monotonic()
+
+    def mark_end(self):
+        self.window[1] = time.monotonic()
 
     def stop(self):
+        """Summary over the samples taken while the GPU ran this benchmark's kernels (warm-up, the
+        timed region and the per-kernel timings); `samples_in_timed_region` counts those that fell
+        between mark_begin() and mark_end()."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.05)
         self.proc.terminate()
-        sm, mx, reasons = [], [], set()
-        for line in self.lines:
+        sm, mx, reasons, inside = [], [], set(), 0
+        for when, line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -82,11 +97,13 @@ class ClockSampler:
                 mx.append(float(parts[2]))
             except ValueError:
                 continue
+            if self.window[0] is not None and self.window[1] is not None and self.window[0] <= when <= self.window[1]:
+                inside += 1
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_in_timed_region": inside}
 
 
 def make_inputs(rows):
@@ -380,11 +397,12 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark_begin()
     launches0 = ops.launchCount()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)
@@ -392,9 +410,9 @@ def run_ours(args):
         step()
     stop.record(stream)
     barrier()
+    sampler.mark_end()
     launches = ops.launchCount() - launches0
     ms_step = start.elapsed_time(stop) / args.steps
-    clocks = sampler.stop()
     if dist is not None:
         t = torch.tensor([ms_step], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -407,6 +425,7 @@ def run_ours(args):
         for _ in range(3):
             fn()
         per[name] = time_graph(torch, stream, fn, 20)
+    clocks = sampler.stop()
     dom = max(per, key=lambda n: per[n])
     achieved = BYTES[dom] / per[dom] / 1e6
     roofline = {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

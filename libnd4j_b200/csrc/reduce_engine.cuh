@@ -278,6 +278,74 @@ template <class T, class P> struct ColUnroll {
     static constexpr int v = kFull > 8 ? 8 : kFull;
 };
 
+// Epilogue shared by the across-TAD kernels. The CTA's 8 row-lanes are merged through shared
+// memory in one round: thread t of the CTA then owns TAD t of the tile (32 * W TADs), so partial
+// states and results are written with consecutive threads on consecutive TADs. Partials of the
+// across-TAD kernels are laid out [split][TAD] for that reason (a.partTadStride == 1).
+// `rows` is shared memory for 8 * 32 * W states, `lastFlag` one shared int.
+template <class T, class P, int W>
+ND_D void cols_finish(const ReduceArgs &a, const typename P::State (&s)[W], typename P::State *rowsFlat, int *lastFlag,
+                      LL hi, LL tile, const typename Elem<T>::C *p) {
+    typedef typename P::State State;
+    constexpr int kTile = 32 * W;
+    State (*rows)[kTile] = reinterpret_cast<State (*)[kTile]>(rowsFlat);
+    T *az = static_cast<T *>(a.z);
+    State *parts = reinterpret_cast<State *>(a.partials);
+#pragma unroll
+    for (int w = 0; w < W; w++) rows[threadIdx.y][threadIdx.x * W + w] = s[w];
+    __syncthreads();
+    const int t = threadIdx.y * 32 + threadIdx.x;
+    const LL tlo = tile * kTile + t;
+    const bool owner = t < kTile && tlo < a.colLo;
+    const LL tr = hi * a.colLo + tlo;
+    if (owner) {
+        State m = rows[0][t];
+#pragma unroll
+        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
+        if (a.splits == 1) az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        else parts[(LL) blockIdx.y * a.partSplitStride + tr] = m;
+    }
+    if (a.splits == 1 || a.counters == nullptr) return;
+    // the CTA that completes this TAD tile last merges the tile's partials (nobody waits)
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const int last = atomicAdd(&a.counters[blockIdx.x], 1u) == (unsigned) (a.splits - 1);
+        if (last) a.counters[blockIdx.x] = 0u;
+        *lastFlag = last;
+    }
+    __syncthreads();
+    if (!*lastFlag) return;
+    __threadfence();
+    // row-lane y folds segments y, y + 8, ... (ascending) of every TAD of the tile, then the
+    // owners fold the 8 row-lane results in ascending order
+    for (int c = threadIdx.x; c < kTile; c += 32) {
+        State m;
+        P::init(m);
+        const LL clo = tile * kTile + c;
+        if (clo < a.colLo) {
+            const State *src = parts + hi * a.colLo + clo;
+            int k = threadIdx.y;
+            for (; k + 3 * kColRows < a.splits; k += 4 * kColRows) {
+                State q0 = load_state_cg(src + (LL) k * a.partSplitStride);
+                State q1 = load_state_cg(src + (LL) (k + kColRows) * a.partSplitStride);
+                State q2 = load_state_cg(src + (LL) (k + 2 * kColRows) * a.partSplitStride);
+                State q3 = load_state_cg(src + (LL) (k + 3 * kColRows) * a.partSplitStride);
+                P::merge(m, q0); P::merge(m, q1); P::merge(m, q2); P::merge(m, q3);
+            }
+            for (; k < a.splits; k += kColRows) P::merge(m, load_state_cg(src + (LL) k * a.partSplitStride));
+        }
+        rows[threadIdx.y][c] = m;
+    }
+    __syncthreads();
+    if (owner) {
+        State m = rows[0][t];
+#pragma unroll
+        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
+        az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+    }
+}
+
 template <class T, class P, int W>
 __global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceArgs a) {
     grid_dependency_sync();
@@ -344,67 +412,9 @@ __global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceAr
             }
         }
     }
-    // The CTA's 8 row-lanes are merged through shared memory in one round: thread t of the CTA
-    // then owns TAD t of the tile (32 * W TADs), so partial states and results are written with
-    // consecutive threads on consecutive TADs. Partials of the across-TAD kernel are laid out
-    // [split][TAD] for that reason (a.partTadStride == 1).
-    constexpr int kTile = 32 * W;
-    __shared__ State rows[kColRows][kTile];
+    __shared__ State rows[kColRows * 32 * W];
     __shared__ int lastFlag;
-    State *parts = reinterpret_cast<State *>(a.partials);
-#pragma unroll
-    for (int w = 0; w < W; w++) rows[threadIdx.y][threadIdx.x * W + w] = s[w];
-    __syncthreads();
-    const int t = threadIdx.y * 32 + threadIdx.x;
-    const LL tlo = tile * kTile + t;
-    const bool owner = t < kTile && tlo < a.colLo;
-    const LL tr = hi * a.colLo + tlo;
-    if (owner) {
-        State m = rows[0][t];
-#pragma unroll
-        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
-        if (a.splits == 1) az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
-        else parts[(LL) blockIdx.y * a.partSplitStride + tr] = m;
-    }
-    if (a.splits == 1 || a.counters == nullptr) return;
-    // the CTA that completes this TAD tile last merges the tile's partials (nobody waits)
-    __threadfence();
-    __syncthreads();
-    if (t == 0) {
-        const int last = atomicAdd(&a.counters[blockIdx.x], 1u) == (unsigned) (a.splits - 1);
-        if (last) a.counters[blockIdx.x] = 0u;
-        lastFlag = last;
-    }
-    __syncthreads();
-    if (!lastFlag) return;
-    __threadfence();
-    // row-lane y folds segments y, y + 8, ... (ascending) of every TAD of the tile, then the
-    // owners fold the 8 row-lane results in ascending order
-    for (int c = threadIdx.x; c < kTile; c += 32) {
-        State m;
-        P::init(m);
-        const LL clo = tile * kTile + c;
-        if (clo < a.colLo) {
-            const State *src = parts + hi * a.colLo + clo;
-            int k = threadIdx.y;
-            for (; k + 3 * kColRows < a.splits; k += 4 * kColRows) {
-                State q0 = load_state_cg(src + (LL) k * a.partSplitStride);
-                State q1 = load_state_cg(src + (LL) (k + kColRows) * a.partSplitStride);
-                State q2 = load_state_cg(src + (LL) (k + 2 * kColRows) * a.partSplitStride);
-                State q3 = load_state_cg(src + (LL) (k + 3 * kColRows) * a.partSplitStride);
-                P::merge(m, q0); P::merge(m, q1); P::merge(m, q2); P::merge(m, q3);
-            }
-            for (; k < a.splits; k += kColRows) P::merge(m, load_state_cg(src + (LL) k * a.partSplitStride));
-        }
-        rows[threadIdx.y][c] = m;
-    }
-    __syncthreads();
-    if (owner) {
-        State m = rows[0][t];
-#pragma unroll
-        for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
-        az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
-    }
+    cols_finish<T, P, W>(a, s, rows, &lastFlag, hi, tile, p);
 }
 
 // Separate merge pass for calls whose partials were not merged inside the reduction launch.
