@@ -44,34 +44,84 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the benchmark's kernels run: through NVML
+    (read-only queries every ~2 ms from a thread) when the bindings are importable, else by
+    parsing `nvidia-smi -lms`."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index = index
-        self.lines = []          # (arrival time, csv line)
+        self.samples = []        # (arrival time, sm MHz, max sm MHz, set of reasons)
         self.proc = None
+        self.thread = None
+        self.running = False
+        self.source = None
         self.window = [None, None]
 
+    def _visible_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
+
     def start(self):
-        """Starts nvidia-smi and waits (up to 3 s) for its first sample, so that the sampler is
-        already running when the timed region begins."""
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._visible_index())
+            self.source = "nvml"
+            self.running = True
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+        except Exception:
+            self._start_smi()
+        t0 = time.monotonic()
+        while not self.samples and time.monotonic() - t0 < 3.0:
+            time.sleep(0.01)
+
+    def _poll_nvml(self):
+        n = self.nvml
+        mx = float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM))
+        bits = (("hw_slowdown", n.nvmlClocksThrottleReasonHwSlowdown),
+                ("hw_thermal_slowdown", n.nvmlClocksThrottleReasonHwThermalSlowdown),
+                ("sw_thermal_slowdown", n.nvmlClocksThrottleReasonSwThermalSlowdown),
+                ("sw_power_cap", n.nvmlClocksThrottleReasonSwPowerCap))
+        while self.running:
+            try:
+                sm = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.monotonic(), sm, mx, {name for name, bit in bits if mask & bit}))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def _start_smi(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self._visible_index()), "--query-gpu=" + self.FIELDS,
                                           "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-            t0 = time.monotonic()
-            while not self.lines and time.monotonic() - t0 < 3.0:
-                time.sleep(0.01)
+            self.source = "nvidia-smi"
+            threading.Thread(target=self._pump_smi, daemon=True).start()
         except OSError:
             self.proc = None
 
-    def _pump(self):
+    def _pump_smi(self):
         for line in self.proc.stdout:
-            self.lines.append((time.monotonic(), line.strip()))
+            parts = [p.strip() for p in line.strip().split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm, mx = float(parts[1]), float(parts[2])
+            except ValueError:
+                continue
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            self.samples.append((time.monotonic(), sm, mx,
+                                 {n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")}))
 
     def mark_begin(self):
         self.window[0] = time.monotonic()
@@ -80,30 +130,26 @@ class ClockSampler:
         self.window[1] = time.monotonic()
 
     def stop(self):
-        """Summary over the samples taken while the GPU ran this benchmark's kernels (warm-up, the
-        timed region and the per-kernel timings); `samples_in_timed_region` counts those that fell
-        between mark_begin() and mark_end()."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
-        time.sleep(0.05)
-        self.proc.terminate()
-        sm, mx, reasons, inside = [], [], set(), 0
-        for when, line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            if self.window[0] is not None and self.window[1] is not None and self.window[0] <= when <= self.window[1]:
-                inside += 1
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "samples_in_timed_region": inside}
+        """Summary over the samples taken between mark_begin() and mark_end() (the timed region);
+        when the region was too short to catch one, over all samples taken while this benchmark's
+        kernels ran (warm-up through the per-kernel timings), and `scope` says which."""
+        self.running = False
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
+        if self.proc is not None:
+            time.sleep(0.05)
+            self.proc.terminate()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock samples"], "samples": 0}
+        w0, w1 = self.window
+        inside = [s for s in self.samples if w0 is not None and w1 is not None and w0 <= s[0] <= w1]
+        use = inside if inside else self.samples
+        reasons = set()
+        for s in use:
+            reasons |= s[3]
+        return {"sm_mhz": float(np.median([s[1] for s in use])), "sm_max_mhz": max(s[2] for s in use),
+                "reasons": sorted(reasons), "samples": len(use), "scope": "timed region" if inside else "whole run",
+                "source": self.source}
 
 
 def make_inputs(rows):
@@ -438,13 +484,43 @@ def run_ours(args):
         with open(traffic_file) as f:
             roofline["traffic"] = json.load(f).get(dom)
 
-    # end to end through host buffers: H2D of x, b, y, the chain, D2H of the result
+    # End to end through host buffers: H2D of x, b, y, the chain, D2H of the result. The arrays are
+    # cut into row blocks; block k's chain runs while block k+1 is copied in and block k-1 is copied
+    # out (three streams, the same exec* calls on [rows/blocks, COLS] shapeInfos), so the step costs
+    # about max(H2D, D2H) on a full-duplex link instead of their sum.
+    NBLK = 16
+    brow = ROWS // NBLK
+    bbytes = brow * COLS * 4
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    h_in, h_cmp, h_out = (ctypes.c_void_p(q.cuda_stream) for q in (s_in, stream, s_out))
+    ev_in = [torch.cuda.Event() for _ in range(NBLK)]
+    ev_cmp = [torch.cuda.Event() for _ in range(NBLK)]
+    ev_begin, ev_end = torch.cuda.Event(), torch.cuda.Event()
+    xib = calls.longs(S.shape_info([brow, COLS]))
+    cp = lib.nd4jb200_memcpy_async
+    V = ctypes.c_void_p
+
     def e2e_step():
-        ops.memcpyAsync(dx, hx.data_ptr(), ELEMS * 4, 1, stream.cuda_stream)
-        ops.memcpyAsync(db, hb.data_ptr(), COLS * 4, 1, stream.cuda_stream)
-        ops.memcpyAsync(dy, hy.data_ptr(), ELEMS * 4, 1, stream.cuda_stream)
-        step()
-        ops.memcpyAsync(hz.data_ptr(), dz, ELEMS * 4, 2, stream.cuda_stream)
+        ev_begin.record(stream)             # the copies of this step follow the previous step's work
+        s_in.wait_event(ev_begin)
+        s_out.wait_event(ev_begin)
+        calls.check(cp(V(db.data_ptr()), V(hb.data_ptr()), COLS * 4, 1, h_in))
+        for k in range(NBLK):
+            off = k * bbytes
+            calls.check(cp(V(dx.data_ptr() + off), V(hx.data_ptr() + off), bbytes, 1, h_in))
+            calls.check(cp(V(dy.data_ptr() + off), V(hy.data_ptr() + off), bbytes, 1, h_in))
+            ev_in[k].record(s_in)
+            stream.wait_event(ev_in[k])
+            calls.check(lib.nd4jb200_exec_broadcast(h_cmp, 0, 0, V(dx.data_ptr() + off), xib, P(db), bi,
+                                                    V(t1.data_ptr() + off), xib, d1, 1))
+            calls.check(lib.nd4jb200_exec_transform(h_cmp, 0, 15, V(t1.data_ptr() + off), xib, V(t2.data_ptr() + off), xib, None))
+            calls.check(lib.nd4jb200_exec_pairwise(h_cmp, 0, 6, V(t2.data_ptr() + off), xib, V(dy.data_ptr() + off), xib,
+                                                   V(dz.data_ptr() + off), xib, None))
+            ev_cmp[k].record(stream)
+            s_out.wait_event(ev_cmp[k])
+            calls.check(cp(V(hz.data_ptr() + off), V(dz.data_ptr() + off), bbytes, 2, h_out))
+        ev_end.record(s_out)
+        stream.wait_event(ev_end)           # the step ends when the last block is back on the host
 
     e2e_step()
     barrier()
@@ -455,7 +531,8 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": round(world * ELEMS / e2e_ms / 1e6, 3), "unit": "Gelem/s", "ms_per_step": round(e2e_ms, 3),
-           "h2d_bytes_per_step": 2 * ELEMS * 4 + COLS * 4, "d2h_bytes_per_step": ELEMS * 4}
+           "h2d_bytes_per_step": 2 * ELEMS * 4 + COLS * 4, "d2h_bytes_per_step": ELEMS * 4,
+           "pipeline": "%d row blocks; H2D, chain and D2H on three streams" % NBLK}
 
     families = None
     if world == 1 and not args.no_families:

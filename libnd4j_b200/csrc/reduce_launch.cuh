@@ -119,8 +119,10 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         // few, long TADs: cut each into segments so that every SM has work
         LL groups = a.numTads;
         LL splits = 1;
-        if (groups * a.group < kTargetThreads) {
-            splits = ceil_div(kTargetThreads, groups * a.group);
+        // whole CTAs per TAD (few, long TADs) stream best with twice as many threads resident
+        const LL target = a.group == kBlock ? 2 * kTargetThreads : kTargetThreads;
+        if (groups * a.group < target) {
+            splits = ceil_div(target, groups * a.group);
             const LL maxSplits = a.tadLen / ((LL) a.group * perLane * 8);
             if (splits > maxSplits) splits = maxSplits;
             if (splits < 1) splits = 1;
