@@ -348,6 +348,22 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
                     calls.check(lib.nd4jb200_exec_reduce3(st, code, op, P(xa[k[0]]), info, None, P(ya[k[0]]), info, P(zz), zi4, d1, 1))
                 record("reduce3_%s_%s_%s_32768x512" % (opname, lay, name), nb, 32768 * 512, f)
         del xa, ya
+    # reduce3 over all TAD pairs: every row of x [4096,512] against every row of y [4096,512]. The work is
+    # 4096 * 4096 * 512 pair operations over 16 MB of input: bound by the FP32 pipes, not by HBM, so the
+    # entry reports pair operations per second instead of a bandwidth fraction.
+    xa_, ya_ = torch.randn(4096, 512, device=dev, generator=g), torch.randn(4096, 512, device=dev, generator=g)
+    za_ = torch.zeros(4096 * 4096, device=dev)
+    ai, azi = calls.longs(S.shape_info([4096, 512])), calls.longs(S.shape_info([4096, 4096]))
+    for op, opname in ((2, "cosine"), (1, "euclidean")):
+        name = "reduce3_all_%s_f32_4096x4096x512" % opname
+        record(name, 2 * 4096 * 512 * 4 + 4096 * 4096 * 4, 4096 * 4096,
+               lambda op=op: calls.check(lib.nd4jb200_exec_reduce3_all(st, 0, op, P(xa_), ai, None, P(ya_), ai, P(za_), azi, d1, 1)),
+               iters=5)
+        if name in out:
+            out[name]["bound"] = "fp32 pipes (all-pairs work, inputs stay in L2)"
+            out[name]["Gpairops_s"] = round(4096 * 4096 * 512 / out[name]["ms"] / 1e6, 1)
+            del out[name]["frac_of_measured_peak"]
+    del xa_, ya_, za_
     # scalar family: x * 1.5 on the chain-sized array
     xs_ = torch.randn(ELEMS, device=dev, generator=g)
     zs_ = torch.empty_like(xs_)

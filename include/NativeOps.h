@@ -55,6 +55,11 @@ struct float16 {
     void execReduce3##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParamsVals,      \
                         T *y, Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,     \
                         int dimensionLength);                                                                       \
+    /* nd4jb200_exec_reduce3_all (NativeOps.h:314-360); the TAD descriptors are not needed */                       \
+    void execReduce3All##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xInfo, T *extraParamsVals,        \
+                           T *y, Nd4jLong *yInfo, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,       \
+                           int dimensionLength, Nd4jLong *xTadShapeInfo, Nd4jLong *xOffsets,                        \
+                           Nd4jLong *yTadShapeInfo, Nd4jLong *yOffsets);                                            \
     /* nd4jb200_exec_scalar_along_dimension (NativeOps.h:1160-1214) */                                              \
     void execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,                     \
                        Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension, int dimensionLength);      \

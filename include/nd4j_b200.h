@@ -95,6 +95,11 @@ int nd4jb200_exec_summary_stats_scalar(void *stream, int dtype, int opNum, const
 int nd4jb200_exec_reduce3(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                           const void *extraParams, const void *y, const Nd4jLong *yShapeInfo,
                           void *z, const Nd4jLong *zShapeInfo, const int *dimension, int dimensionLength);
+/* every TAD of x against every TAD of y: z[r * yTads + g]; NativeOps::execReduce3All{Float,Double,Half}
+ * (blas/NativeOps.h:314-360; include/loops/reduce3.h:919-990). z must be dense. */
+int nd4jb200_exec_reduce3_all(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                              const void *extraParams, const void *y, const Nd4jLong *yShapeInfo, void *z,
+                              const Nd4jLong *zShapeInfo, const int *dimension, int dimensionLength);
 int nd4jb200_exec_reduce3_scalar(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                                  const void *extraParams, const void *y, const Nd4jLong *yShapeInfo,
                                  double *result);

@@ -338,6 +338,32 @@ int nd4jb200_exec_reduce3(void *stream, int dtype, int opNum, const void *x, con
     return BY_DTYPE(dtype, reduce3, opNum, s.call, as_stream(stream));
 }
 
+int nd4jb200_exec_reduce3_all(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                              const void *extraParams, const void *y, const Nd4jLong *yShapeInfo, void *z,
+                              const Nd4jLong *zShapeInfo, const int *dimension, int dimensionLength) {
+    (void) extraParams;   // the reference hands the functors a zeroed parameter block here (reduce3.h:957-962)
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(y, "y")); ND_TRY(need(z, "z"));
+    ShapeDesc xd, yd, zd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &yd));
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    ReduceCall c;
+    ND_TRY(make_tad_plan(xd, dimension, dimensionLength, &c.xPlan));
+    ND_TRY(make_tad_plan(yd, dimension, dimensionLength, &c.yPlan));
+    if (c.xPlan.tadLen != c.yPlan.tadLen) return bad_arg("reduce3 all-pairs: the TADs of x and y differ in length");
+    if (zd.length != c.xPlan.numTads * c.yPlan.numTads) return bad_arg("reduce3 all-pairs: result must hold xTads * yTads elements");
+    if (zd.ews != 1) return unsupported("reduce3 all-pairs: the result must be dense (the reference writes result[r * yTads + g])");
+    // inside a TAD both operands are walked in c-order; the reference pairs element f of x with
+    // element f of y in each TAD's own order, which is the same pairing unless the orders differ
+    if (c.xPlan.inner.rank > 1 && xd.order != yd.order)
+        return unsupported("reduce3 all-pairs: multi-axis TADs of arrays with different orders");
+    if (xd.length == 0 || yd.length == 0) return kOk;
+    c.x = x; c.y = y; c.extra = nullptr; c.z = z;
+    c.finishLen = c.xPlan.tadLen;
+    return BY_DTYPE(dtype, reduce3_all, opNum, c, as_stream(stream));
+}
+
 int nd4jb200_exec_reduce3_scalar(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                                  const void *extraParams, const void *y, const Nd4jLong *yShapeInfo, double *result) {
     ND_TRY(check_dtype(dtype));

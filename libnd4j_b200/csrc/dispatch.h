@@ -4,6 +4,7 @@
 #include "elementwise_engine.cuh"
 #include "reduce_launch.cuh"
 #include "rng_engine.cuh"
+#include "reduce3_all.cuh"
 
 namespace nd4jb200 {
 
@@ -15,6 +16,7 @@ namespace nd4jb200 {
     Status scalar_tad_##S(int opNum, const BcArgs &a, cudaStream_t st);                \
     Status reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);                \
     Status reduce3_##S(int opNum, const ReduceCall &c, cudaStream_t st);               \
+    Status reduce3_all_##S(int opNum, const ReduceCall &c, cudaStream_t st);           \
     Status index_reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);          \
     Status summary_stats_##S(int opNum, const ReduceCall &c, cudaStream_t st);         \
     Status random_##S(int opNum, int arity, const RngArgs &a, cudaStream_t st);

@@ -2,7 +2,7 @@
 // opNum of the reference's table and exposes a switch-based dispatcher.
 //   ND_DTYPE:  0 float, 1 double, 2 half
 //   ND_FAMILY: 0 transform, 1 binary (pairwise, scalar, broadcast, scalar-along-dimension),
-//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random
+//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random, 5 reduce3 over all TAD pairs
 #include "dispatch.h"
 #include "functors.cuh"
 #include "policies.cuh"
@@ -110,6 +110,20 @@ Status ND_S(summary_stats)(int opNum, const ReduceCall &c, cudaStream_t st) {
         case 0: return run_reduction<ND_T, pol::Stats<0, CT> >(c, st);
         case 1: return run_reduction<ND_T, pol::Stats<1, CT> >(c, st);
         default: return unknown_op("summary stats", opNum);
+    }
+}
+#elif ND_FAMILY == 5
+Status ND_S(reduce3_all)(int opNum, const ReduceCall &c, cudaStream_t st) {
+    switch (opNum) {
+        case 0: return run_reduce3_all<ND_T, pol::Reduce3<0, CT> >(c, st);
+        case 1: return run_reduce3_all<ND_T, pol::Reduce3<1, CT> >(c, st);
+        case 2: return run_reduce3_all<ND_T, pol::Reduce3<2, CT> >(c, st);
+        case 3: return run_reduce3_all<ND_T, pol::Reduce3<3, CT> >(c, st);
+        case 4: return run_reduce3_all<ND_T, pol::Reduce3<4, CT> >(c, st);
+        case 5: return run_reduce3_all<ND_T, pol::Reduce3<5, CT> >(c, st);
+        case 6: return run_reduce3_all<ND_T, pol::Reduce3<6, CT> >(c, st);
+        case 7: return run_reduce3_all<ND_T, pol::Reduce3<7, CT> >(c, st);
+        default: return unknown_op("reduce3", opNum);
     }
 }
 #elif ND_FAMILY == 4

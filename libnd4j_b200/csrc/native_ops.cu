@@ -144,6 +144,14 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
                                     Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),             \
                                     dimensionLength), "execReduce3" #S);                                               \
     }                                                                                                                  \
+    void NativeOps::execReduce3All##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,              \
+                                      T *extraParamsVals, T *y, Nd4jLong *yShapeInfo, T *result,                      \
+                                      Nd4jLong *resultShapeInfoBuffer, int *dimension, int dimensionLength,           \
+                                      Nd4jLong *, Nd4jLong *, Nd4jLong *, Nd4jLong *) {                               \
+        check(nd4jb200_exec_reduce3_all(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO,         \
+                                        result, Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength), \
+                                        dimensionLength), "execReduce3All" #S);                                        \
+    }                                                                                                                  \
     void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,            \
                                   Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension,                   \
                                   int dimensionLength) {                                                              \

@@ -81,6 +81,7 @@ def load_library(path=None):
         "nd4jb200_exec_summary_stats": (i, [vp, i, i, vp, llp, vp, vp, llp, ip, i, i]),
         "nd4jb200_exec_summary_stats_scalar": (i, [vp, i, i, vp, llp, vp, i, dp]),
         "nd4jb200_exec_reduce3": (i, [vp, i, i, vp, llp, vp, vp, llp, vp, llp, ip, i]),
+        "nd4jb200_exec_reduce3_all": (i, [vp, i, i, vp, llp, vp, vp, llp, vp, llp, ip, i]),
         "nd4jb200_exec_reduce3_scalar": (i, [vp, i, i, vp, llp, vp, vp, llp, dp]),
         "nd4jb200_exec_transform": (i, [vp, i, i, vp, llp, vp, llp, vp]),
         "nd4jb200_exec_transform_strided": (i, [vp, i, i, vp, ll, vp, ll, vp, ll]),
@@ -222,6 +223,19 @@ class NativeOps:
         self._check(self.lib.nd4jb200_exec_reduce3(self._stream(extraPointers), dt, opNum, _ptr(x), xsp,
                                                    _ptr(extraParamsVals), _ptr(y), ysp, _ptr(result), zsp, dmp,
                                                    dimensionLength))
+
+    def _execReduce3All(self, dt, extraPointers, opNum, x, xInfo, extraParamsVals, y, yInfo, result,
+                        resultShapeInfoBuffer, dimension, dimensionLength, xTadShapeInfo=None, xOffsets=None,
+                        yTadShapeInfo=None, yOffsets=None):
+        """Every TAD of x against every TAD of y; the TAD descriptors of the reference's signature are
+        accepted and ignored (the geometry is derived from the shapeInfos and the dimension list)."""
+        xs, xsp = _longs(xInfo)
+        ys, ysp = _longs(yInfo)
+        zs, zsp = _longs(resultShapeInfoBuffer)
+        dm, dmp = _ints(dimension)
+        self._check(self.lib.nd4jb200_exec_reduce3_all(self._stream(extraPointers), dt, opNum, _ptr(x), xsp,
+                                                       _ptr(extraParamsVals), _ptr(y), ysp, _ptr(result), zsp, dmp,
+                                                       dimensionLength))
 
     def _execReduce3Scalar(self, dt, extraPointers, opNum, x, xShapeInfo, extraParamsVals, y, yShapeInfo):
         xs, xsp = _longs(xShapeInfo)
@@ -457,7 +471,7 @@ def _bind(generic, dt):
 
 
 for _fam in ("execReduce", "execReduceScalar", "execIndexReduce", "execIndexReduceScalar", "execSummaryStats",
-             "execSummaryStatsScalar", "execReduce3", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
+             "execSummaryStatsScalar", "execReduce3", "execReduce3All", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
              "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom"):
     for _sfx, _dt in _SUFFIX.items():
         _m = _bind("_" + _fam, _dt)

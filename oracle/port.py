@@ -225,6 +225,23 @@ class Port:
         z[:out.size] = out
         return z
 
+    def reduce3_all(self, op, x, x_info, y, y_info, z, z_info, dims, extra=None):
+        """Every TAD of x against every TAD of y, z[r * yTads + g] (reduce3.h:919-990); the functors see a
+        zeroed parameter block, as in the reference."""
+        self._need_f32(x, y)
+        mx, _, _ = self._gather(x, x_info, list(dims))
+        my, _, _ = self._gather(y, y_info, list(dims))
+        my = np.ascontiguousarray(my)
+        out = np.zeros(my.shape[0], dtype=np.float32)
+        for r in range(mx.shape[0]):
+            row = np.ascontiguousarray(np.broadcast_to(mx[r], my.shape))
+            rc = self.lib.port_reduce3_f32(op, _c(row), _c(my), ctypes.c_longlong(my.shape[1]),
+                                           ctypes.c_longlong(my.shape[0]), ctypes.c_longlong(my.shape[1]), _c(out),
+                                           ctypes.c_float(0.0))
+            assert rc == 0
+            z[r * my.shape[0]:(r + 1) * my.shape[0]] = out
+        return z
+
     def reduce3_scalar(self, op, x, x_info, y, y_info, extra=None):
         out = np.zeros(1, dtype=np.float32)
         return self.reduce3(op, x, x_info, y, y_info, out, np.array([2, 1, 1, 1, 1, 0, 1, 99]), None, extra)[0]

@@ -117,6 +117,17 @@ class Reference:
         self._f("ref_execReduce3", x)(op, _p(x), _p(xi), _p(extra), _p(y), _p(yi), _p(z), _p(zi), _p(d), len(d))
         return z
 
+    def reduce3_all(self, op, x, x_info, y, y_info, z, z_info, dims, extra=None):
+        """execReduce3All (include/loops/reduce3.h:919-990): z[r * yTads + g]; z is zeroed first because
+        the reference accumulates onto whatever the result buffer holds."""
+        xi, yi, zi, d = _li(x_info), _li(y_info), _li(z_info), _ii(dims)
+        xt, xo = self.tad(x_info, dims)
+        yt, yo = self.tad(y_info, dims)
+        z[...] = 0
+        self._f("ref_execReduce3All", x)(op, _p(x), _p(xi), _p(extra), _p(y), _p(yi), _p(z), _p(zi), _p(d), len(d),
+                                         _p(xt), _p(xo), _p(yt), _p(yo))
+        return z
+
     def reduce3_scalar(self, op, x, x_info, y, y_info, extra=None):
         xi, yi = _li(x_info), _li(y_info)
         out = np.zeros(1, dtype=x.dtype)

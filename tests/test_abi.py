@@ -43,6 +43,8 @@ def test_every_declared_c_symbol_is_exported(lib):
 
 # Manglings of the reference's members as produced by gcc for blas/NativeOps.h.
 MANGLED = [
+    "_ZN9NativeOps19execReduce3AllFloatEPPviPfPxS2_S2_S3_S2_S3_PiiS3_S3_S3_S3_",
+    "_ZN9NativeOps18execReduce3AllHalfEPPviP7float16PxS3_S3_S4_S3_S4_PiiS4_S4_S4_S4_",
     "_ZN9NativeOps15execReduceFloatEPPviPfPxS2_S2_S3_Pii",
     "_ZN9NativeOps15execReduceFloatEPPviPfPxS2_S2_S3_",
     "_ZN9NativeOps21execReduceScalarFloatEPPviPfPxS2_",

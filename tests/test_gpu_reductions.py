@@ -373,3 +373,63 @@ def test_reduce3_full_config(ops, real_ref):
                 tol = TOL[dt]
                 scale = np.maximum(np.abs(truth), 1.0 if op == 2 else 0.0)
                 assert (np.abs(host(dz).astype(np.float64) - truth) <= tol * scale).all(), (dt, kind, op)
+
+
+# ---- reduce3 over all TAD pairs -------------------------------------------------------------------
+def reduce3_all_truth(op, a, b):
+    """a [xTads, len], b [yTads, len] -> [xTads, yTads] in float64."""
+    return np.stack([reduce3_truth(op, np.broadcast_to(a[r], b.shape), b) for r in range(a.shape[0])])
+
+
+@pytest.mark.parametrize("op", range(8))
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.float16])
+def test_reduce3_all_pairs(ops, real_ref, op, dt):
+    """execReduce3All: ragged tile edges (70 x 45 TADs, 129 elements) against the reference's own
+    loop (include/loops/reduce3.h:919-990)."""
+    rng = np.random.default_rng(100 + op)
+    xs, ys = (70, 129), (45, 129)
+    kind = "positive" if op == 6 else ("levels" if op in (4, 7) else "normal")
+    x, y = rand_input(rng, xs, dt, kind), rand_input(rng, ys, dt, kind)
+    xi, yi, zi = S.shape_info(xs), S.shape_info(ys), S.shape_info([70, 45])
+    truth = reduce3_all_truth(op, x.astype(np.float64), y.astype(np.float64))
+    if op == 4:
+        # EqualsWithEps reads index 2 of a parameter block the reference never allocates here
+        # (extraParamsLen is 0, include/ops/ops.h:2839-2859): the truth stands in for it, eps = 0
+        want = truth.astype(dt)
+    else:
+        want = real_ref.reduce3_all(op, x.ravel(), xi, y.ravel(), yi, np.zeros(70 * 45, dt), zi, [1]).reshape(70, 45)
+    dz = dev(np.full(70 * 45, 7, dt))
+    getattr(ops, "execReduce3All" + NAME[dt])(None, op, dev(x), xi, None, dev(y), yi, dz, zi, [1], 1, None, None, None, None)
+    got = host(dz).astype(np.float64).reshape(70, 45)
+    tol = TOL[dt]
+    scale = np.maximum(np.abs(truth), 1.0 if op in (2, 5) else 1e-30)
+    bound = np.maximum(tol * scale, np.abs(want.astype(np.float64) - truth) * 1.0000001)
+    if op in (0, 3):
+        ax, ay = np.abs(x.astype(np.float64)), np.abs(y.astype(np.float64))
+        mag = ax.sum(1)[:, None] + ay.sum(1)[None, :] if op == 0 else ax @ ay.T
+        bound = np.maximum(bound, tol * mag)
+    assert (np.abs(got - truth) <= bound).all()
+
+
+@pytest.mark.parametrize("kind", ["f", "fview2", "cview2"])
+def test_reduce3_all_pairs_views_and_columns(ops, real_ref, kind):
+    """TADs along dimension 0 of strided operands: every column of x against every column of y."""
+    rng = np.random.default_rng(77)
+    x, y = rand_input(rng, (200, 33), np.float32), rand_input(rng, (200, 70), np.float32)
+    lx, ly = Layout(x, kind), Layout(y, kind)
+    zi = S.shape_info([33, 70])
+    dz = torch.zeros(33 * 70, device="cuda")
+    ops.execReduce3AllFloat(None, 1, dev(lx.buffer), lx.info, None, dev(ly.buffer), ly.info, dz, zi, [0], 1,
+                            None, None, None, None)
+    want = real_ref.reduce3_all(1, lx.buffer, lx.info, ly.buffer, ly.info, np.zeros(33 * 70, np.float32), zi, [0])
+    truth = reduce3_all_truth(1, x.T.astype(np.float64), y.T.astype(np.float64)).ravel()
+    np.testing.assert_allclose(host(dz), truth, rtol=1e-5)
+    np.testing.assert_allclose(host(dz), want, rtol=1e-5)
+
+
+def test_reduce3_all_pairs_rejects_mismatched_tads(ops):
+    xi, yi, zi = S.shape_info([4, 8]), S.shape_info([4, 9]), S.shape_info([4, 4])
+    z = torch.zeros(16, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.execReduce3AllFloat(None, 1, torch.zeros(32, device="cuda"), xi, None, torch.zeros(36, device="cuda"), yi,
+                                z, zi, [1], 1, None, None, None, None)
