@@ -218,6 +218,24 @@ Status random_common(void *stream, int dtype, int opNum, int arity, RandomState 
         a.mode = 1;
     }
     if (gaussian && (first & 1)) return bad_arg("the Gaussian family pairs elements (2k, 2k+1): `first` must be even");
+    a.aux = nullptr; a.auxLen = 0;
+    if ((opNum == 5 || opNum == 8 || opNum == 9) && arity == 2) {
+        // Choice / Binomial / BinomialEx: whole calls on operands addressed by elementWiseStride
+        if (!zd || first != 0 || count != length) return unsupported("Choice and the binomial ops are served for whole calls only");
+        if (zd->ews < 1 || xd->ews < 1 || yd->ews < 1)
+            return unsupported("Choice and the binomial ops address their operands by elementWiseStride (>= 1)");
+        a.mode = 1;
+        if (opNum == 5) {
+            const size_t es = dtype == kF64 ? 8 : (dtype == kF32 ? 4 : 2);
+            void *ws = nullptr;
+            // the sums go behind the result slot and the arrival counters of the reductions, which
+            // must stay zero between launches
+            const size_t skip = 256 + kCounterSlots * sizeof(unsigned);
+            ND_TRY(workspace(as_stream(stream), skip + es * (size_t) yd->length, &ws, nullptr));
+            a.aux = static_cast<char *>(ws) + skip;
+            a.auxLen = yd->length;
+        }
+    }
     // special ops exist only in the three-operand form; the other arities of the reference fall
     // through to the functor defaults (-1 / -2), include/loops/cpu/random.cpp:86-185
     int op = opNum;
@@ -604,10 +622,30 @@ int nd4jb200_exec_random_xy(void *stream, int dtype, int opNum, Nd4jPointer stat
     ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
     ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &yd));
     ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
-    if (xd.length < zd.length || yd.length < zd.length) return bad_arg("execRandom: x or y holds fewer elements than z");
+    // Choice reads x and y by choice index and Binomial reads y by trial index: their lengths are unrelated to z's
+    const bool tableOperands = opNum == 5 || opNum == 8;
+    if (!tableOperands && (xd.length < zd.length || yd.length < zd.length))
+        return bad_arg("execRandom: x or y holds fewer elements than z");
+    if (opNum == 5 && xd.length < yd.length) return bad_arg("Choice: x holds fewer values than y holds probabilities");
     RandomState *s = static_cast<RandomState *>(state);
     ND_TRY(random_common(stream, dtype, opNum, 2, s, x, &xd, y, &yd, z, &zd, extraArguments, 0, zd.length, zd.length));
-    rewind_state(s, zd.length);
+    LL advance = zd.length;
+    if (opNum == 8 || opNum == 9) {
+        // the binomial ops consume zLength * trials draws (special_random_ops.h:523-524); trials is
+        // extraArguments[0], which lives on the device
+        ND_TRY(need(extraArguments, "extraArguments"));
+        double trials = 0;
+        unsigned char raw[8] = {0};
+        const size_t es = dtype == kF64 ? 8 : (dtype == kF32 ? 4 : 2);
+        ND_CUDA(cudaMemcpyAsync(raw, extraArguments, es, cudaMemcpyDeviceToHost, as_stream(stream)));
+        ND_CUDA(cudaStreamSynchronize(as_stream(stream)));
+        if (dtype == kF64) trials = *reinterpret_cast<double *>(raw);
+        else if (dtype == kF32) trials = *reinterpret_cast<float *>(raw);
+        else trials = __half2float(*reinterpret_cast<__half *>(raw));
+        const int t = (int) trials;
+        advance = t > 0 ? zd.length * (LL) t : 0;
+    }
+    rewind_state(s, advance);
     return kOk;
 }
 

@@ -161,6 +161,11 @@ static Status launch_gaussian(RngArgs a, cudaStream_t st) {
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
+static LL special_blocks(LL count) {
+    LL blocks = ceil_div(count, kRngBlock);
+    const LL cap = (LL) kNumSMs * 32;
+    return blocks > cap ? cap : blocks;
+}
 template <int OP>
 static Status by_arity(int arity, const RngArgs &a, cudaStream_t st) {
     if (arity == 0) return launch_random<OP, 0>(a, st);
@@ -180,9 +185,25 @@ Status ND_S(random)(int opNum, int arity, const RngArgs &a, cudaStream_t st) {
         case 100: return by_arity<100>(arity, a, st);
         case 6: return launch_gaussian<false>(a, st);    // reached only in the three-operand form
         case 10: return launch_gaussian<true>(a, st);
-        case 5: case 8: case 9: case 11:
-            return unsupported("random opNum " + std::to_string(opNum) +
-                               " (Choice / Binomial / BinomialEx / TruncatedNormal) is not served yet");
+        case 5: {
+            if (a.count <= 0) return kOk;
+            // running sums first (one thread, the reference's summation order), then the draws
+            launch_kernel(k_choice_sums<ND_T>, dim3(1), dim3(32), st, static_cast<const ND_T *>(a.y), a.sy, a.auxLen,
+                          static_cast<ND_T *>(const_cast<void *>(a.aux)));
+            launch_kernel(k_random_choice<ND_T>, dim3((unsigned) special_blocks(a.count)), dim3(kRngBlock), st, a);
+            ND_CUDA(cudaGetLastError());
+            return kOk;
+        }
+        case 8: case 9: {
+            if (a.count <= 0) return kOk;
+            if (opNum == 8) launch_kernel(k_random_binomial<ND_T, false>, dim3((unsigned) special_blocks(a.count)), dim3(kRngBlock), st, a);
+            else launch_kernel(k_random_binomial<ND_T, true>, dim3((unsigned) special_blocks(a.count)), dim3(kRngBlock), st, a);
+            ND_CUDA(cudaGetLastError());
+            return kOk;
+        }
+        case 11:
+            return unsupported("random opNum 11 (TruncatedNormalDistribution) is not served: its rejection loop "
+                               "compares rounded transcendental results, which cannot be reproduced bit for bit");
         default: return unknown_op("random", opNum);
     }
 }

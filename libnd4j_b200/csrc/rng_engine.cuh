@@ -163,6 +163,8 @@ struct RngArgs {
     View vx, vy, vz;
     int yIsZ;      // Gaussian family: y aliases z, so the mean comes from extra[0]
     LL chunk;      // dense path: elements per CTA (a multiple of 256 * pack width)
+    const void *aux;   // Choice: running sums of the probabilities (element type), auxLen of them
+    LL auxLen;
 };
 
 // Does (op, arity) consume the uniform draw of its element?
@@ -328,6 +330,68 @@ __global__ void __launch_bounds__(kRngBlock) k_random_gaussian(const RngArgs a) 
             if (LOGNORMAL) v = exp(v);
             Elem<T>::store(az + oz, v);
         }
+    }
+}
+
+// BinomialDistribution (8) and BinomialDistributionEx (9): z[e] = number of t in 1..trials whose
+// uniform draw at global index (e + 1) * t is below the success probability. extra = {trials,
+// probability}; when y does not alias z the probability is y[t - 1] (8: one per trial) or y[e]
+// (9: one per element) instead (special_random_ops.h:474-520, 598-650). Operands are addressed by
+// their elementWiseStride, as in the reference.
+template <class T, bool PER_ELEMENT>
+__global__ void __launch_bounds__(kRngBlock) k_random_binomial(const RngArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    const T *ay = static_cast<const T *>(a.y);
+    T *az = static_cast<T *>(a.z);
+    C p[2];
+    load_params<T, 2>(static_cast<const T *>(a.extra), p);
+    const int trials = (int) p[0];
+    const LL nthreads = (LL) gridDim.x * kRngBlock;
+    for (LL i = (LL) blockIdx.x * kRngBlock + threadIdx.x; i < a.count; i += nthreads) {
+        const LL e = a.first + i;
+        C prob = p[1];
+        if (!a.yIsZ && PER_ELEMENT) prob = Elem<T>::load(ay + e * a.sy);
+        int success = 0;
+        for (int t = 1; t <= trials; t++) {
+            const C u = rng_uniform<T>(rng_element(a.g, (e + 1) * t));
+            if (!a.yIsZ && !PER_ELEMENT) prob = Elem<T>::load(ay + (LL) (t - 1) * a.sy);
+            success += u < prob ? 1 : 0;
+        }
+        Elem<T>::store(az + e * a.sz, C(success));
+    }
+}
+
+// Choice (5): z[e] = x[f] for the first f whose running probability sum reaches the uniform draw
+// of element e, the last f if none does (special_random_ops.h:176-190). The running sums are
+// accumulated once, in the reference's order and in the element type's own arithmetic (a half
+// sum is rounded to half after every addition), by k_choice_sums; every element then scans them.
+template <class T>
+__global__ void k_choice_sums(const T *y, LL sy, LL n, T *sums) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    C c = C(0);
+    for (LL f = 0; f < n; f++) {
+        c = Elem<T>::to_c(Elem<T>::from_c(c + Elem<T>::load(y + f * sy)));
+        Elem<T>::store(sums + f, c);
+    }
+}
+
+template <class T>
+__global__ void __launch_bounds__(kRngBlock) k_random_choice(const RngArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    const T *ax = static_cast<const T *>(a.x);
+    const T *sums = static_cast<const T *>(a.aux);
+    T *az = static_cast<T *>(a.z);
+    const LL nthreads = (LL) gridDim.x * kRngBlock;
+    for (LL i = (LL) blockIdx.x * kRngBlock + threadIdx.x; i < a.count; i += nthreads) {
+        const LL e = a.first + i;
+        const C u = rng_uniform<T>(rng_element(a.g, e));
+        LL f = 0;
+        while (f < a.auxLen - 1 && !(u <= Elem<T>::load(sums + f))) f++;
+        az[e * a.sz] = ax[f * a.sx];
     }
 }
 

@@ -197,3 +197,69 @@ def test_large_uniform_properties(ops, pair):
     b = torch.zeros(n, device="cuda")
     ops.execRandomFloat(None, 0, st, b, zi, ex)
     assert torch.equal(a, b)
+
+
+
+
+@pytest.mark.parametrize("dt,name", [(np.float32, "Float"), (np.float64, "Double"), (np.float16, "Half")])
+def test_binomial_and_binomial_ex_bit_exact(ops, real_ref, pair, dt, name):
+    """BinomialDistribution with one probability (y aliases z) and with per-trial probabilities,
+    BinomialDistributionEx with per-element probabilities; then a Uniform call, which only matches
+    if the state advanced by zLength * trials as in the reference (special_random_ops.h:474-650)."""
+    st, rs, _ = pair
+    n, trials = 5000, 7
+    zi = S.shape_info([1, n])
+    fn = getattr(ops, "execRandom" + name)
+    rng = np.random.default_rng(5)
+    # 8, scalar probability: x, y and z are the same buffer
+    ex = np.array([trials, 0.35], dtype=dt)
+    z = np.zeros(n, dt); dz = dev(z)
+    fn(None, 8, st, dz, zi, dz, zi, dz, zi, dev(ex))
+    real_ref.random_xy(8, rs, z, zi, z, zi, z, zi, ex)
+    np.testing.assert_array_equal(host(dz), z)
+    assert 0 < z.mean() < trials
+    # 8, one probability per trial
+    probs = rng.uniform(0.1, 0.9, trials).astype(dt)
+    pi = S.shape_info([1, trials])
+    z = np.zeros(n, dt); dz = dev(z)
+    fn(None, 8, st, dz, zi, dev(probs), pi, dz, zi, dev(ex))
+    real_ref.random_xy(8, rs, z, zi, probs, pi, z, zi, ex)
+    np.testing.assert_array_equal(host(dz), z)
+    # 9, one probability per element
+    probs = rng.uniform(0.0, 1.0, n).astype(dt)
+    z = np.zeros(n, dt); dz = dev(z)
+    fn(None, 9, st, dz, zi, dev(probs), zi, dz, zi, dev(ex))
+    real_ref.random_xy(9, rs, z, zi, probs, zi, z, zi, ex)
+    np.testing.assert_array_equal(host(dz), z)
+    # the states moved in step
+    got, want = run_both(ops, real_ref, st, rs, 0, 1000, [0.0, 1.0], dt=dt, name=name)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt,name", [(np.float32, "Float"), (np.float64, "Double"), (np.float16, "Half")])
+def test_choice_bit_exact(ops, real_ref, pair, dt, name):
+    """Choice: z[e] = x[f] for the first f whose running probability sum reaches the draw; the sums are
+    accumulated in the element type (special_random_ops.h:176-190)."""
+    st, rs, _ = pair
+    n, k = 20000, 37
+    rng = np.random.default_rng(6)
+    values = rng.standard_normal(k).astype(dt)
+    probs = rng.uniform(0.0, 1.0, k)
+    probs = (probs / probs.sum()).astype(dt)
+    zi, ki = S.shape_info([1, n]), S.shape_info([1, k])
+    ex = np.array([1.0], dtype=dt)
+    z = np.zeros(n, dt); dz = dev(z)
+    getattr(ops, "execRandom" + name)(None, 5, st, dev(values), ki, dev(probs), ki, dz, zi, dev(ex))
+    real_ref.random_xy(5, rs, values, ki, probs, ki, z, zi, ex)
+    np.testing.assert_array_equal(host(dz), z)
+    assert len(np.unique(z)) > k // 2
+    got, want = run_both(ops, real_ref, st, rs, 0, 1000, [0.0, 1.0], dt=dt, name=name)
+    np.testing.assert_array_equal(got, want)
+
+
+def test_truncated_normal_is_refused_with_a_reason(ops, pair):
+    st, _, _ = pair
+    zi = S.shape_info([1, 64])
+    dz = torch.zeros(64, device="cuda")
+    with pytest.raises(RuntimeError, match="TruncatedNormal"):
+        ops.execRandomFloat(None, 11, st, dz, zi, dz, zi, dz, zi, torch.tensor([0.0, 1.0], device="cuda"))
