@@ -41,6 +41,10 @@ struct float16 {
                                   Nd4jLong yStride, T *result, Nd4jLong resultStride, T *extraParams, Nd4jLong n);  \
     void execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong *xShapeInfo, T *y,         \
                                   Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfo, T *extraParams);      \
+    /* nd4jb200_exec_pairwise_indexed (NativeOps.h:167-178, 715-754): index arrays live on the device */          \
+    void execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong *xShapeInfo, T *y,         \
+                                  Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfo, T *extraParams,       \
+                                  Nd4jLong *xIndexes, Nd4jLong *yIndexes, Nd4jLong *resultIndexes);                 \
     /* nd4jb200_exec_reduce / nd4jb200_exec_reduce_scalar (NativeOps.h:809-906) */                                  \
     void execReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParams,           \
                        T *result, Nd4jLong *resultShapeInfo);                                                       \
@@ -104,6 +108,16 @@ public:
                         Nd4jLong resultStride, float scalar, float16 *extraParams, Nd4jLong n);
     void execScalarHalf(Nd4jPointer *extraPointers, int opNum, float16 *x, Nd4jLong *xShapeInfo, float16 *result,
                         Nd4jLong *resultShapeInfo, float scalar, float16 *extraParams);
+    /* nd4jb200_exec_scalar_indexed (NativeOps.h:1132-1141 and the Double / Half twins) */
+    void execScalarDouble(Nd4jPointer *extraPointers, int opNum, double *x, Nd4jLong *xShapeInfo, double *result,
+                          Nd4jLong *resultShapeInfo, double scalar, double *extraParams, Nd4jLong *xIndexes,
+                          Nd4jLong *resultIndexes);
+    void execScalarFloat(Nd4jPointer *extraPointers, int opNum, float *x, Nd4jLong *xShapeInfo, float *result,
+                         Nd4jLong *resultShapeInfo, float scalar, float *extraParams, Nd4jLong *xIndexes,
+                         Nd4jLong *resultIndexes);
+    void execScalarHalf(Nd4jPointer *extraPointers, int opNum, float16 *x, Nd4jLong *xShapeInfo, float16 *result,
+                        Nd4jLong *resultShapeInfo, float scalar, float16 *extraParams, Nd4jLong *xIndexes,
+                        Nd4jLong *resultIndexes);
 
     /* nd4jb200_init_random and friends (NativeOps.h:2510-2539). extraPointers[0] = host table,
      * [1] = stream, ptrToBuffer = device table (blas/cuda/NativeOps.cu:5384-5391). */

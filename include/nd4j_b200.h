@@ -116,6 +116,12 @@ int nd4jb200_exec_transform_strided(void *stream, int dtype, int opNum, const vo
 int nd4jb200_exec_pairwise(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                            const void *y, const Nd4jLong *yShapeInfo, void *z, const Nd4jLong *zShapeInfo,
                            const void *extraParams);
+/* indexed overloads: z[zIndexes[i]] = op(x[xIndexes[i]], y[yIndexes[i]]) for i < length(x); the index arrays
+ * are DEVICE arrays of element offsets (NativeOps::execPairwiseTransform* with xIndexes/yIndexes/resultIndexes,
+ * blas/NativeOps.h:167-178, 715-754; include/loops/pairwise_transform.h:136-152) */
+int nd4jb200_exec_pairwise_indexed(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                                   const void *y, void *z, const void *extraParams, const Nd4jLong *xIndexes,
+                                   const Nd4jLong *yIndexes, const Nd4jLong *zIndexes);
 int nd4jb200_exec_pairwise_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
                                    const void *y, Nd4jLong yStride, void *z, Nd4jLong zStride,
                                    const void *extraParams, Nd4jLong n);
@@ -130,6 +136,11 @@ int nd4jb200_exec_broadcast(void *stream, int dtype, int opNum, const void *x, c
  *      (blas/NativeOps.h:1046-1214; blas/cuda/NativeOps.cu:2642-2816, 5135-5190) ------------ */
 int nd4jb200_exec_scalar(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                          void *z, const Nd4jLong *zShapeInfo, double scalar, const void *extraParams);
+/* z[zIndexes[i]] = op(x[xIndexes[i]], scalar) (NativeOps::execScalar* with xIndexes/resultIndexes,
+ * blas/NativeOps.h:1132-1141; include/loops/cpu/scalar.cpp:118-131) */
+int nd4jb200_exec_scalar_indexed(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo, void *z,
+                                 double scalar, const void *extraParams, const Nd4jLong *xIndexes,
+                                 const Nd4jLong *zIndexes);
 int nd4jb200_exec_scalar_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
                                  void *z, Nd4jLong zStride, double scalar, const void *extraParams, Nd4jLong n);
 int nd4jb200_exec_scalar_along_dimension(void *stream, int dtype, int opNum, const void *x,

@@ -448,6 +448,38 @@ int nd4jb200_exec_pairwise(void *stream, int dtype, int opNum, const void *x, co
     return BY_DTYPE(dtype, pairwise, opNum, a, as_stream(stream));
 }
 
+int nd4jb200_exec_pairwise_indexed(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
+                                   const void *y, void *z, const void *extraParams, const Nd4jLong *xIndexes,
+                                   const Nd4jLong *yIndexes, const Nd4jLong *zIndexes) {
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(y, "y")); ND_TRY(need(z, "z"));
+    ND_TRY(need(xIndexes, "xIndexes")); ND_TRY(need(yIndexes, "yIndexes")); ND_TRY(need(zIndexes, "resultIndexes"));
+    ShapeDesc xd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    EwArgs a;
+    a.x = x; a.y = y; a.z = z; a.extra = extraParams; a.n = xd.length; a.scalar = 0;
+    a.mode = 3; a.sx = a.sy = a.sz = 0;
+    a.vx.rank = a.vy.rank = a.vz.rank = 0;
+    a.ix = xIndexes; a.iy = yIndexes; a.iz = zIndexes;
+    return BY_DTYPE(dtype, pairwise, opNum, a, as_stream(stream));
+}
+
+int nd4jb200_exec_scalar_indexed(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo, void *z,
+                                 double scalar, const void *extraParams, const Nd4jLong *xIndexes,
+                                 const Nd4jLong *zIndexes) {
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(z, "z"));
+    ND_TRY(need(xIndexes, "xIndexes")); ND_TRY(need(zIndexes, "resultIndexes"));
+    ShapeDesc xd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    EwArgs a;
+    a.x = x; a.y = nullptr; a.z = z; a.extra = extraParams; a.n = xd.length; a.scalar = scalar;
+    a.mode = 3; a.sx = a.sy = a.sz = 0;
+    a.vx.rank = a.vy.rank = a.vz.rank = 0;
+    a.ix = xIndexes; a.iy = nullptr; a.iz = zIndexes;
+    return BY_DTYPE(dtype, scalar, opNum, a, as_stream(stream));
+}
+
 int nd4jb200_exec_pairwise_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride, const void *y,
                                    Nd4jLong yStride, void *z, Nd4jLong zStride, const void *extraParams, Nd4jLong n) {
     ND_TRY(check_dtype(dtype));

@@ -7,6 +7,8 @@
 //            four packs in flight per thread, grid sized to a multiple of the SM count.
 //   strided  every operand walks linearly with its own element stride (ews path of the reference).
 //   views    general rank-N strided operands: linear c-order index -> per-operand offset.
+//   indexed  element i of every operand sits at an offset read from that operand's index array
+//            (the xIndexes / yIndexes / resultIndexes overloads): a gather / scatter.
 // In-place calls (z aliasing x or y) are legal: each element is read and written by the same
 // thread and inputs are fetched with ordinary (coherent) loads.
 #pragma once
@@ -22,9 +24,10 @@ struct EwArgs {
     const void *extra;
     LL n;
     double scalar;
-    int mode;          // 0 dense, 1 strided, 2 views
+    int mode;          // 0 dense, 1 strided, 2 views, 3 indexed
     LL sx, sy, sz;
     View vx, vy, vz;
+    const LL *ix = nullptr, *iy = nullptr, *iz = nullptr;   // indexed: device arrays of n offsets per operand
 };
 
 constexpr int kEwBlock = 256;
@@ -86,6 +89,7 @@ __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
         for (LL i = tid; i < a.n; i += nthreads) {
             LL ox, oy = 0, oz;
             if (a.mode == 1) { ox = i * a.sx; oz = i * a.sz; if (ARITY == 2) oy = i * a.sy; }
+            else if (a.mode == 3) { ox = __ldg(a.ix + i); oz = __ldg(a.iz + i); if (ARITY == 2) oy = __ldg(a.iy + i); }
             else {
                 ox = view_offset(a.vx, i); oz = view_offset(a.vz, i);
                 if (ARITY == 2) oy = view_offset(a.vy, i);

@@ -106,6 +106,12 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
         check(nd4jb200_exec_pairwise(STREAM, TypeCode<T>::v, opNum, dx, X_INFO, y, Y_INFO, result,                    \
                                      Z_INFO(resultShapeInfo), extraParams), "execPairwiseTransform" #S);               \
     }                                                                                                                  \
+    void NativeOps::execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong *xShapeInfo,      \
+                                             T *y, Nd4jLong *, T *result, Nd4jLong *, T *extraParams,                 \
+                                             Nd4jLong *xIndexes, Nd4jLong *yIndexes, Nd4jLong *resultIndexes) {       \
+        check(nd4jb200_exec_pairwise_indexed(STREAM, TypeCode<T>::v, opNum, dx, X_INFO, y, result, extraParams,       \
+                                             xIndexes, yIndexes, resultIndexes), "execPairwiseTransform" #S);          \
+    }                                                                                                                  \
     void NativeOps::execReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParams,  \
                                   T *result, Nd4jLong *resultShapeInfo) {                                             \
         check(nd4jb200_exec_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,                     \
@@ -222,6 +228,12 @@ ND4JB200_DEFINE_FAMILIES(float16, Half, float)
                                   Nd4jLong *resultShapeInfo, ST scalar, T *extraParams) {                             \
         check(nd4jb200_exec_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, result, Z_INFO(resultShapeInfo),         \
                                    (double) scalar, extraParams), "execScalar" #S);                                    \
+    }                                                                                                                  \
+    void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *result,       \
+                                  Nd4jLong *, ST scalar, T *extraParams, Nd4jLong *xIndexes,                          \
+                                  Nd4jLong *resultIndexes) {                                                          \
+        check(nd4jb200_exec_scalar_indexed(STREAM, TypeCode<T>::v, opNum, x, X_INFO, result, (double) scalar,         \
+                                           extraParams, xIndexes, resultIndexes), "execScalar" #S);                    \
     }
 ND4JB200_DEFINE_SCALAR(double, Double, double)
 ND4JB200_DEFINE_SCALAR(float, Float, float)

@@ -87,6 +87,8 @@ def load_library(path=None):
         "nd4jb200_exec_transform_strided": (i, [vp, i, i, vp, ll, vp, ll, vp, ll]),
         "nd4jb200_exec_pairwise": (i, [vp, i, i, vp, llp, vp, llp, vp, llp, vp]),
         "nd4jb200_exec_pairwise_strided": (i, [vp, i, i, vp, ll, vp, ll, vp, ll, vp, ll]),
+        "nd4jb200_exec_pairwise_indexed": (i, [vp, i, i, vp, llp, vp, vp, vp, vp, vp, vp]),
+        "nd4jb200_exec_scalar_indexed": (i, [vp, i, i, vp, llp, vp, d, vp, vp, vp]),
         "nd4jb200_exec_broadcast": (i, [vp, i, i, vp, llp, vp, llp, vp, llp, ip, i]),
         "nd4jb200_exec_scalar": (i, [vp, i, i, vp, llp, vp, llp, d, vp]),
         "nd4jb200_exec_scalar_strided": (i, [vp, i, i, vp, ll, vp, ll, d, vp, ll]),
@@ -256,8 +258,17 @@ class NativeOps:
         self._check(self.lib.nd4jb200_exec_transform(st, dt, opNum, _ptr(dx), xsp, _ptr(result), zsp, _ptr(extraParams)))
 
     def _execPairwiseTransform(self, dt, extraPointers, opNum, dx, xShapeInfo, y, yShapeInfo, result, resultShapeInfo,
-                               extraParams, n=None):
+                               extraParams, n=None, yIndexes=None, resultIndexes=None):
+        """Three overloads, as in the reference: shaped (nine arguments), strided (`n` = element count, the
+        three shapeInfo slots carry strides) and indexed (`n`, `yIndexes`, `resultIndexes` carry the device
+        index arrays xIndexes, yIndexes, resultIndexes)."""
         st = self._stream(extraPointers)
+        if yIndexes is not None:  # indexed overload
+            xs, xsp = _longs(xShapeInfo)
+            self._check(self.lib.nd4jb200_exec_pairwise_indexed(st, dt, opNum, _ptr(dx), xsp, _ptr(y), _ptr(result),
+                                                                _ptr(extraParams), _ptr(n), _ptr(yIndexes),
+                                                                _ptr(resultIndexes)))
+            return
         if n is not None:  # strided overload
             self._check(self.lib.nd4jb200_exec_pairwise_strided(st, dt, opNum, _ptr(dx), int(xShapeInfo), _ptr(y),
                                                                 int(yShapeInfo), _ptr(result), int(resultShapeInfo),
@@ -279,8 +290,15 @@ class NativeOps:
                                                      _ptr(result), zsp, dmp, dimensionLength))
 
     def _execScalar(self, dt, extraPointers, opNum, x, xShapeInfo, result, resultShapeInfo, scalar, extraParams,
-                    n=None):
+                    n=None, resultIndexes=None):
+        """Shaped, strided (`n` = element count) and indexed (`n`, `resultIndexes` carry the device index
+        arrays xIndexes, resultIndexes) overloads."""
         st = self._stream(extraPointers)
+        if resultIndexes is not None:  # indexed overload
+            xs, xsp = _longs(xShapeInfo)
+            self._check(self.lib.nd4jb200_exec_scalar_indexed(st, dt, opNum, _ptr(x), xsp, _ptr(result), float(scalar),
+                                                              _ptr(extraParams), _ptr(n), _ptr(resultIndexes)))
+            return
         if n is not None:  # strided overload
             self._check(self.lib.nd4jb200_exec_scalar_strided(st, dt, opNum, _ptr(x), int(xShapeInfo), _ptr(result),
                                                               int(resultShapeInfo), float(scalar), _ptr(extraParams),

@@ -342,3 +342,40 @@ def test_errors_are_reported_not_fatal(ops):
     # the context is still usable
     ops.execTransformFloat(None, 26, x, info, x, info, None)
     assert host(x).sum() == 16
+
+
+# ---- indexed overloads ----------------------------------------------------------------------------
+@pytest.mark.parametrize("op", [0, 1, 6, 13])
+def test_pairwise_indexed_gather_scatter(ops, op):
+    """z[zIdx[i]] = op(x[xIdx[i]], y[yIdx[i]]) (include/loops/pairwise_transform.h:136-152): checked against the
+    reference's shaped call on the gathered operands, since the indexed loop applies the same functor."""
+    rng = np.random.default_rng(op)
+    n, span = 5000, 12000
+    x, y = rng.standard_normal(span).astype(np.float32), rng.standard_normal(span).astype(np.float32) + 3
+    xi_, yi_ = rng.integers(0, span, n), rng.integers(0, span, n)
+    zi_ = rng.permutation(span)[:n]
+    z = np.full(span, -7, np.float32)
+    dz = dev(z)
+    info = S.shape_info([1, n])
+    ops.execPairwiseTransformFloat(None, op, dev(x), info, dev(y), info, dz, info, None,
+                                   dev(xi_.astype(np.int64)), dev(yi_.astype(np.int64)), dev(zi_.astype(np.int64)))
+    dense = torch.zeros(n, device="cuda")
+    ops.execPairwiseTransformFloat(None, op, dev(x[xi_]), info, dev(y[yi_]), info, dense, info, None)
+    want = z.copy()
+    want[zi_] = host(dense)
+    np.testing.assert_array_equal(host(dz), want)
+
+
+def test_scalar_indexed(ops):
+    rng = np.random.default_rng(3)
+    n, span = 3000, 9000
+    x = rng.standard_normal(span).astype(np.float32)
+    xi_ = rng.integers(0, span, n)
+    zi_ = rng.permutation(span)[:n]
+    z = np.zeros(span, np.float32)
+    dz = dev(z)
+    info = S.shape_info([1, n])
+    ops.execScalarFloat(None, 2, dev(x), info, dz, info, 1.5, None, dev(xi_.astype(np.int64)), dev(zi_.astype(np.int64)))
+    want = z.copy()
+    want[zi_] = x[xi_] * np.float32(1.5)
+    np.testing.assert_array_equal(host(dz), want)
