@@ -405,6 +405,24 @@ int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, c
     ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
     ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
     if (xd.length != zd.length) return bad_arg("transform: x and z hold different numbers of elements");
+    if (opNum == 38 || opNum == 39 || opNum == 40) {
+        // SoftMax / SoftMaxDerivative / LogSoftMax: row-wise on matrices, whole-array on vectors; other
+        // ranks are left untouched by the reference (include/ops/special_ops.h:1484-1570, 1640-1730, 1808-1940)
+        if (xd.rank != 2 || zd.rank != 2) return unsupported("the softmax family is defined for matrices and vectors (rank 2)");
+        for (int i = 0; i < 2; i++) if (xd.shape[i] != zd.shape[i]) return bad_arg("softmax: x and z differ in shape");
+        SoftmaxArgs sa;
+        sa.x = x; sa.z = z;
+        const bool vector = xd.shape[0] == 1 || xd.shape[1] == 1;
+        if (vector) {
+            const int ax = xd.shape[0] == 1 ? 1 : 0;
+            sa.rows = 1; sa.cols = xd.length;
+            sa.xRow = 0; sa.zRow = 0; sa.xCol = xd.stride[ax]; sa.zCol = zd.stride[ax];
+        } else {
+            sa.rows = xd.shape[0]; sa.cols = xd.shape[1];
+            sa.xRow = xd.stride[0]; sa.xCol = xd.stride[1]; sa.zRow = zd.stride[0]; sa.zCol = zd.stride[1];
+        }
+        return BY_DTYPE(dtype, softmax, opNum - 38, sa, as_stream(stream));
+    }
     EwArgs a;
     a.x = x; a.y = nullptr; a.z = z; a.extra = extraParams; a.n = xd.length; a.scalar = 0;
     ND_TRY(setup_linear(&xd, nullptr, &zd, x, nullptr, z, &a));

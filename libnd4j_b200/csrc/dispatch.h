@@ -5,6 +5,7 @@
 #include "reduce_launch.cuh"
 #include "rng_engine.cuh"
 #include "reduce3_all.cuh"
+#include "softmax.cuh"
 
 namespace nd4jb200 {
 
@@ -17,6 +18,7 @@ namespace nd4jb200 {
     Status reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);                \
     Status reduce3_##S(int opNum, const ReduceCall &c, cudaStream_t st);               \
     Status reduce3_all_##S(int opNum, const ReduceCall &c, cudaStream_t st);           \
+    Status softmax_##S(int kind, const SoftmaxArgs &a, cudaStream_t st);               \
     Status index_reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);          \
     Status summary_stats_##S(int opNum, const ReduceCall &c, cudaStream_t st);         \
     Status random_##S(int opNum, int arity, const RngArgs &a, cudaStream_t st);

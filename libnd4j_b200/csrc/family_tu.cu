@@ -2,7 +2,7 @@
 // opNum of the reference's table and exposes a switch-based dispatcher.
 //   ND_DTYPE:  0 float, 1 double, 2 half
 //   ND_FAMILY: 0 transform, 1 binary (pairwise, scalar, broadcast, scalar-along-dimension),
-//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random, 5 reduce3 over all TAD pairs
+//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random, 5 composites (reduce3 over all TAD pairs, row softmax family)
 #include "dispatch.h"
 #include "functors.cuh"
 #include "policies.cuh"
@@ -28,7 +28,7 @@ Status ND_S(transform)(int opNum, const EwArgs &a, cudaStream_t st) {
 #define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 1>(a, st);
         ND_TRANSFORM_TABLE(X)
 #undef X
-        case 36: case 37: case 38: case 39: case 40: case 41: case 48: case 70: case 71:
+        case 36: case 37: case 41: case 48: case 70: case 71:
             return unsupported("transform opNum " + std::to_string(opNum) +
                                " is a composite (special) transform, not an elementwise functor");
         case 43: case 44:
@@ -125,6 +125,12 @@ Status ND_S(reduce3_all)(int opNum, const ReduceCall &c, cudaStream_t st) {
         case 7: return run_reduce3_all<ND_T, pol::Reduce3<7, CT> >(c, st);
         default: return unknown_op("reduce3", opNum);
     }
+}
+// kind: 0 SoftMax, 1 SoftMaxDerivative, 2 LogSoftMax
+Status ND_S(softmax)(int kind, const SoftmaxArgs &a, cudaStream_t st) {
+    if (kind == 0) return run_softmax<ND_T, 0>(a, st);
+    if (kind == 1) return run_softmax<ND_T, 1>(a, st);
+    return run_softmax<ND_T, 2>(a, st);
 }
 #elif ND_FAMILY == 4
 // Dense launches give every CTA one contiguous chunk of indices (a multiple of `quantum`), enough

@@ -334,7 +334,7 @@ def test_errors_are_reported_not_fatal(ops):
         ops.execTransformFloat(None, 57, x, info, x, info, None)   # hole in the transform table
     assert e.value.code == 2
     with pytest.raises(Nd4jError) as e:
-        ops.execTransformFloat(None, 38, x, info, x, info, None)   # SoftMax: composite, not served
+        ops.execTransformFloat(None, 41, x, info, x, info, None)   # IsMax: composite, not served
     assert e.value.code == 3
     with pytest.raises(Nd4jError) as e:
         ops.execPairwiseTransformFloat(None, 0, x, info, x, S.shape_info([3, 3]), x, info, None)
@@ -379,3 +379,68 @@ def test_scalar_indexed(ops):
     want = z.copy()
     want[zi_] = x[xi_] * np.float32(1.5)
     np.testing.assert_array_equal(host(dz), want)
+
+
+# ---- row softmax family (special transforms 38, 39, 40) -------------------------------------------
+def _softmax_truth(op, x):
+    x = x.astype(np.float64)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    y = e / e.sum(axis=1, keepdims=True)
+    with np.errstate(divide="ignore"):
+        return y if op == 38 else (y * (1 - y) if op == 39 else np.log(y))
+
+
+@pytest.mark.parametrize("op", [38, 39, 40])
+@pytest.mark.parametrize("shape", [(64, 10), (300, 1000), (7, 3000), (1, 777), (513, 1)])
+@pytest.mark.parametrize("dt,name,tol", [(np.float32, "Float", 1e-5), (np.float64, "Double", 1e-12), (np.float16, "Half", 1e-2)])
+def test_softmax_family_rows(ops, real_ref, op, shape, dt, name, tol):
+    """Fused row softmax against the reference's composite (include/ops/special_ops.h:1484-1940). The
+    derivative is called in place: out of place the reference subtracts the row maximum from the
+    result buffer's previous content instead of x (special_ops.h:1826)."""
+    rng = np.random.default_rng(op + shape[1])
+    x = (rng.standard_normal(shape) * 3).astype(dt)
+    info = S.shape_info(shape)
+    want = x.copy().ravel()
+    real_ref.transform(op, want, info, want, info)
+    if op == 39:
+        dz = dev(x)
+        getattr(ops, "execTransform" + name)(None, op, dz, info, dz, info, None)
+    else:
+        dz = dev(np.zeros(x.size, dt))
+        getattr(ops, "execTransform" + name)(None, op, dev(x), info, dz, info, None)
+    # a column vector is one "row" of its whole length, like a row vector
+    truth = _softmax_truth(op, x.reshape(1, -1) if 1 in shape else x).reshape(shape)
+    got = host(dz).astype(np.float64).reshape(shape)
+    ref = want.astype(np.float64).reshape(shape)
+    finite = np.isfinite(truth) & np.isfinite(ref)
+    scale = np.maximum(np.abs(truth), 1e-30 if op != 40 else 1.0)
+    bound = np.maximum(tol * scale, np.abs(ref - truth) * 1.0000001)
+    if dt == np.float16:
+        # x - max is stored as a half before Exp reads it (spacing 2^-6 at magnitude 16..32), which alone
+        # moves a probability by up to 0.8 %; the stored probability adds half an ulp (or the 6e-8 quantum)
+        bound = np.maximum(bound, 3e-2 * scale + (1.2e-7 if op != 40 else 0.0))
+        # probabilities near half's subnormal quantum (6e-8) round to different neighbours, or to
+        # zero, depending on the last bits of the row sum: those elements only have to be tiny
+        y = _softmax_truth(38, x.reshape(1, -1) if 1 in shape else x).reshape(shape)
+        tiny = y < 2e-6
+        finite &= ~tiny
+        small = host(dz).astype(np.float64).reshape(shape)[tiny]
+        if op != 40:
+            assert (np.abs(small) <= 4e-6).all()
+        else:
+            assert (small <= np.log(4e-6)).all()
+    else:
+        assert (np.isneginf(got) == np.isneginf(ref))[~finite].all()
+    assert (np.abs(got - truth)[finite] <= bound[finite]).all()
+
+
+def test_softmax_f_order_rows(ops, real_ref):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((40, 33)).astype(np.float32)
+    lay = Layout(x, "f")
+    want = lay.buffer.copy()
+    real_ref.transform(38, want, lay.info, want, lay.info)
+    dz = dev(np.zeros_like(lay.buffer))
+    ops.execTransformFloat(None, 38, dev(lay.buffer), lay.info, dz, lay.info, None)
+    np.testing.assert_allclose(host(dz), want, rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(host(dz).reshape(33, 40).T.sum(axis=1), 1.0, rtol=1e-5)
