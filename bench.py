@@ -364,6 +364,18 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
             out[name]["Gpairops_s"] = round(4096 * 4096 * 512 / out[name]["ms"] / 1e6, 1)
             del out[name]["frac_of_measured_peak"]
     del xa_, ya_, za_
+    # fused row softmax (special transform 38): one read + one write per element; the reference runs it as
+    # max / subtract / exp / sum / divide passes (about 10 array sweeps)
+    for rows_, cols_ in ((65536, 1000), (16384, 4096)):
+        xs_m = [torch.randn(rows_, cols_, device=dev, generator=g) for _ in range(2)]
+        zs_m = torch.empty(rows_, cols_, device=dev)
+        mi = calls.longs(S.shape_info([rows_, cols_]))
+
+        def f(mi=mi, xs_m=xs_m, zs_m=zs_m):
+            k[0] = (k[0] + 1) % 2
+            calls.check(lib.nd4jb200_exec_transform(st, 0, 38, P(xs_m[k[0]]), mi, P(zs_m), mi, None))
+        record("softmax_rows_f32_%dx%d" % (rows_, cols_), 2 * rows_ * cols_ * 4, rows_ * cols_, f, iters=10)
+        del xs_m, zs_m
     # scalar family: x * 1.5 on the chain-sized array
     xs_ = torch.randn(ELEMS, device=dev, generator=g)
     zs_ = torch.empty_like(xs_)

@@ -4,12 +4,12 @@
 // The reference composes them from five to seven passes of the other families -- row max (reduce),
 // subtract (broadcast), Exp (transform), row sum (reduce), divide (broadcast), then Log or y(1-y)
 // -- each a full read and write of the matrix (special_ops.h:1490-1516). Here a row is read once,
-// kept in registers (rows up to 1024 elements: one warp per row) or re-read from L2 (longer rows:
-// one CTA per row), and written once. The arithmetic per element is the reference's:
+// kept in registers (rows up to 128 elements) or re-read from L1/L2 (a warp per row in two sweeps;
+// a CTA per row in three sweeps when there are only a few very long rows), and written once. The arithmetic per element is the reference's:
 //   e = exp(x - max);  y = e / sum(e);  SoftMax: y;  LogSoftMax: log(y);  Derivative: y * (1 - y)
-// with the Exp and Log of the transform family. Only the order of the row sum differs (a tree
-// instead of the reference's sequential / OpenMP-chunked loop), so results agree to the
-// tolerance of a sum reduction.
+// Two things differ from the reference's passes: the order of the row sum (a tree instead of its
+// sequential / OpenMP-chunked loop) and the last bits of exp (library exp, multiply by 1/sum), so
+// results agree to the tolerance of a sum reduction (1e-5 relative in float), not to 2 ulp.
 #pragma once
 #include "functors.cuh"
 #include "device_utils.cuh"
@@ -24,15 +24,21 @@ struct SoftmaxArgs {
     LL xRow, xCol, zRow, zCol;     // element strides of a row start and of a column step
 };
 
-constexpr int kSmWarpCols = 1024;  // longest row a warp keeps in registers (32 per lane)
 constexpr int kSmBlock = 256;
 
-template <class T, int KIND, class C> ND_D C softmax_finish(C e, C sum) {
-    const C y = Elem<T>::to_c(Elem<T>::from_c(e / sum));     // the quotient is stored before Log / y(1-y) read it
+// `inv` is 1 / sum, rounded once per row: e * inv is within one ulp of e / sum (the reference's own
+// build is free to make the same substitution, it is compiled with reciprocal math).
+template <class T, int KIND, class C> ND_D C softmax_finish(C e, C inv) {
+    const C y = Elem<T>::to_c(Elem<T>::from_c(e * inv));     // the quotient is stored before Log / y(1-y) read it
     if (KIND == 0) return y;
     if (KIND == 1) return y * (C(1) - y);
     return log(y);
 }
+
+// exp(x - max) with the CUDA library's expf / exp (2 / 1 ulp): a third of the instructions of the
+// correctly-rounded-class exp of the Exp transform, and far inside this family's tolerance.
+ND_D float softmax_exp(float x) { return expf(x); }
+ND_D double softmax_exp(double x) { return exp(x); }
 
 template <class C> ND_D C warp_max(C v) {
     for (int m = 16; m > 0; m >>= 1) { C o = __shfl_xor_sync(0xffffffffu, v, m); v = o > v ? o : v; }
@@ -43,12 +49,74 @@ template <class C> ND_D C warp_sum(C v) {
     return v;
 }
 
-// One warp per row, the row cached in registers: lane l holds columns l, l + 32, ...
-template <class T, int KIND>
-__global__ void __launch_bounds__(kSmBlock) k_softmax_warp(const SoftmaxArgs a) {
+// A row cached in registers by G threads (one warp, or the whole CTA), K values per thread: thread t
+// holds columns t, t + G, ...; rows of up to G * K elements are read once and written once. Max and
+// sum are reduced by shuffles inside a warp and, for G = 256, across the CTA's warps through shared
+// memory (every thread folds the eight warp results in the same order).
+template <class C> ND_D C block_combine(C v, C *slots, bool isMax) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();                    // the slots may still be read from the previous reduction
+    if (lane == 0) slots[w] = v;
+    __syncthreads();
+    C r = slots[0];
+#pragma unroll
+    for (int k = 1; k < kSmBlock / 32; k++) r = isMax ? (slots[k] > r ? slots[k] : r) : r + slots[k];
+    return r;
+}
+
+template <class T, int KIND, int G, int K>
+__global__ void __launch_bounds__(kSmBlock, 4) k_softmax_cached(const SoftmaxArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
-    constexpr int K = kSmWarpCols / 32;
+    const T *ax = static_cast<const T *>(a.x);
+    T *az = static_cast<T *>(a.z);
+    __shared__ C slots[kSmBlock / 32];
+    constexpr int kRowsPerBlock = kSmBlock / G;
+    const int t = threadIdx.x % G;
+    const int cols = (int) a.cols;       // at most G * K
+    const LL stride = (LL) gridDim.x * kRowsPerBlock;
+    // with G = 256 the row index is uniform over the CTA, so the barriers inside are reached by all
+    for (LL r = (LL) blockIdx.x * kRowsPerBlock + threadIdx.x / G; r < a.rows; r += stride) {
+        const T *xr = ax + r * a.xRow;
+        T *zr = az + r * a.zRow;
+        C v[K];
+        C mx = -ND_INF(C);
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+            const int c = t + G * k;
+            v[k] = c < cols ? Elem<T>::load(xr + c * a.xCol) : -ND_INF(C);
+            mx = v[k] > mx ? v[k] : mx;
+        }
+        mx = warp_max(mx);
+        if (G > 32) mx = block_combine(mx, slots, true);
+        C sum = C(0);
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+            const int c = t + G * k;
+            // intermediate results are stored in the element type by the reference (half rows round here)
+            v[k] = c < cols ? Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(v[k] - mx))))) : C(0);
+            sum += v[k];
+        }
+        sum = warp_sum(sum);
+        if (G > 32) sum = block_combine(sum, slots, false);
+        const C inv = C(1) / Elem<T>::to_c(Elem<T>::from_c(sum));
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+            const int c = t + G * k;
+            if (c < cols) Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(v[k], inv));
+        }
+    }
+}
+
+// One warp per row, two sweeps, nothing cached: the first sweep carries a running maximum m and the
+// sum of exp(x - m), rescaled whenever the maximum moves ("online" softmax); the second re-reads the
+// row, which the first left in L1/L2, and writes the results. Warps never wait for each other, so a
+// CTA keeps eight independent rows in flight. VEC: unit column strides and 16-byte aligned rows.
+template <class T, int KIND, bool VEC>
+__global__ void __launch_bounds__(kSmBlock) k_softmax_online(const SoftmaxArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    constexpr int V = Elem<T>::kVec;
     const T *ax = static_cast<const T *>(a.x);
     T *az = static_cast<T *>(a.z);
     const int lane = threadIdx.x & 31;
@@ -56,28 +124,50 @@ __global__ void __launch_bounds__(kSmBlock) k_softmax_warp(const SoftmaxArgs a) 
     for (LL r = (LL) blockIdx.x * (kSmBlock / 32) + (threadIdx.x >> 5); r < a.rows; r += warps) {
         const T *xr = ax + r * a.xRow;
         T *zr = az + r * a.zRow;
-        C v[K];
-        C mx = -ND_INF(C);
+        C m = -ND_INF(C), s = C(0);
+        if (VEC) {
+            for (LL c = (LL) lane * V; c < a.cols; c += 32 * V) {
+                const Pack<T> pk = load_pack_rw(xr + c);
+                C xv[V];
+                C mp = -ND_INF(C);
 #pragma unroll
-        for (int k = 0; k < K; k++) {
-            const LL c = lane + 32 * k;
-            v[k] = c < a.cols ? Elem<T>::load(xr + c * a.xCol) : -ND_INF(C);
-            mx = v[k] > mx ? v[k] : mx;
+                for (int k = 0; k < V; k++) { xv[k] = Elem<T>::to_c(pk.v[k]); mp = xv[k] > mp ? xv[k] : mp; }
+                if (mp > m) { s *= softmax_exp(m - mp); m = mp; }
+#pragma unroll
+                for (int k = 0; k < V; k++) s += softmax_exp(Elem<T>::to_c(Elem<T>::from_c(xv[k] - m)));
+            }
+        } else {
+            for (LL c = lane; c < a.cols; c += 32) {
+                const C xv = Elem<T>::load(xr + c * a.xCol);
+                if (xv > m) { s *= softmax_exp(m - xv); m = xv; }
+                s += softmax_exp(Elem<T>::to_c(Elem<T>::from_c(xv - m)));
+            }
         }
-        mx = warp_max(mx);
-        C sum = C(0);
-#pragma unroll
-        for (int k = 0; k < K; k++) {
-            const LL c = lane + 32 * k;
-            // intermediate results are stored in the element type by the reference (half rows round here)
-            v[k] = c < a.cols ? Elem<T>::to_c(Elem<T>::from_c(fn::expv(Elem<T>::to_c(Elem<T>::from_c(v[k] - mx))))) : C(0);
-            sum += v[k];
+        // butterfly over the lanes' (m, s) pairs; equal maxima (also two empty lanes at -inf) need no rescale
+        for (int off = 16; off > 0; off >>= 1) {
+            const C mo = __shfl_xor_sync(0xffffffffu, m, off), so = __shfl_xor_sync(0xffffffffu, s, off);
+            const C mn = mo > m ? mo : m;
+            const C fa = m == mn ? C(1) : softmax_exp(m - mn), fb = mo == mn ? C(1) : softmax_exp(mo - mn);
+            s = s * fa + so * fb;
+            m = mn;
         }
-        sum = Elem<T>::to_c(Elem<T>::from_c(warp_sum(sum)));
+        const C inv = C(1) / Elem<T>::to_c(Elem<T>::from_c(s));
+        if (VEC) {
+            for (LL c = (LL) lane * V; c < a.cols; c += 32 * V) {
+                const Pack<T> pk = load_pack_rw(xr + c);
+                Pack<T> o;
 #pragma unroll
-        for (int k = 0; k < K; k++) {
-            const LL c = lane + 32 * k;
-            if (c < a.cols) Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(v[k], sum));
+                for (int k = 0; k < V; k++) {
+                    const C e = Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::to_c(pk.v[k]) - m)))));
+                    o.v[k] = Elem<T>::from_c(softmax_finish<T, KIND, C>(e, inv));
+                }
+                store_pack(zr + c, o);
+            }
+        } else {
+            for (LL c = lane; c < a.cols; c += 32) {
+                const C e = Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::load(xr + c * a.xCol) - m)))));
+                Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(e, inv));
+            }
         }
     }
 }
@@ -106,17 +196,17 @@ __global__ void __launch_bounds__(kSmBlock) k_softmax_block(const SoftmaxArgs a)
         mx = bcast;
         C sum = C(0);
         for (LL c = threadIdx.x; c < a.cols; c += kSmBlock)
-            sum += Elem<T>::to_c(Elem<T>::from_c(fn::expv(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::load(xr + c * a.xCol) - mx)))));
+            sum += Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::load(xr + c * a.xCol) - mx)))));
         sum = warp_sum(sum);
         __syncthreads();
         if (lane == 0) part[w] = sum;
         __syncthreads();
         if (threadIdx.x == 0) { C s = part[0]; for (int k = 1; k < kSmBlock / 32; k++) s += part[k]; bcast = Elem<T>::to_c(Elem<T>::from_c(s)); }
         __syncthreads();
-        sum = bcast;
+        const C inv = C(1) / bcast;
         for (LL c = threadIdx.x; c < a.cols; c += kSmBlock) {
-            const C e = Elem<T>::to_c(Elem<T>::from_c(fn::expv(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::load(xr + c * a.xCol) - mx)))));
-            Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(e, sum));
+            const C e = Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(Elem<T>::load(xr + c * a.xCol) - mx)))));
+            Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(e, inv));
         }
         __syncthreads();
     }
@@ -125,14 +215,20 @@ __global__ void __launch_bounds__(kSmBlock) k_softmax_block(const SoftmaxArgs a)
 template <class T, int KIND>
 Status run_softmax(const SoftmaxArgs &a, cudaStream_t stream) {
     if (a.rows <= 0 || a.cols <= 0) return kOk;
-    if (a.cols <= kSmWarpCols) {
+    const LL cap = (LL) kNumSMs * 16;
+    constexpr int V = Elem<T>::kVec;
+    if (a.cols <= 128 || a.rows >= (LL) kNumSMs * 8 || a.cols <= 8192) {
+        // a warp per row: short rows cached in registers, the rest in two sweeps
         LL blocks = ceil_div(a.rows, kSmBlock / 32);
-        const LL cap = (LL) kNumSMs * 16;
         if (blocks > cap) blocks = cap;
-        launch_kernel(k_softmax_warp<T, KIND>, dim3((unsigned) blocks), dim3(kSmBlock), stream, a);
+        const dim3 grid((unsigned) blocks), block(kSmBlock);
+        const bool vec = a.xCol == 1 && a.zCol == 1 && a.cols % V == 0 && a.xRow % V == 0 && a.zRow % V == 0 &&
+                         aligned16(a.x) && aligned16(a.z);
+        if (a.cols <= 128) launch_kernel(k_softmax_cached<T, KIND, 32, 4>, grid, block, stream, a);
+        else if (vec) launch_kernel(k_softmax_online<T, KIND, true>, grid, block, stream, a);
+        else launch_kernel(k_softmax_online<T, KIND, false>, grid, block, stream, a);
     } else {
         LL blocks = a.rows;
-        const LL cap = (LL) kNumSMs * 8;
         if (blocks > cap) blocks = cap;
         launch_kernel(k_softmax_block<T, KIND>, dim3((unsigned) blocks), dim3(kSmBlock), stream, a);
     }
