@@ -47,6 +47,13 @@ def cases():
         yield "reduce3/%d" % op, dict(fam="reduce3", op=op, seed=8000 + op, shape=(10, 64), dims=[1])
     seq = [(0, 0, [0.0, 1.0]), (6, 2, [0.0, 1.0]), (7, 0, [0.3]), (2, 1, [0.5]), (0, 0, [-2.0, 3.0]), (1, 1, [0.8])]
     yield "random/sequence", dict(fam="random", seed=119, table=100000, n=70001, calls=seq)
+    for op in (0, 1, 2, 3, 5, 6, 7):
+        yield "reduce3_all/%d" % op, dict(fam="reduce3_all", op=op, seed=9000 + op, xshape=(9, 37), yshape=(5, 37), dims=[1])
+    # families the port does not restate (port=False): held against the CUDA path only
+    for op in (38, 39, 40):
+        for shape in ((12, 10), (5, 700)):
+            yield "softmax/%d/%dx%d" % (op, shape[0], shape[1]), dict(fam="softmax", op=op, seed=9100 + op, shape=shape, port=False)
+    yield "random/special", dict(fam="random_special", seed=119, table=100000, n=3001, trials=5, choices=23, port=False)
 
 
 def _inputs(case):
@@ -109,6 +116,44 @@ def run_case(ref, case):
             else:
                 ref.random_xy(op, state, z, zi, z, zi, z, zi, ex)
             outs.append(z)
+        outs.append(np.array([ref.rng_position(state), ref.rng_generation(state)], np.float32))
+        ref.destroy_random(state)
+        return np.concatenate(outs)
+    if fam == "reduce3_all":
+        kind = "positive" if case["op"] == 6 else ("levels" if case["op"] == 7 else "normal")
+        x, y = rand_input(rng, case["xshape"], np.float32, kind), rand_input(rng, case["yshape"], np.float32, kind)
+        xi, yi = S.shape_info(case["xshape"]), S.shape_info(case["yshape"])
+        nz = case["xshape"][0] * case["yshape"][0]
+        zi = S.shape_info([case["xshape"][0], case["yshape"][0]])
+        return ref.reduce3_all(case["op"], x.ravel(), xi, y.ravel(), yi, np.zeros(nz, np.float32), zi, case["dims"])
+    if fam == "softmax":
+        x = (rand_input(rng, case["shape"], np.float32) * 3).astype(np.float32).ravel()
+        info = S.shape_info(case["shape"])
+        z = x.copy()                      # in place: the derivative is only well defined that way in the reference
+        return ref.transform(case["op"], z, info, z, info)
+    if fam == "random_special":
+        # Binomial (scalar probability, then one probability per trial), BinomialEx, Choice, then a Uniform call
+        # whose values show that the state advanced as in the reference
+        state, _ = ref.init_random(case["seed"], case["table"])
+        n, trials, k = case["n"], case["trials"], case["choices"]
+        zi, ti, ki = S.shape_info([1, n]), S.shape_info([1, trials]), S.shape_info([1, k])
+        ex = np.array([trials, 0.4], np.float32)
+        outs = []
+        z = np.zeros(n, np.float32)
+        outs.append(ref.random_xy(8, state, z, zi, z, zi, z, zi, ex).copy())
+        probs = rng.uniform(0.1, 0.9, trials).astype(np.float32)
+        z = np.zeros(n, np.float32)
+        outs.append(ref.random_xy(8, state, z, zi, probs, ti, z, zi, ex).copy())
+        pe = rng.uniform(0.0, 1.0, n).astype(np.float32)
+        z = np.zeros(n, np.float32)
+        outs.append(ref.random_xy(9, state, z, zi, pe, zi, z, zi, ex).copy())
+        values = rng.standard_normal(k).astype(np.float32)
+        pk = rng.uniform(0.0, 1.0, k)
+        pk = (pk / pk.sum()).astype(np.float32)
+        z = np.zeros(n, np.float32)
+        outs.append(ref.random_xy(5, state, values, ki, pk, ki, z, zi, np.array([1.0], np.float32)).copy())
+        z = np.zeros(n, np.float32)
+        outs.append(ref.random(0, state, z, zi, np.array([0.0, 1.0], np.float32)).copy())
         outs.append(np.array([ref.rng_position(state), ref.rng_generation(state)], np.float32))
         ref.destroy_random(state)
         return np.concatenate(outs)
