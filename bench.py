@@ -376,6 +376,33 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
             calls.check(lib.nd4jb200_exec_transform(st, 0, 38, P(xs_m[k[0]]), mi, P(zs_m), mi, None))
         record("softmax_rows_f32_%dx%d" % (rows_, cols_), 2 * rows_ * cols_ * 4, rows_ * cols_, f, iters=10)
         del xs_m, zs_m
+    # memory-movement utilities: pullRows of 32768 random rows out of [65536,1024] f32, concat of four
+    # [4096,4096] blocks along dimension 0, average of 8 parameter vectors of 2^24 floats
+    src_ = torch.randn(65536, 1024, device=dev, generator=g)
+    pick_ = torch.randint(0, 65536, (32768,), device=dev, generator=g, dtype=torch.int64)
+    out_ = torch.empty(32768, 1024, device=dev)
+    tinfo_, toffs_ = ops.tadOnlyShapeInfo(S.shape_info([65536, 1024]), [1], 1)
+    zinfo_, zoffs_ = ops.tadOnlyShapeInfo(S.shape_info([32768, 1024]), [1], 1)
+    toffs_d, zoffs_d = torch.from_numpy(toffs_).cuda(), torch.from_numpy(zoffs_).cuda()
+    ti_, zi_ = calls.longs(tinfo_), calls.longs(zinfo_)
+    record("pull_rows_f32_32768_of_65536x1024", 2 * 32768 * 1024 * 4, 32768 * 1024,
+           lambda: calls.check(lib.nd4jb200_pull_rows(st, 0, P(src_), P(out_), 32768, P(pick_), ti_, P(toffs_d), zi_, P(zoffs_d))))
+    del src_, out_
+    blocks_ = [torch.randn(4096, 4096, device=dev, generator=g) for _ in range(4)]
+    cat_ = torch.empty(16384, 4096, device=dev)
+    ptrs_ = (ctypes.c_void_p * 4)(*[b_.data_ptr() for b_ in blocks_])
+    binfo_ = calls.longs(S.shape_info([4096, 4096]))
+    infos_ = (ctypes.c_void_p * 4)(*[ctypes.cast(binfo_, ctypes.c_void_p).value] * 4)
+    cinfo_ = calls.longs(S.shape_info([16384, 4096]))
+    record("concat_dim0_f32_4x4096x4096", 2 * 16384 * 4096 * 4, 16384 * 4096,
+           lambda: calls.check(lib.nd4jb200_concat(st, 0, 0, 4, ptrs_, infos_, P(cat_), cinfo_)))
+    del blocks_, cat_
+    params_ = [torch.randn(1 << 24, device=dev, generator=g) for _ in range(8)]
+    avg_ = torch.empty(1 << 24, device=dev)
+    pp_ = (ctypes.c_void_p * 8)(*[p_.data_ptr() for p_ in params_])
+    record("average_f32_8x2p24", 9 * (1 << 24) * 4, 1 << 24,
+           lambda: calls.check(lib.nd4jb200_average(st, 0, pp_, P(avg_), 8, 1 << 24, 0)))
+    del params_, avg_
     # scalar family: x * 1.5 on the chain-sized array
     xs_ = torch.randn(ELEMS, device=dev, generator=g)
     zs_ = torch.empty_like(xs_)

@@ -64,6 +64,17 @@ struct float16 {
                            T *y, Nd4jLong *yInfo, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,       \
                            int dimensionLength, Nd4jLong *xTadShapeInfo, Nd4jLong *xOffsets,                        \
                            Nd4jLong *yTadShapeInfo, Nd4jLong *yOffsets);                                            \
+    /* nd4jb200_flatten / _concat / _pull_rows / _average / _accumulate (NativeOps.h:1457-1601, 1904-2037) */      \
+    void flatten##S(Nd4jPointer *extraPointers, int offset, char order, T *result, Nd4jLong *resultShapeInfo,       \
+                    T *input, Nd4jLong *inputShapeInfo);                                                            \
+    void concat##S(Nd4jPointer *extraPointers, int dimension, int numArrays, Nd4jPointer *data,                     \
+                   Nd4jPointer *inputShapeInfo, T *result, Nd4jLong *resultShapeInfo, Nd4jPointer *tadPointers,     \
+                   Nd4jPointer *offsetPointers);                                                                    \
+    void pullRows##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, T *z, Nd4jLong *zShapeInfo,            \
+                     Nd4jLong n, Nd4jLong *indexes, Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets,                   \
+                     Nd4jLong *zTadShapeInfo, Nd4jLong *zTadOffsets);                                               \
+    void average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length, bool propagate);           \
+    void accumulate##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length);                        \
     /* nd4jb200_exec_scalar_along_dimension (NativeOps.h:1160-1214) */                                              \
     void execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,                     \
                        Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension, int dimensionLength);      \

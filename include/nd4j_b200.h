@@ -188,6 +188,31 @@ int nd4jb200_tad_only_shape_info(const Nd4jLong *xShapeInfo, const int *dimensio
                                  Nd4jLong *target, Nd4jLong *offsets);
 Nd4jLong nd4jb200_tad_count(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength);
 
+/* ---- memory-movement utilities on the same boundary (blas/NativeOps.h:1457-1601, 1904-2037). Pointer
+ *      arrays (`sources`, `data`, `inputShapeInfo`) are HOST arrays; what they point to follows the usual
+ *      rule (data on the device, shapeInfo on the host). `indexes` and the TAD offset arrays of pullRows are
+ *      DEVICE arrays, as in the reference's CUDA build; the TAD shapeInfos are host arrays. ------------------ */
+/* NativeOps::flatten{Float,Double,Half}: z[offset + i * zEws] = element i of x walked in `order` ('c' / 'f')
+ * (blas/NativeOps.h:1457-1500; blas/cpu/NativeOps.cpp:1530-1700) */
+int nd4jb200_flatten(void *stream, int dtype, Nd4jLong offset, char order, void *z, const Nd4jLong *zShapeInfo,
+                     const void *x, const Nd4jLong *xShapeInfo);
+/* NativeOps::concat{Float,Double,Half}: inputs side by side along `dimension` of z
+ * (blas/NativeOps.h:1510-1555; include/ops/impl/specials.cpp concatCpuGeneric) */
+int nd4jb200_concat(void *stream, int dtype, int dimension, int numArrays, const void *const *data,
+                    const Nd4jLong *const *inputShapeInfo, void *z, const Nd4jLong *zShapeInfo);
+/* NativeOps::pullRows{Float,Double,Half}: TAD indexes[k] of x onto TAD k of z
+ * (blas/NativeOps.h:1930-1980; blas/cpu/NativeOps.cpp:2045-2104) */
+int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong n, const Nd4jLong *indexes,
+                       const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets, const Nd4jLong *zTadShapeInfo,
+                       const Nd4jLong *zTadOffsets);
+/* NativeOps::average{Float,Double,Half}: z[i] = sum_k sources[k][i] / n (z == NULL: into sources[0]); with
+ * `propagate` the result is also written over every source (blas/NativeOps.h:1996-2025;
+ * include/ops/impl/specials.cpp:374-433). At most 128 sources, all on this device or peer-mapped. */
+int nd4jb200_average(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length, int propagate);
+/* NativeOps::accumulate{Float,Double,Half}: z[i] += sum_k sources[k][i] (blas/NativeOps.h:2027-2037;
+ * include/ops/impl/specials.cpp:343-359) */
+int nd4jb200_accumulate(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length);
+
 /* ---- device / memory / stream utilities the same object offers
  *      (blas/NativeOps.h:1607-1870; blas/cuda/NativeOps.cu:3854-4260) ------------------------- */
 int nd4jb200_get_available_devices(void);

@@ -158,6 +158,34 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
                                         result, Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength), \
                                         dimensionLength), "execReduce3All" #S);                                        \
     }                                                                                                                  \
+    void NativeOps::flatten##S(Nd4jPointer *extraPointers, int offset, char order, T *result,                         \
+                               Nd4jLong *resultShapeInfo, T *input, Nd4jLong *inputShapeInfo) {                       \
+        check(nd4jb200_flatten(STREAM, TypeCode<T>::v, offset, order, result, host_info(nullptr, -1, resultShapeInfo),\
+                               input, host_info(nullptr, -1, inputShapeInfo)), "flatten" #S);                          \
+    }                                                                                                                  \
+    void NativeOps::concat##S(Nd4jPointer *extraPointers, int dimension, int numArrays, Nd4jPointer *data,            \
+                              Nd4jPointer *inputShapeInfo, T *result, Nd4jLong *resultShapeInfo, Nd4jPointer *,       \
+                              Nd4jPointer *) {                                                                        \
+        std::vector<const Nd4jLong *> infos(numArrays > 0 ? numArrays : 0);                                           \
+        for (int k = 0; k < numArrays; k++)                                                                            \
+            infos[k] = host_info(nullptr, -1, static_cast<const Nd4jLong *>(inputShapeInfo[k]));                       \
+        check(nd4jb200_concat(STREAM, TypeCode<T>::v, dimension, numArrays, data, infos.data(), result,               \
+                              host_info(nullptr, -1, resultShapeInfo)), "concat" #S);                                  \
+    }                                                                                                                  \
+    void NativeOps::pullRows##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *, T *z, Nd4jLong *, Nd4jLong n,           \
+                                Nd4jLong *indexes, Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets,                      \
+                                Nd4jLong *zTadShapeInfo, Nd4jLong *zTadOffsets) {                                     \
+        check(nd4jb200_pull_rows(STREAM, TypeCode<T>::v, x, z, n, indexes, host_info(nullptr, -1, tadShapeInfo),      \
+                                 tadOffsets, host_info(nullptr, -1, zTadShapeInfo), zTadOffsets), "pullRows" #S);      \
+    }                                                                                                                  \
+    void NativeOps::average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length,                   \
+                               bool propagate) {                                                                      \
+        check(nd4jb200_average(stream_of(extras), TypeCode<T>::v, dx, dz, n, length, propagate ? 1 : 0),              \
+              "average" #S);                                                                                           \
+    }                                                                                                                  \
+    void NativeOps::accumulate##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length) {              \
+        check(nd4jb200_accumulate(stream_of(extras), TypeCode<T>::v, dx, dz, n, length), "accumulate" #S);             \
+    }                                                                                                                  \
     void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,            \
                                   Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension,                   \
                                   int dimensionLength) {                                                              \

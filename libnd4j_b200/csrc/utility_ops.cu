@@ -1,0 +1,286 @@
+// Memory-movement utilities that sit on the same boundary as the legacy op families and share their
+// shapeInfo / TAD decoding: flatten, concat, pullRows, and the parameter-averaging pair average /
+// accumulate (NativeOps.h:1457-1601, 1904-2037). All of them are pure streams through HBM: each
+// element is read once and written once, nothing is re-laid-out on the way.
+//
+//   flatten    z[offset + i * zEws] = element i of x walked in the requested order
+//              (blas/cpu/NativeOps.cpp:1530-1700)
+//   concat     the inputs are laid side by side along one axis of z (include/ops/impl/specials.cpp,
+//              concatCpuGeneric): one strided block copy per input
+//   pullRows   TAD number indexes[k] of x is copied onto TAD k of z (blas/cpu/NativeOps.cpp:2045-2104)
+//   average    z[i] = sum_k x_k[i] / n, then (optionally) every x_k = z  (specials.cpp:374-433)
+//   accumulate z[i] += sum_k x_k[i]  (onto what z already holds)          (specials.cpp:343-359)
+//
+// Copies move raw 2-, 4- or 8-byte elements; only average / accumulate look at the values.
+#include "../../include/nd4j_b200.h"
+#include "device_utils.cuh"
+#include "runtime.h"
+#include <sstream>
+
+namespace nd4jb200 {
+namespace {
+
+template <int BYTES> struct Raw;
+template <> struct Raw<2> { typedef unsigned short T; };
+template <> struct Raw<4> { typedef unsigned int T; };
+template <> struct Raw<8> { typedef unsigned long long T; };
+
+struct CopyArgs {
+    const void *x;
+    void *z;
+    LL n;
+    int dense;        // both sides one unit-stride run, 16-byte aligned, n * size a multiple of 16
+    View vx, vz;      // otherwise: linear index -> offset on either side
+};
+
+constexpr int kCopyBlock = 256;
+
+template <int BYTES>
+__global__ void __launch_bounds__(kCopyBlock) k_copy_views(const CopyArgs a) {
+    grid_dependency_sync();
+    typedef typename Raw<BYTES>::T E;
+    const LL tid = (LL) blockIdx.x * kCopyBlock + threadIdx.x, nthreads = (LL) gridDim.x * kCopyBlock;
+    if (a.dense) {
+        const uint4 *src = static_cast<const uint4 *>(a.x);
+        uint4 *dst = static_cast<uint4 *>(a.z);
+        const LL packs = a.n * BYTES / 16;
+        LL i = tid;
+        for (; i + 3 * nthreads < packs; i += 4 * nthreads) {
+            const uint4 p0 = src[i], p1 = src[i + nthreads], p2 = src[i + 2 * nthreads], p3 = src[i + 3 * nthreads];
+            dst[i] = p0; dst[i + nthreads] = p1; dst[i + 2 * nthreads] = p2; dst[i + 3 * nthreads] = p3;
+        }
+        for (; i < packs; i += nthreads) dst[i] = src[i];
+        return;
+    }
+    const E *src = static_cast<const E *>(a.x);
+    E *dst = static_cast<E *>(a.z);
+    for (LL i = tid; i < a.n; i += nthreads) dst[view_offset(a.vz, i)] = src[view_offset(a.vx, i)];
+}
+
+Status launch_copy(int bytes, CopyArgs a, cudaStream_t stream) {
+    if (a.n <= 0) return kOk;
+    LL work = a.dense ? ceil_div(a.n * bytes / 16, 4) : a.n;
+    LL blocks = ceil_div(work, kCopyBlock);
+    const LL cap = (LL) kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (bytes == 2) launch_kernel(k_copy_views<2>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, a);
+    else if (bytes == 4) launch_kernel(k_copy_views<4>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, a);
+    else launch_kernel(k_copy_views<8>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, a);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+bool unit_run(const View &v) { return v.rank == 0 || (v.rank == 1 && v.stride[0] == 1); }
+
+Status copy_between(int bytes, const void *x, const View &vx, void *z, const View &vz, LL n, cudaStream_t stream) {
+    CopyArgs a;
+    a.x = x; a.z = z; a.n = n; a.vx = vx; a.vz = vz;
+    a.dense = unit_run(vx) && unit_run(vz) && aligned16(x) && aligned16(z) && (n * bytes) % 16 == 0;
+    return launch_copy(bytes, a, stream);
+}
+
+// f-order traversal of an array: the same view with the axes reversed
+Status forder_traversal(const ShapeDesc &d, View *out) {
+    LL shp[kMaxRank], str[kMaxRank];
+    for (int i = 0; i < d.rank; i++) { shp[i] = d.shape[d.rank - 1 - i]; str[i] = d.stride[d.rank - 1 - i]; }
+    return collapse_view(d.rank, shp, str, out);
+}
+
+inline int dtype_bytes(int dtype) { return dtype == ND4JB200_DOUBLE ? 8 : (dtype == ND4JB200_FLOAT ? 4 : 2); }
+inline Status check_dtype(int dtype) {
+    if (dtype < 0 || dtype > 2) return bad_arg("dtype must be 0 (float), 1 (double) or 2 (half)");
+    return kOk;
+}
+inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+// ---- pullRows ----------------------------------------------------------------------------------
+struct PullArgs {
+    const void *x;
+    void *z;
+    LL n, tadLen;
+    const LL *indexes, *xOffsets, *zOffsets;   // device arrays
+    View xInner, zInner;
+    int dense;        // unit-stride TADs whose bases and length keep 16-byte alignment
+};
+
+template <int BYTES>
+__global__ void __launch_bounds__(kCopyBlock) k_pull_rows(const PullArgs a) {
+    grid_dependency_sync();
+    typedef typename Raw<BYTES>::T E;
+    const E *ax = static_cast<const E *>(a.x);
+    E *az = static_cast<E *>(a.z);
+    // one CTA per pulled TAD (grid-stride): 256 threads stream the row
+    for (LL k = blockIdx.x; k < a.n; k += gridDim.x) {
+        const LL xo = __ldg(a.xOffsets + __ldg(a.indexes + k)), zo = __ldg(a.zOffsets + k);
+        const bool vec = a.dense && ((xo * BYTES) & 15) == 0 && ((zo * BYTES) & 15) == 0;
+        if (vec) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(ax + xo);
+            uint4 *dst = reinterpret_cast<uint4 *>(az + zo);
+            const LL packs = a.tadLen * BYTES / 16;
+            for (LL i = threadIdx.x; i < packs; i += kCopyBlock) dst[i] = __ldg(src + i);
+        } else {
+            for (LL i = threadIdx.x; i < a.tadLen; i += kCopyBlock)
+                az[zo + view_offset(a.zInner, i)] = ax[xo + view_offset(a.xInner, i)];
+        }
+    }
+}
+
+// ---- average / accumulate -----------------------------------------------------------------------
+constexpr int kMaxSources = 128;
+struct SumArgs {
+    const void *src[kMaxSources];
+    void *z;
+    int n;
+    LL length;
+    int average;      // divide every term by n (the reference divides before adding)
+    int propagate;    // write the result back over every source
+};
+
+template <class T>
+__global__ void __launch_bounds__(kCopyBlock) k_sum_sources(const SumArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    T *az = static_cast<T *>(a.z);
+    const C nn = C(a.n);
+    const LL nthreads = (LL) gridDim.x * kCopyBlock;
+    for (LL i = (LL) blockIdx.x * kCopyBlock + threadIdx.x; i < a.length; i += nthreads) {
+        // terms are added in source order and every intermediate is rounded to the element type,
+        // as the reference's loop over T does
+        C acc = a.average ? C(0) : Elem<T>::load(az + i);     // accumulate adds onto what z holds
+        for (int k = 0; k < a.n; k++) {
+            C v = Elem<T>::load(static_cast<const T *>(a.src[k]) + i);
+            if (a.average) v = Elem<T>::to_c(Elem<T>::from_c(v / nn));
+            acc = Elem<T>::to_c(Elem<T>::from_c(acc + v));
+        }
+        Elem<T>::store(az + i, acc);
+        if (a.propagate)
+            for (int k = 0; k < a.n; k++) Elem<T>::store(static_cast<T *>(const_cast<void *>(a.src[k])) + i, acc);
+    }
+}
+
+Status sum_sources(void *stream, int dtype, const void *const *sources, void *z, int n, LL length, bool average, bool propagate) {
+    ND_TRY(check_dtype(dtype));
+    if (!sources) return bad_arg("null source pointer array");
+    if (n < 1 || n > kMaxSources) {
+        set_error("average / accumulate take between 1 and 128 source arrays");
+        return kTooLarge;
+    }
+    if (length < 0) return bad_arg("negative length");
+    SumArgs a;
+    for (int k = 0; k < n; k++) {
+        if (!sources[k]) return bad_arg("null source array");
+        a.src[k] = sources[k];
+    }
+    // without a result array the first source receives it (specials.cpp:376-378)
+    a.z = z ? z : const_cast<void *>(sources[0]);
+    a.n = n; a.length = length; a.average = average; a.propagate = propagate;
+    if (length == 0) return kOk;
+    LL blocks = ceil_div(length, kCopyBlock);
+    const LL cap = (LL) kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    const cudaStream_t st = as_stream(stream);
+    if (dtype == ND4JB200_FLOAT) launch_kernel(k_sum_sources<float>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else if (dtype == ND4JB200_DOUBLE) launch_kernel(k_sum_sources<double>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else launch_kernel(k_sum_sources<__half>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+}  // namespace
+}  // namespace nd4jb200
+
+using namespace nd4jb200;
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int nd4jb200_flatten(void *stream, int dtype, Nd4jLong offset, char order, void *z, const Nd4jLong *zShapeInfo,
+                     const void *x, const Nd4jLong *xShapeInfo) {
+    ND_TRY(check_dtype(dtype));
+    if (!x || !z) return bad_arg("flatten: null operand");
+    if (order != 'c' && order != 'f') return bad_arg("flatten: order must be 'c' or 'f'");
+    ShapeDesc xd, zd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    if (offset < 0 || offset + xd.length > zd.length) return bad_arg("flatten: the input does not fit behind `offset` in the result");
+    if (zd.ews < 1) return unsupported("flatten: the result must be addressable by elementWiseStride");
+    View vx, vz;
+    if (order == 'c') ND_TRY(coord_view(xd, &vx)); else ND_TRY(forder_traversal(xd, &vx));
+    LL shp[1] = {xd.length}, str[1] = {zd.ews};
+    ND_TRY(collapse_view(1, shp, str, &vz));
+    const int bytes = dtype_bytes(dtype);
+    return copy_between(bytes, x, vx, static_cast<char *>(z) + offset * zd.ews * bytes, vz, xd.length, as_stream(stream));
+}
+
+int nd4jb200_concat(void *stream, int dtype, int dimension, int numArrays, const void *const *data,
+                    const Nd4jLong *const *inputShapeInfo, void *z, const Nd4jLong *zShapeInfo) {
+    ND_TRY(check_dtype(dtype));
+    if (!data || !inputShapeInfo || !z) return bad_arg("concat: null argument");
+    if (numArrays < 1) return bad_arg("concat: no inputs");
+    ShapeDesc zd;
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    if (dimension < 0) dimension += zd.rank;
+    if (dimension < 0 || dimension >= zd.rank) return bad_arg("concat: dimension out of range");
+    const int bytes = dtype_bytes(dtype);
+    LL at = 0;
+    for (int k = 0; k < numArrays; k++) {
+        ShapeDesc xd;
+        ND_TRY(parse_shape(inputShapeInfo[k], "inputShapeInfo", &xd));
+        if (!data[k]) return bad_arg("concat: null input array");
+        if (xd.rank != zd.rank) return bad_arg("concat: inputs and result differ in rank");
+        for (int d = 0; d < zd.rank; d++)
+            if (d != dimension && xd.shape[d] != zd.shape[d]) return bad_arg("concat: an input does not match the result off the concatenation axis");
+        if (at + xd.shape[dimension] > zd.shape[dimension]) return bad_arg("concat: the inputs overflow the result along the axis");
+        // the block of z this input lands in: the input's shape with z's strides
+        View vx, vz;
+        ND_TRY(coord_view(xd, &vx));
+        ND_TRY(collapse_view(zd.rank, xd.shape, zd.stride, &vz));
+        ND_TRY(copy_between(bytes, data[k], vx, static_cast<char *>(z) + at * zd.stride[dimension] * bytes, vz, xd.length,
+                            as_stream(stream)));
+        at += xd.shape[dimension];
+    }
+    if (at != zd.shape[dimension]) return bad_arg("concat: the inputs do not fill the result along the axis");
+    return kOk;
+}
+
+int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong n, const Nd4jLong *indexes,
+                       const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets, const Nd4jLong *zTadShapeInfo,
+                       const Nd4jLong *zTadOffsets) {
+    ND_TRY(check_dtype(dtype));
+    if (!x || !z || !indexes || !tadOffsets || !zTadOffsets) return bad_arg("pullRows: null argument");
+    if (n < 0) return bad_arg("pullRows: negative row count");
+    ShapeDesc xt, zt;
+    ND_TRY(parse_shape(tadShapeInfo, "tadShapeInfo", &xt));
+    ND_TRY(parse_shape(zTadShapeInfo, "zTadShapeInfo", &zt));
+    if (xt.length != zt.length) return bad_arg("pullRows: source and target TADs differ in length");
+    if (n == 0 || xt.length == 0) return kOk;
+    PullArgs a;
+    a.x = x; a.z = z; a.n = n; a.tadLen = xt.length;
+    a.indexes = indexes; a.xOffsets = tadOffsets; a.zOffsets = zTadOffsets;
+    ND_TRY(linear_view(xt, &a.xInner));
+    ND_TRY(linear_view(zt, &a.zInner));
+    const int bytes = dtype_bytes(dtype);
+    a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0 && aligned16(x) && aligned16(z);
+    LL blocks = n;
+    const LL cap = (LL) kNumSMs * 32;
+    if (blocks > cap) blocks = cap;
+    const cudaStream_t st = as_stream(stream);
+    if (bytes == 2) launch_kernel(k_pull_rows<2>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else if (bytes == 4) launch_kernel(k_pull_rows<4>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else launch_kernel(k_pull_rows<8>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+int nd4jb200_average(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length, int propagate) {
+    return sum_sources(stream, dtype, sources, z, n, length, true, propagate != 0);
+}
+
+int nd4jb200_accumulate(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length) {
+    if (!z) return bad_arg("accumulate: null result array");
+    return sum_sources(stream, dtype, sources, z, n, length, false, false);
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

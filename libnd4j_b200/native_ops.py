@@ -73,6 +73,11 @@ def load_library(path=None):
     sig = {
         "nd4jb200_last_error": (ctypes.c_char_p, []),
         "nd4jb200_launch_count": (ctypes.c_ulonglong, []),
+        "nd4jb200_flatten": (i, [vp, i, ll, ctypes.c_char, vp, llp, vp, llp]),
+        "nd4jb200_concat": (i, [vp, i, i, i, vp, vp, vp, llp]),
+        "nd4jb200_pull_rows": (i, [vp, i, vp, vp, ll, vp, llp, vp, llp, vp]),
+        "nd4jb200_average": (i, [vp, i, vp, vp, i, ll, i]),
+        "nd4jb200_accumulate": (i, [vp, i, vp, vp, i, ll]),
         "nd4jb200_set_tuning": (ctypes.c_int, [ctypes.c_int, ctypes.c_longlong]),
         "nd4jb200_exec_reduce": (i, [vp, i, i, vp, llp, vp, vp, llp, ip, i]),
         "nd4jb200_exec_reduce_scalar": (i, [vp, i, i, vp, llp, vp, dp]),
@@ -457,6 +462,38 @@ class NativeOps:
         self._check(self.lib.nd4jb200_event_elapsed_ms(_ptr(start), _ptr(stop), ctypes.byref(ms)))
         return ms.value
 
+    # ---- memory-movement utilities (generic bodies; Float / Double / Half names are bound below) ----
+    def _flatten(self, dt, extraPointers, offset, order, result, resultShapeInfo, input, inputShapeInfo):
+        zs, zsp = _longs(resultShapeInfo)
+        xs, xsp = _longs(inputShapeInfo)
+        o = order.encode() if isinstance(order, str) else order
+        self._check(self.lib.nd4jb200_flatten(self._stream(extraPointers), dt, offset, o, _ptr(result), zsp, _ptr(input), xsp))
+
+    def _concat(self, dt, extraPointers, dimension, numArrays, data, inputShapeInfo, result, resultShapeInfo,
+                tadPointers=None, offsetPointers=None):
+        """`data`: sequence of device arrays; `inputShapeInfo`: sequence of shapeInfo arrays."""
+        ptrs = (ctypes.c_void_p * numArrays)(*[_ptr(d).value for d in data])
+        keep = [_longs(s) for s in inputShapeInfo]
+        infos = (ctypes.c_void_p * numArrays)(*[ctypes.cast(k[1], ctypes.c_void_p).value for k in keep])
+        zs, zsp = _longs(resultShapeInfo)
+        self._check(self.lib.nd4jb200_concat(self._stream(extraPointers), dt, dimension, numArrays, ptrs, infos,
+                                             _ptr(result), zsp))
+
+    def _pullRows(self, dt, extraPointers, x, xShapeInfo, z, zShapeInfo, n, indexes, tadShapeInfo, tadOffsets,
+                  zTadShapeInfo, zTadOffsets):
+        ts, tsp = _longs(tadShapeInfo)
+        zts, ztsp = _longs(zTadShapeInfo)
+        self._check(self.lib.nd4jb200_pull_rows(self._stream(extraPointers), dt, _ptr(x), _ptr(z), n, _ptr(indexes), tsp,
+                                                _ptr(tadOffsets), ztsp, _ptr(zTadOffsets)))
+
+    def _average(self, dt, extras, dx, dz, n, length, propagate):
+        ptrs = (ctypes.c_void_p * n)(*[_ptr(d).value for d in dx])
+        self._check(self.lib.nd4jb200_average(self._stream(extras), dt, ptrs, _ptr(dz), n, length, 1 if propagate else 0))
+
+    def _accumulate(self, dt, extras, dx, dz, n, length):
+        ptrs = (ctypes.c_void_p * n)(*[_ptr(d).value for d in dx])
+        self._check(self.lib.nd4jb200_accumulate(self._stream(extras), dt, ptrs, _ptr(dz), n, length))
+
     def memcpyAsync(self, dst, src, size, flags, reserved=None):
         self._check(self.lib.nd4jb200_memcpy_async(_ptr(dst), _ptr(src), size, flags, _ptr(reserved)))
 
@@ -490,7 +527,8 @@ def _bind(generic, dt):
 
 for _fam in ("execReduce", "execReduceScalar", "execIndexReduce", "execIndexReduceScalar", "execSummaryStats",
              "execSummaryStatsScalar", "execReduce3", "execReduce3All", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
-             "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom"):
+             "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom", "flatten", "concat", "pullRows",
+             "average", "accumulate"):
     for _sfx, _dt in _SUFFIX.items():
         _m = _bind("_" + _fam, _dt)
         _m.__name__ = _fam + _sfx

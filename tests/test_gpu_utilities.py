@@ -1,0 +1,131 @@
+"""flatten / concat / pullRows / average / accumulate on the GPU. They move or add elements without
+any transcendental arithmetic, so the expected values are computed with numpy following the reference's
+loops (blas/cpu/NativeOps.cpp:1530-1700, 2045-2104; include/ops/impl/specials.cpp:250-433), and every
+result must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from libnd4j_b200 import shape as S
+from tests.cases import Layout
+
+pytestmark = pytest.mark.gpu
+
+NAMES = [(np.float32, "Float"), (np.float64, "Double"), (np.float16, "Half")]
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("order", ["c", "f"])
+@pytest.mark.parametrize("kind", ["c", "f", "cview2"])
+def test_flatten_orders_and_offset(ops, dt, name, order, kind):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((6, 5, 4)).astype(dt)
+    lay = Layout(x, kind)
+    total = x.size + 17
+    z = np.full(total, -1, dt)
+    dz = dev(z)
+    getattr(ops, "flatten" + name)(None, 9, order, dz, S.shape_info([1, total]), dev(lay.buffer), lay.info)
+    want = z.copy()
+    want[9:9 + x.size] = x.ravel(order="C" if order == "c" else "F")
+    np.testing.assert_array_equal(host(dz), want)
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_concat_along_each_axis(ops, dt, name, dim):
+    rng = np.random.default_rng(dim)
+    base = [3, 4, 5]
+    parts = []
+    for extent in (2, 1, 4):
+        shp = list(base)
+        shp[dim] = extent
+        parts.append(rng.standard_normal(shp).astype(dt))
+    want = np.concatenate(parts, axis=dim)
+    # inputs in mixed layouts: c-order, f-order, strided view
+    lays = [Layout(parts[0], "c"), Layout(parts[1], "f"), Layout(parts[2], "cview2")]
+    dz = dev(np.zeros(want.size, dt))
+    getattr(ops, "concat" + name)(None, dim, 3, [dev(l.buffer) for l in lays], [l.info for l in lays], dz,
+                                  S.shape_info(list(want.shape)))
+    np.testing.assert_array_equal(host(dz).reshape(want.shape), want)
+
+
+def test_concat_large_rows_takes_the_dense_path(ops):
+    a = np.arange(4096 * 256, dtype=np.float32).reshape(4096, 256)
+    b = -a[:1024]
+    dz = torch.zeros(5120 * 256, device="cuda")
+    ops.concatFloat(None, 0, 2, [dev(a), dev(b)], [S.shape_info([4096, 256]), S.shape_info([1024, 256])], dz,
+                    S.shape_info([5120, 256]))
+    np.testing.assert_array_equal(host(dz).reshape(5120, 256), np.concatenate([a, b]))
+    with pytest.raises(RuntimeError):      # the inputs do not fill the result
+        ops.concatFloat(None, 0, 1, [dev(a)], [S.shape_info([4096, 256])], dz, S.shape_info([5120, 256]))
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("kind,dim", [("c", 1), ("f", 1), ("c", 0)])
+def test_pull_rows(ops, dt, name, kind, dim):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((50, 24)).astype(dt)
+    lay = Layout(x, kind)
+    tad_info, tad_offsets = ops.tadOnlyShapeInfo(lay.info, [dim], 1)
+    picks = rng.integers(0, len(tad_offsets), 13)
+    rows = x[picks] if dim == 1 else x[:, picks].T
+    zshape = list(rows.shape)
+    zinfo = S.shape_info(zshape)
+    ztad_info, ztad_offsets = ops.tadOnlyShapeInfo(zinfo, [1], 1)
+    dz = dev(np.zeros(rows.size, dt))
+    getattr(ops, "pullRows" + name)(None, dev(lay.buffer), lay.info, dz, zinfo, len(picks), dev(picks.astype(np.int64)),
+                                    tad_info, dev(tad_offsets.astype(np.int64)), ztad_info,
+                                    dev(ztad_offsets.astype(np.int64)))
+    np.testing.assert_array_equal(host(dz).reshape(zshape), rows)
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+def test_average_and_accumulate(ops, dt, name):
+    rng = np.random.default_rng(11)
+    n, length = 5, 10007
+    xs = [rng.standard_normal(length).astype(dt) for _ in range(n)]
+
+    def seq(terms, start, divide):
+        acc = start.copy()
+        for t in terms:
+            v = (t / dt(n)).astype(dt) if divide else t
+            acc = (acc + v).astype(dt)
+        return acc
+
+    want_avg = seq(xs, np.zeros(length, dt), True)
+    dxs = [dev(x) for x in xs]
+    dz = dev(np.full(length, 3, dt))
+    getattr(ops, "average" + name)(None, dxs, dz, n, length, False)
+    got = host(dz)
+    # the reference's build may replace x / n by x * (1 / n): one ulp per term at most
+    tol = 0 if dt == np.float64 else None
+    assert np.abs(got.astype(np.float64) - want_avg.astype(np.float64)).max() <= n * np.spacing(np.abs(want_avg).max())
+    for x, d in zip(xs, dxs):
+        np.testing.assert_array_equal(host(d), x)             # sources untouched without propagate
+    getattr(ops, "average" + name)(None, dxs, dz, n, length, True)
+    for d in dxs:
+        np.testing.assert_array_equal(host(d), host(dz))       # propagated
+    # accumulate adds onto what z holds
+    dxs = [dev(x) for x in xs]
+    start = rng.standard_normal(length).astype(dt)
+    dz = dev(start)
+    getattr(ops, "accumulate" + name)(None, dxs, dz, n, length)
+    np.testing.assert_array_equal(host(dz), seq(xs, start, False))
+
+
+def test_average_into_first_source_and_limits(ops):
+    xs = [np.full(1000, v, np.float32) for v in (1.0, 2.0, 6.0)]
+    dxs = [dev(x) for x in xs]
+    ops.averageFloat(None, dxs, None, 3, 1000, True)
+    for d in dxs:
+        np.testing.assert_array_equal(host(d), np.full(1000, 3.0, np.float32))
+    with pytest.raises(RuntimeError):
+        ops.averageFloat(None, [dxs[0]] * 129, None, 129, 1000, False)
