@@ -110,17 +110,24 @@ __global__ void __launch_bounds__(kCopyBlock) k_pull_rows(const PullArgs a) {
     typedef typename Raw<BYTES>::T E;
     const E *ax = static_cast<const E *>(a.x);
     E *az = static_cast<E *>(a.z);
-    // one CTA per pulled TAD (grid-stride): 256 threads stream the row
-    for (LL k = blockIdx.x; k < a.n; k += gridDim.x) {
+    // one warp per pulled TAD (grid-stride), four 16-byte packs in flight per lane
+    const int lane = threadIdx.x & 31;
+    const LL warps = (LL) gridDim.x * (kCopyBlock / 32);
+    for (LL k = (LL) blockIdx.x * (kCopyBlock / 32) + (threadIdx.x >> 5); k < a.n; k += warps) {
         const LL xo = __ldg(a.xOffsets + __ldg(a.indexes + k)), zo = __ldg(a.zOffsets + k);
         const bool vec = a.dense && ((xo * BYTES) & 15) == 0 && ((zo * BYTES) & 15) == 0;
         if (vec) {
             const uint4 *src = reinterpret_cast<const uint4 *>(ax + xo);
             uint4 *dst = reinterpret_cast<uint4 *>(az + zo);
             const LL packs = a.tadLen * BYTES / 16;
-            for (LL i = threadIdx.x; i < packs; i += kCopyBlock) dst[i] = __ldg(src + i);
+            LL i = lane;
+            for (; i + 96 < packs; i += 128) {
+                const uint4 p0 = __ldg(src + i), p1 = __ldg(src + i + 32), p2 = __ldg(src + i + 64), p3 = __ldg(src + i + 96);
+                dst[i] = p0; dst[i + 32] = p1; dst[i + 64] = p2; dst[i + 96] = p3;
+            }
+            for (; i < packs; i += 32) dst[i] = __ldg(src + i);
         } else {
-            for (LL i = threadIdx.x; i < a.tadLen; i += kCopyBlock)
+            for (LL i = lane; i < a.tadLen; i += 32)
                 az[zo + view_offset(a.zInner, i)] = ax[xo + view_offset(a.xInner, i)];
         }
     }
@@ -137,25 +144,57 @@ struct SumArgs {
     int propagate;    // write the result back over every source
 };
 
-template <class T>
+// Terms are added in source order and every intermediate is rounded to the element type, as the
+// reference's loop over T does; x / n is taken as x * (1 / n), which is what the reference's
+// reciprocal-math build makes of it.
+template <class T> ND_D typename Elem<T>::C sum_term(const SumArgs &a, typename Elem<T>::C acc, typename Elem<T>::C v,
+                                                      typename Elem<T>::C inv) {
+    if (a.average) v = Elem<T>::to_c(Elem<T>::from_c(v * inv));
+    return Elem<T>::to_c(Elem<T>::from_c(acc + v));
+}
+
+template <class T, bool VEC>
 __global__ void __launch_bounds__(kCopyBlock) k_sum_sources(const SumArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
+    constexpr int V = Elem<T>::kVec;
     T *az = static_cast<T *>(a.z);
-    const C nn = C(a.n);
-    const LL nthreads = (LL) gridDim.x * kCopyBlock;
-    for (LL i = (LL) blockIdx.x * kCopyBlock + threadIdx.x; i < a.length; i += nthreads) {
-        // terms are added in source order and every intermediate is rounded to the element type,
-        // as the reference's loop over T does
-        C acc = a.average ? C(0) : Elem<T>::load(az + i);     // accumulate adds onto what z holds
-        for (int k = 0; k < a.n; k++) {
-            C v = Elem<T>::load(static_cast<const T *>(a.src[k]) + i);
-            if (a.average) v = Elem<T>::to_c(Elem<T>::from_c(v / nn));
-            acc = Elem<T>::to_c(Elem<T>::from_c(acc + v));
+    const C inv = C(1) / C(a.n);
+    const LL tid = (LL) blockIdx.x * kCopyBlock + threadIdx.x, nthreads = (LL) gridDim.x * kCopyBlock;
+    if (VEC) {
+        // 16-byte packs; the loads of all sources for a pack are independent of each other
+        const LL packs = a.length / V;
+        for (LL i = tid; i < packs; i += nthreads) {
+            C acc[V];
+            if (a.average) {
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = C(0);
+            } else {
+                const Pack<T> pz = load_pack_rw(az + i * V);     // accumulate adds onto what z holds
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = Elem<T>::to_c(pz.v[j]);
+            }
+#pragma unroll 4
+            for (int k = 0; k < a.n; k++) {
+                const Pack<T> p = load_pack_rw(static_cast<const T *>(a.src[k]) + i * V);
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = sum_term<T>(a, acc[j], Elem<T>::to_c(p.v[j]), inv);
+            }
+            Pack<T> o;
+#pragma unroll
+            for (int j = 0; j < V; j++) o.v[j] = Elem<T>::from_c(acc[j]);
+            store_pack(az + i * V, o);
+            if (a.propagate)
+                for (int k = 0; k < a.n; k++) store_pack(static_cast<T *>(const_cast<void *>(a.src[k])) + i * V, o);
         }
-        Elem<T>::store(az + i, acc);
+        return;
+    }
+    for (LL i = tid; i < a.length; i += nthreads) {
+        C acc = a.average ? C(0) : Elem<T>::to_c(az[i]);
+        for (int k = 0; k < a.n; k++) acc = sum_term<T>(a, acc, Elem<T>::to_c(static_cast<const T *>(a.src[k])[i]), inv);
+        az[i] = Elem<T>::from_c(acc);
         if (a.propagate)
-            for (int k = 0; k < a.n; k++) Elem<T>::store(static_cast<T *>(const_cast<void *>(a.src[k])) + i, acc);
+            for (int k = 0; k < a.n; k++) static_cast<T *>(const_cast<void *>(a.src[k]))[i] = Elem<T>::from_c(acc);
     }
 }
 
@@ -176,13 +215,24 @@ Status sum_sources(void *stream, int dtype, const void *const *sources, void *z,
     a.z = z ? z : const_cast<void *>(sources[0]);
     a.n = n; a.length = length; a.average = average; a.propagate = propagate;
     if (length == 0) return kOk;
-    LL blocks = ceil_div(length, kCopyBlock);
+    const int vlen = dtype == ND4JB200_DOUBLE ? 2 : (dtype == ND4JB200_FLOAT ? 4 : 8);
+    bool vec = length % vlen == 0 && aligned16(a.z);
+    for (int k = 0; k < n; k++) vec = vec && aligned16(a.src[k]);
+    LL blocks = ceil_div(vec ? length / vlen : length, kCopyBlock);
     const LL cap = (LL) kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     const cudaStream_t st = as_stream(stream);
-    if (dtype == ND4JB200_FLOAT) launch_kernel(k_sum_sources<float>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
-    else if (dtype == ND4JB200_DOUBLE) launch_kernel(k_sum_sources<double>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
-    else launch_kernel(k_sum_sources<__half>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    const dim3 grid((unsigned) blocks), block(kCopyBlock);
+    if (dtype == ND4JB200_FLOAT) {
+        if (vec) launch_kernel(k_sum_sources<float, true>, grid, block, st, a);
+        else launch_kernel(k_sum_sources<float, false>, grid, block, st, a);
+    } else if (dtype == ND4JB200_DOUBLE) {
+        if (vec) launch_kernel(k_sum_sources<double, true>, grid, block, st, a);
+        else launch_kernel(k_sum_sources<double, false>, grid, block, st, a);
+    } else {
+        if (vec) launch_kernel(k_sum_sources<__half, true>, grid, block, st, a);
+        else launch_kernel(k_sum_sources<__half, false>, grid, block, st, a);
+    }
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
@@ -262,8 +312,8 @@ int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong
     ND_TRY(linear_view(zt, &a.zInner));
     const int bytes = dtype_bytes(dtype);
     a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0 && aligned16(x) && aligned16(z);
-    LL blocks = n;
-    const LL cap = (LL) kNumSMs * 32;
+    LL blocks = ceil_div(n, kCopyBlock / 32);
+    const LL cap = (LL) kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     const cudaStream_t st = as_stream(stream);
     if (bytes == 2) launch_kernel(k_pull_rows<2>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
