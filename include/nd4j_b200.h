@@ -44,7 +44,9 @@ unsigned long long nd4jb200_launch_count(void);
  * along-TAD reduction kernel aims for (default 1024); key 2: most segments per TAD that are still
  * merged inside the reduction launch instead of by a separate pass (default 32); key 3: 1 (default)
  * launches kernels with programmatic stream serialisation so that a kernel's launch overlaps the
- * tail of the previous kernel on the stream, 0 launches them plainly. Results do not
+ * tail of the previous kernel on the stream, 0 launches them plainly; key 4: largest thread-block cluster
+ * (1, 2, 4 or 8, default 4) the across-TAD reduction uses to merge segments in distributed shared memory.
+ * Results do not
  * depend on these values beyond the summation order of floating-point reductions. */
 int nd4jb200_set_tuning(int key, long long value);
 

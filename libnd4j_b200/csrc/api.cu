@@ -252,7 +252,7 @@ const char *nd4jb200_last_error(void) { return last_error(); }
 unsigned long long nd4jb200_launch_count(void) { return g_launches; }
 
 int nd4jb200_set_tuning(int key, long long value) {
-    if (key < 0 || key >= kTuneCount || value < (key == kTuneOverlapLaunch ? 0 : 1) ||
+    if (key < 0 || key >= kTuneCount || value < (key == kTuneOverlapLaunch ? 0 : 1) || (key == kTuneMaxCluster && value > 8) ||
         (key == kTuneRowThreadsPerSm && value > kMaxRowThreadsPerSm)) {
         set_error("nd4jb200_set_tuning: unknown key or value out of range");
         return kBadArgument;

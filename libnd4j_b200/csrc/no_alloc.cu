@@ -119,6 +119,7 @@ extern "C" int nd4jb200_exec_reduce_scalar_noalloc(void *stream, int dtype, int 
     a.group = kBlock;
     a.splits = (int) segments;
     a.partTadStride = a.splits; a.partSplitStride = 1;
+    a.cluster = 1;
     a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;
     a.xOuterHi = plan.outer; a.yOuterHi = plan.outer;
     a.finishLen = xd.length;

@@ -29,6 +29,7 @@
 //       folds N elements with indices j0, j0 + jstep, ... (ascending) in one go;
 //   C finish(const State&, LL n, const C* p);
 #pragma once
+#include <cooperative_groups.h>
 #include "device_utils.cuh"
 
 namespace nd4jb200 {
@@ -47,7 +48,9 @@ struct ReduceArgs {
     View xOuter, xInner;
     View yOuter, yInner;
     int group;           // threads cooperating on one TAD segment (along-TAD kernel)
-    int splits;          // segments per TAD
+    int splits;          // segments per TAD whose partial states meet in global memory
+    int cluster;         // across-TAD kernel: CTAs per thread-block cluster (1 = none). gridDim.y = splits * cluster;
+                         // the segments of one cluster are merged through distributed shared memory first
     LL partTadStride;    // partial state of (TAD r, segment k) lives at partials[r * partTadStride + k * partSplitStride]
     LL partSplitStride;
     int mode;            // along-TAD: 0 = unit-stride inner + 128-bit loads, 1 = rank-1 inner, 2 = general inner view
@@ -298,12 +301,36 @@ ND_D void cols_finish(const ReduceArgs &a, const typename P::State (&s)[W], type
     const LL tlo = tile * kTile + t;
     const bool owner = t < kTile && tlo < a.colLo;
     const LL tr = hi * a.colLo + tlo;
+    State m;
+    P::init(m);
     if (owner) {
-        State m = rows[0][t];
+        m = rows[0][t];
 #pragma unroll
         for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
+    }
+    if (a.cluster > 1) {
+        // The CTAs of a cluster hold consecutive row segments of the same TAD tile. Each leaves its
+        // merged states in its own shared memory; rank 0 folds them in rank order through distributed
+        // shared memory, so these segments never travel through global memory, fences or atomics.
+        // Both cluster barriers are reached by every thread of every CTA of the cluster.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cl = cg::this_cluster();
+        __syncthreads();                       // every owner has read rows[*][t]
+        if (owner) rowsFlat[t] = m;
+        cl.sync();
+        const unsigned rank = cl.block_rank();
+        if (rank == 0 && owner) {
+            for (unsigned q = 1; q < (unsigned) a.cluster; q++) {
+                const State *remote = cl.map_shared_rank(rowsFlat, q);
+                P::merge(m, remote[t]);
+            }
+        }
+        cl.sync();                             // remote shared memory stays valid until rank 0 has read it
+        if (rank != 0) return;
+    }
+    if (owner) {
         if (a.splits == 1) az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
-        else parts[(LL) blockIdx.y * a.partSplitStride + tr] = m;
+        else parts[(LL) (blockIdx.y / a.cluster) * a.partSplitStride + tr] = m;
     }
     if (a.splits == 1 || a.counters == nullptr) return;
     // the CTA that completes this TAD tile last merges the tile's partials (nobody waits)

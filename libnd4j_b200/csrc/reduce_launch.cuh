@@ -55,7 +55,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     a.yOuter = two ? c.yPlan.outer : c.xPlan.outer;
     a.yInner = two ? c.yPlan.inner : c.xPlan.inner;
     a.finishLen = c.finishLen;
-    a.splits = 1; a.group = 32; a.mode = 2;
+    a.splits = 1; a.cluster = 1; a.group = 32; a.mode = 2;
     a.partTadStride = 1; a.partSplitStride = 1;
     a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;
     a.xOuterHi = a.xOuter; a.yOuterHi = a.yOuter;
@@ -92,11 +92,23 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         if (splits > maxSplits) splits = maxSplits;
         if (splits < 1) splits = 1;
         if (splits > 4096) splits = 4096;
-        a.splits = (int) splits;
+        // Segments of a TAD tile are grouped into thread-block clusters of 2, 4 or 8 CTAs that merge
+        // through distributed shared memory; only one partial state per cluster reaches global memory.
+        LL cluster = 1;
+        const LL maxCluster = g_tuning[kTuneMaxCluster] < 8 ? g_tuning[kTuneMaxCluster] : 8;
+        while (cluster < splits && cluster * 2 <= maxCluster && cluster * 2 <= maxSplits) cluster *= 2;
+        LL groups = ceil_div(splits, cluster);
+        while (groups > 1 && groups * cluster > maxSplits) groups--;
+        if (cluster == 1) groups = splits;
+        a.cluster = (int) cluster;
+        a.splits = (int) groups;
         a.partTadStride = 1; a.partSplitStride = a.numTads;
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) tiles));
-        dim3 grid((unsigned) tiles, (unsigned) a.splits), block(32, kColRows);
-        if (vec) launch_kernel(k_reduce_cols<T, P, W>, grid, block, stream, a);
+        dim3 grid((unsigned) tiles, (unsigned) (groups * cluster)), block(32, kColRows);
+        if (cluster > 1) {
+            if (vec) launch_kernel_clustered(k_reduce_cols<T, P, W>, grid, block, (unsigned) cluster, stream, a);
+            else launch_kernel_clustered(k_reduce_cols<T, P, 1>, grid, block, (unsigned) cluster, stream, a);
+        } else if (vec) launch_kernel(k_reduce_cols<T, P, W>, grid, block, stream, a);
         else launch_kernel(k_reduce_cols<T, P, 1>, grid, block, stream, a);
     } else {
         if (xUnit && yUnit) {

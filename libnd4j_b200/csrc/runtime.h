@@ -32,7 +32,7 @@ extern unsigned long long g_launches;
 inline void count_launch(int n = 1) { g_launches += n; }
 
 // Launch heuristics that may be overridden at run time (nd4jb200_set_tuning); defaults in runtime.cu.
-enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneCount = 4 };
+enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneMaxCluster = 4, kTuneCount = 5 };
 extern long long g_tuning[kTuneCount];
 
 // Every kernel of the library starts with grid_dependency_sync() (device_utils.cuh): it lets the
@@ -53,6 +53,28 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaS
     cfg.attrs = attr;
     cfg.numAttrs = g_tuning[kTuneOverlapLaunch] ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
+    count_launch();
+}
+
+// Same, with the CTAs of gridDim.y grouped into thread-block clusters of `clusterY` (<= 8, the portable limit).
+template <class... KArgs, class... Args>
+inline void launch_kernel_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned clusterY, cudaStream_t stream,
+                                    Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = clusterY;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_tuning[kTuneOverlapLaunch] ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     count_launch();
 }
 
