@@ -109,3 +109,39 @@ def test_whole_array_reductions_at_awkward_lengths(ops):
         info = S.shape_info([1, n])
         assert ops.execReduceScalarFloat(None, 1, dev(x), info, None) == np.float32(n + 4)   # exact up to float rounding of the result
         assert ops.execIndexReduceScalarFloat(None, 0, dev(x), info, None) == n // 2
+
+
+def test_two_streams_and_two_host_threads_do_not_share_scratch(ops):
+    """Split reductions keep partial states and arrival counters in a per-stream workspace: calls issued
+    concurrently from two host threads on two streams must not disturb each other."""
+    import threading
+    rng = np.random.default_rng(2)
+    data = [rng.integers(-4, 5, (2048, 4096)).astype(np.float32) for _ in range(2)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    results = [None, None]
+
+    def worker(k):
+        torch.cuda.set_device(0)
+        st = streams[k]
+        extra = [None, st.cuda_stream]
+        with torch.cuda.stream(st):
+            dx = dev(data[k])
+            cols = torch.zeros(4096, device="cuda")
+            out = []
+            xi = S.shape_info([2048, 4096])
+            for _ in range(30):
+                ops.execReduceFloat(extra, 1, dx, xi, None, cols, S.shape_info([1, 4096]), [0], 1)   # split across-TAD
+                total = ops.execReduceScalarFloat(extra, 1, dx, xi, None)                             # split whole-array
+                out.append((host(cols).copy(), total))
+        results[k] = out
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for k in range(2):
+        want_cols, want_total = data[k].sum(0), float(data[k].astype(np.float64).sum())
+        for cols, total in results[k]:
+            np.testing.assert_array_equal(cols, want_cols)      # small integers: exact in any order
+            assert total == want_total
