@@ -405,6 +405,69 @@ int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, c
     ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
     ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
     if (xd.length != zd.length) return bad_arg("transform: x and z hold different numbers of elements");
+    if (opNum == 41) {
+        // IsMax: extraParams = {dimensionLength, dimension...} as element-type values on the device; absent, 0 or
+        // {1, MAX_DIMENSION} mean the whole array (include/ops/special_ops.h:2199-2203)
+        if (xd.length != zd.length) return bad_arg("IsMax: x and z hold different numbers of elements");
+        int dims[kMaxRank];
+        int ndims = 0;
+        if (extraParams) {
+            unsigned char raw[8 * (kMaxRank + 1)] = {0};
+            const size_t es = dtype_size(dtype);
+            ND_CUDA(cudaMemcpyAsync(raw, extraParams, es, cudaMemcpyDeviceToHost, as_stream(stream)));
+            ND_CUDA(cudaStreamSynchronize(as_stream(stream)));
+            auto value = [&](int k) -> double {
+                if (dtype == kF64) return reinterpret_cast<double *>(raw)[k];
+                if (dtype == kF32) return reinterpret_cast<float *>(raw)[k];
+                return __half2float(reinterpret_cast<__half *>(raw)[k]);
+            };
+            ndims = (int) value(0);
+            if (ndims < 0 || ndims > xd.rank) return bad_arg("IsMax: extraParams[0] is not a valid dimension count");
+            if (ndims > 0) {
+                ND_CUDA(cudaMemcpyAsync(raw, extraParams, es * (ndims + 1), cudaMemcpyDeviceToHost, as_stream(stream)));
+                ND_CUDA(cudaStreamSynchronize(as_stream(stream)));
+                for (int k = 0; k < ndims; k++) dims[k] = (int) value(k + 1);
+                if (ndims == 1 && dims[0] == 0x7fffffff) ndims = 0;
+            }
+        }
+        ReduceCall c;
+        ND_TRY(make_tad_plan(xd, ndims ? dims : nullptr, ndims, &c.xPlan));
+        TadPlan zPlan;
+        ND_TRY(make_tad_plan(zd, ndims ? dims : nullptr, ndims, &zPlan));
+        if (zPlan.numTads != c.xPlan.numTads || zPlan.tadLen != c.xPlan.tadLen) return bad_arg("IsMax: x and z split into different TADs");
+        // TADs over several axes are scanned by the reference's raw iterator, whose order is the first TAD axis
+        // fastest whatever the array's order (special_ops.h:2383-2420): ties resolve in that order
+        if (ndims > 1) {
+            int axes[kMaxRank];
+            int n = 0;
+            for (int ax = 0; ax < xd.rank; ax++) {              // the listed axes, ascending and unique
+                bool listed = false;
+                for (int k = 0; k < ndims; k++) listed = listed || dims[k] == ax || dims[k] + xd.rank == ax;
+                if (listed) axes[n++] = ax;
+            }
+            LL shp[kMaxRank], sx[kMaxRank], sz[kMaxRank];
+            for (int k = 0; k < n; k++) {
+                const int ax = axes[n - 1 - k];                   // first listed axis last = fastest
+                shp[k] = xd.shape[ax]; sx[k] = xd.stride[ax]; sz[k] = zd.stride[ax];
+            }
+            ND_TRY(collapse_view(n, shp, sx, &c.xPlan.inner));
+            ND_TRY(collapse_view(n, shp, sz, &zPlan.inner));
+        } else if (c.xPlan.whole) {
+            // whole-array calls walk x and z by linear index, like the reference's doAll
+            if (xd.ews < 1 && xd.rank > 1) ND_TRY(coord_view(xd, &c.xPlan.inner));
+            if (zd.ews < 1 && zd.rank > 1) ND_TRY(coord_view(zd, &zPlan.inner));
+        }
+        // the positions go behind everything a split reduction may use of the workspace
+        void *ws = nullptr;
+        ND_TRY(workspace(as_stream(stream), kScalarWorkspace + dtype_size(dtype) * (size_t) c.xPlan.numTads, &ws, nullptr));
+        void *positions = static_cast<char *>(ws) + kScalarWorkspace;
+        c.x = x; c.extra = nullptr; c.z = positions; c.finishLen = c.xPlan.tadLen;
+        ND_TRY(BY_DTYPE(dtype, index_reduce, 0, c, as_stream(stream)));
+        IsMaxArgs m;
+        m.index = positions; m.z = z; m.numTads = zPlan.numTads; m.tadLen = zPlan.tadLen;
+        m.zOuter = zPlan.outer; m.zInner = zPlan.inner;
+        return BY_DTYPE(dtype, ismax_mark, m, as_stream(stream));
+    }
     if (opNum == 38 || opNum == 39 || opNum == 40) {
         // SoftMax / SoftMaxDerivative / LogSoftMax: row-wise on matrices, whole-array on vectors; other
         // ranks are left untouched by the reference (include/ops/special_ops.h:1484-1570, 1640-1730, 1808-1940)

@@ -19,6 +19,7 @@ namespace nd4jb200 {
     Status reduce3_##S(int opNum, const ReduceCall &c, cudaStream_t st);               \
     Status reduce3_all_##S(int opNum, const ReduceCall &c, cudaStream_t st);           \
     Status softmax_##S(int kind, const SoftmaxArgs &a, cudaStream_t st);               \
+    Status ismax_mark_##S(const IsMaxArgs &a, cudaStream_t st);                        \
     Status index_reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);          \
     Status summary_stats_##S(int opNum, const ReduceCall &c, cudaStream_t st);         \
     Status random_##S(int opNum, int arity, const RngArgs &a, cudaStream_t st);

@@ -28,7 +28,7 @@ Status ND_S(transform)(int opNum, const EwArgs &a, cudaStream_t st) {
 #define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 1>(a, st);
         ND_TRANSFORM_TABLE(X)
 #undef X
-        case 36: case 37: case 41: case 48: case 70: case 71:
+        case 36: case 37: case 48: case 70: case 71:
             return unsupported("transform opNum " + std::to_string(opNum) +
                                " is a composite (special) transform, not an elementwise functor");
         case 43: case 44:
@@ -132,6 +132,7 @@ Status ND_S(softmax)(int kind, const SoftmaxArgs &a, cudaStream_t st) {
     if (kind == 1) return run_softmax<ND_T, 1>(a, st);
     return run_softmax<ND_T, 2>(a, st);
 }
+Status ND_S(ismax_mark)(const IsMaxArgs &a, cudaStream_t st) { return run_ismax_mark<ND_T>(a, st); }
 #elif ND_FAMILY == 4
 // Dense launches give every CTA one contiguous chunk of indices (a multiple of `quantum`), enough
 // CTAs to fill the machine a few times over, so that the per-thread cursor set-up is amortised.

@@ -38,13 +38,14 @@ template <class C> ND_D C rel_err(C a, C b) {
 }
 
 // tanh for float with error well below one ulp, so that results stay within 2 ulp of the host
-// libm the reference calls (templatemath.h:847). |x| < 0.55: odd minimax polynomial. Otherwise
+// libm the reference calls (templatemath.h:847). |x| < 11/32: odd polynomial. Otherwise
 // |x| = k/16 + d with |d| <= 1/32, and
 //     tanh(k/16 + d) = T + (1 - T^2) tanh(d) / (1 + T tanh(d)),   T = tanh(k/16),
-// where T comes from a 139-entry table as an unevaluated float pair and the second term is at
-// most 0.03, so its rounding errors are a small fraction of an ulp of the result. Both chains are
-// straight-line code (most warps hold arguments of both kinds anyway).
-static __device__ const float4 kTanhTable[139] = {
+// where T comes from a 141-entry table (k = 6..146) as an unevaluated float pair and the second term is
+// at most 0.03 against T >= 0.36, so its rounding errors are a small fraction of an ulp of the result
+// (0.78 ulp worst case over every float below 0.75 in an emulation that also perturbs the reciprocal by
+// one ulp either way). Both chains are straight-line code (most warps hold arguments of both kinds).
+static __device__ const float4 kTanhTable[141] = {
 #include "tanh_table.inc"
 };
 ND_D float rcp_fast(float x) {
@@ -54,28 +55,27 @@ ND_D float rcp_fast(float x) {
 }
 ND_D float tanh_accurate(float x) {
     const float ax = fabsf(x);
+    // |x| < 11/32: odd polynomial x + x^3 P(x^2), P fitted to (tanh x - x) / x^3 (error 8e-10 relative)
     const float z = ax * ax;
-    float ps = -0.000966387638993646f;
-    ps = fmaf(ps, z, 0.0034055003387174483f);
-    ps = fmaf(ps, z, -0.008826388520025496f);
-    ps = fmaf(ps, z, 0.02186568778676557f);
-    ps = fmaf(ps, z, -0.053968065636603224f);
-    ps = fmaf(ps, z, 0.13333332981667803f);
-    ps = fmaf(ps, z, -0.3333333333225883f);
+    float ps = 0.01974657f;
+    ps = fmaf(ps, z, -0.05379952f);
+    ps = fmaf(ps, z, 0.13332911f);
+    ps = fmaf(ps, z, -0.33333334f);
     const float ts = fmaf(ax * z, ps, ax);
-    // k = round(16 |x|) limited to the table; adding 1.5 * 2^23 leaves k in the low mantissa bits
+    // otherwise k = round(16 |x|) in 6..146; adding 1.5 * 2^23 leaves k in the low mantissa bits. Arguments
+    // above 9.125 are clamped: tanh is 1 to float precision from 9.011 on, and the table's last entries
+    // round to exactly 1, so no separate saturation test is needed (infinity included).
     const float magic = 12582912.0f;
-    const float kb = fmaf(fminf(fmaxf(ax, 0.5f), 9.125f), 16.0f, magic);
+    const float ac = fminf(fmaxf(ax, 0.34375f), 9.125f);
+    const float kb = fmaf(ac, 16.0f, magic);
     const float kf = kb - magic;
-    const float4 e = __ldg(&kTanhTable[(__float_as_int(kb) & 0xff) - 8]);   // {T hi, T lo, 1 - T^2, 0}
-    const float d = fmaf(-kf, 0.0625f, ax);                                  // exact
+    const float4 e = __ldg(&kTanhTable[(__float_as_int(kb) & 0xff) - 6]);   // {T hi, T lo, 1 - T^2, 0}
+    const float d = fmaf(-kf, 0.0625f, ac);                                  // exact, |d| <= 1/32
     const float d2 = d * d;
-    const float td = fmaf(d * d2, fmaf(0.13333333f, d2, -0.33333334f), d);   // tanh(d), |d| <= 1/32
+    const float td = fmaf(d * d2, fmaf(0.13333333f, d2, -0.33333334f), d);   // tanh(d)
     const float corr = (e.z * td) * rcp_fast(fmaf(e.x, td, 1.0f));
     const float tb = e.x + (e.y + corr);
-    float t = ax < 0.55f ? ts : tb;
-    t = ax > 9.1f ? 1.0f : t;
-    t = copysignf(t, x);
+    const float t = copysignf(ax < 0.34375f ? ts : tb, x);
     return x != x ? x : t;
 }
 // exp for float with error close to half an ulp (the host libm's expf is nearly correctly

@@ -236,4 +236,42 @@ Status run_softmax(const SoftmaxArgs &a, cudaStream_t stream) {
     return kOk;
 }
 
+// ---- IsMax (special transform 41; include/ops/special_ops.h:1945-2400) ---------------------------------
+// z = 1 at the position of the maximum of every TAD (the first one among equals, which is what the reference's
+// strict "currMax < x" scan keeps), 0 elsewhere. The positions come from the IndexMax reduction of the
+// indexreduce family; this kernel only writes the marks: element j of TAD r gets (j == index[r]).
+struct IsMaxArgs {
+    const void *index;   // one position per TAD, stored in the element type
+    void *z;
+    LL numTads, tadLen;
+    View zOuter, zInner;
+};
+
+template <class T>
+__global__ void __launch_bounds__(kSmBlock) k_ismax_mark(const IsMaxArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    const T *idx = static_cast<const T *>(a.index);
+    T *az = static_cast<T *>(a.z);
+    const LL total = a.numTads * a.tadLen;
+    const LL nthreads = (LL) gridDim.x * kSmBlock;
+    for (LL i = (LL) blockIdx.x * kSmBlock + threadIdx.x; i < total; i += nthreads) {
+        const LL r = i / a.tadLen, j = i - r * a.tadLen;
+        const LL hit = (LL) Elem<T>::load(idx + r);
+        Elem<T>::store(az + view_offset(a.zOuter, r) + view_offset(a.zInner, j), j == hit ? C(1) : C(0));
+    }
+}
+
+template <class T>
+Status run_ismax_mark(const IsMaxArgs &a, cudaStream_t stream) {
+    const LL total = a.numTads * a.tadLen;
+    if (total <= 0) return kOk;
+    LL blocks = ceil_div(total, kSmBlock);
+    const LL cap = (LL) kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    launch_kernel(k_ismax_mark<T>, dim3((unsigned) blocks), dim3(kSmBlock), stream, a);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
 }  // namespace nd4jb200

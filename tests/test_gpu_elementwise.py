@@ -334,7 +334,7 @@ def test_errors_are_reported_not_fatal(ops):
         ops.execTransformFloat(None, 57, x, info, x, info, None)   # hole in the transform table
     assert e.value.code == 2
     with pytest.raises(Nd4jError) as e:
-        ops.execTransformFloat(None, 41, x, info, x, info, None)   # IsMax: composite, not served
+        ops.execTransformFloat(None, 36, x, info, x, info, None)   # a composite transform that is not served
     assert e.value.code == 3
     with pytest.raises(Nd4jError) as e:
         ops.execPairwiseTransformFloat(None, 0, x, info, x, S.shape_info([3, 3]), x, info, None)
@@ -444,3 +444,22 @@ def test_softmax_f_order_rows(ops, real_ref):
     ops.execTransformFloat(None, 38, dev(lay.buffer), lay.info, dz, lay.info, None)
     np.testing.assert_allclose(host(dz), want, rtol=1e-5, atol=1e-9)
     np.testing.assert_allclose(host(dz).reshape(33, 40).T.sum(axis=1), 1.0, rtol=1e-5)
+
+
+# ---- IsMax (special transform 41) -----------------------------------------------------------------
+@pytest.mark.parametrize("shape,extra", [((1, 777), None), ((40, 33), None), ((40, 33), [1, 1]), ((40, 33), [1, 0]),
+                                         ((6, 7, 8), [1, 2]), ((6, 7, 8), [2, 0, 2]), ((6, 7, 8), [2, 1, 2]),
+                                         ((9, 11), [2, 0, 1])])
+def test_ismax_first_maximum_wins(ops, real_ref, shape, extra):
+    """One-hot of the maximum over the whole array or along dimensions, ties resolved to the first position,
+    against the reference (include/ops/special_ops.h:2001-2400)."""
+    rng = np.random.default_rng(len(shape) + (0 if extra is None else sum(extra)))
+    x = rng.integers(0, 6, shape).astype(np.float32)          # few levels: many ties
+    info = S.shape_info(list(shape))
+    ex = None if extra is None else np.array(extra, np.float32)
+    want = real_ref.transform(41, x.ravel().copy(), info, np.full(x.size, 7, np.float32), info, ex)
+    dz = dev(np.full(x.size, 7, np.float32))
+    ops.execTransformFloat(None, 41, dev(x), info, dz, info, None if ex is None else dev(ex))
+    np.testing.assert_array_equal(host(dz), want)
+    if extra is None:
+        assert host(dz).sum() == 1 and host(dz)[int(x.argmax())] == 1

@@ -433,3 +433,34 @@ def test_reduce3_all_pairs_rejects_mismatched_tads(ops):
     with pytest.raises(RuntimeError):
         ops.execReduce3AllFloat(None, 1, torch.zeros(32, device="cuda"), xi, None, torch.zeros(36, device="cuda"), yi,
                                 z, zi, [1], 1, None, None, None, None)
+
+
+# ---- along-TAD reductions over thousands of back-to-back TADs ---------------------------------------
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.float16])
+@pytest.mark.parametrize("rows,cols", [(8191, 1000), (4099, 4096), (40000, 64), (70001, 24)])
+def test_dimension_reductions_on_many_back_to_back_tads(ops, real_ref, dt, rows, cols):
+    """Shapes with thousands of contiguous TADs (ragged row counts, lengths that leave partial trips): Sum, Max,
+    IMax with ties, Variance and Euclidean distance against the reference."""
+    if dt != np.float32 and rows > 10000:
+        pytest.skip("the float run covers the long shapes")
+    rng = np.random.default_rng(rows + cols)
+    x = rng.integers(-8, 9, (rows, cols)).astype(dt)          # small integers: ties for IMax, exact sums
+    y = rng.integers(-8, 9, (rows, cols)).astype(dt)
+    xi, zi = S.shape_info([rows, cols]), S.shape_info([rows, 1])
+    name = NAME[dt]
+    dx, dy = dev(x), dev(y)
+    out = dev(np.zeros(rows, dt))
+    getattr(ops, "execReduce" + name)(None, 1, dx, xi, None, out, zi, [1], 1)
+    np.testing.assert_array_equal(host(out).astype(np.float64), x.astype(np.float64).sum(1))
+    getattr(ops, "execReduce" + name)(None, 3, dx, xi, None, out, zi, [1], 1)
+    np.testing.assert_array_equal(host(out), x.max(1))
+    getattr(ops, "execIndexReduce" + name)(None, 0, dx, xi, None, out, zi, [1], 1)
+    np.testing.assert_array_equal(host(out).astype(np.int64), x.argmax(1))
+    getattr(ops, "execSummaryStats" + name)(None, 0, dx, xi, None, out, zi, [1], 1, True)
+    np.testing.assert_allclose(host(out).astype(np.float64), x.astype(np.float64).var(1, ddof=1), rtol=TOL[dt] * 10)
+    getattr(ops, "execReduce3" + name)(None, 1, dx, xi, None, dy, xi, out, zi, [1], 1)
+    want = np.sqrt(((x.astype(np.float64) - y.astype(np.float64)) ** 2).sum(1))
+    np.testing.assert_allclose(host(out).astype(np.float64), want, rtol=TOL[dt])
+    if dt == np.float32 and rows < 10000:
+        ref = real_ref.reduce3(1, x.ravel(), xi, y.ravel(), xi, np.zeros(rows, dt), zi, [1])
+        np.testing.assert_allclose(host(out), ref, rtol=1e-5)
