@@ -145,3 +145,31 @@ def test_two_streams_and_two_host_threads_do_not_share_scratch(ops):
         for cols, total in results[k]:
             np.testing.assert_array_equal(cols, want_cols)      # small integers: exact in any order
             assert total == want_total
+
+
+@pytest.mark.parametrize("shape", [(64, 2000, 40), (48, 3000, 37), (3, 5000, 260)])
+def test_middle_axis_reductions_split_into_clusters(ops, shape):
+    """Reductions over the middle axis of rank-3 arrays: neighbouring TADs are adjacent, every TAD is a long
+    strided walk that is cut into segments (thread-block clusters plus, for the longest, arrival counters),
+    tiles are only partly filled, and the odd width takes the scalar-load path. Small integers: exact."""
+    rng = np.random.default_rng(shape[2])
+    x = rng.integers(-6, 7, shape).astype(np.float32)
+    y = rng.integers(-6, 7, shape).astype(np.float32)
+    xi = S.shape_info(list(shape))
+    zi = S.shape_info([shape[0], 1, shape[2]])
+    n = shape[0] * shape[2]
+    dx, dy = dev(x), dev(y)
+    out = torch.zeros(n, device="cuda")
+    ops.execReduceFloat(None, 1, dx, xi, None, out, zi, [1], 1)
+    np.testing.assert_array_equal(host(out).reshape(shape[0], shape[2]), x.sum(1))
+    ops.execIndexReduceFloat(None, 0, dx, xi, None, out, zi, [1], 1)
+    np.testing.assert_array_equal(host(out).reshape(shape[0], shape[2]), x.argmax(1))
+    ops.execReduce3Float(None, 0, dx, xi, None, dy, xi, out, zi, [1], 1)          # Manhattan: exact on integers
+    np.testing.assert_array_equal(host(out).reshape(shape[0], shape[2]), np.abs(x - y).sum(1))
+    ops.execSummaryStatsFloat(None, 0, dx, xi, None, out, zi, [1], 1, True)
+    np.testing.assert_allclose(host(out).reshape(shape[0], shape[2]), x.astype(np.float64).var(1, ddof=1), rtol=1e-5)
+    for cluster in (1, 2, 8):                 # same results whatever the cluster size
+        ops.lib.nd4jb200_set_tuning(4, cluster)
+        ops.execReduceFloat(None, 1, dx, xi, None, out, zi, [1], 1)
+        np.testing.assert_array_equal(host(out).reshape(shape[0], shape[2]), x.sum(1))
+    ops.lib.nd4jb200_set_tuning(4, 4)
