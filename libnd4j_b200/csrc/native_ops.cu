@@ -12,9 +12,6 @@
 
 namespace {
 
-std::mutex g_mu;
-std::map<const void *, std::vector<Nd4jLong> > g_shapeCache;
-std::map<std::pair<const void *, int>, std::vector<int> > g_dimCache;
 
 [[noreturn]] void fail(const char *where) {
     throw std::runtime_error(std::string(where) + ": " + nd4jb200_last_error());
@@ -29,35 +26,38 @@ bool is_device_pointer(const void *p) {
     return attr.type == cudaMemoryTypeDevice;
 }
 
-// Host view of a shapeInfo: the copy in extraPointers[slot] when the caller provided one,
-// otherwise the argument itself if it is host memory, otherwise a cached download.
+// Host view of a shapeInfo: the copy in extraPointers[slot] when the caller provided one, otherwise the
+// argument itself if it is host memory, otherwise a fresh download. Downloads are not cached by address: a
+// caller may free a descriptor and get the same address back for a different shape. The returned pointer
+// stays valid until the calling thread has asked for kKeep further descriptors (one call needs at most 4).
+constexpr int kKeep = 16;
 const Nd4jLong *host_info(Nd4jPointer *extra, int slot, const Nd4jLong *arg) {
     if (extra && slot >= 0 && extra[slot]) return static_cast<const Nd4jLong *>(extra[slot]);
     if (arg == nullptr) return nullptr;
     if (!is_device_pointer(arg)) return arg;
-    std::lock_guard<std::mutex> lock(g_mu);
-    auto it = g_shapeCache.find(arg);
-    if (it != g_shapeCache.end()) return it->second.data();
+    thread_local std::vector<Nd4jLong> ring[kKeep];
+    thread_local int next = 0;
+    std::vector<Nd4jLong> &v = ring[next];
+    next = (next + 1) % kKeep;
     Nd4jLong rank = 0;
     if (cudaMemcpy(&rank, arg, sizeof(Nd4jLong), cudaMemcpyDeviceToHost) != cudaSuccess || rank < 0 || rank > 32)
         throw std::runtime_error("could not read shapeInfo from the device");
-    std::vector<Nd4jLong> v(2 * rank + 4);
+    v.resize(2 * rank + 4);
     if (cudaMemcpy(v.data(), arg, sizeof(Nd4jLong) * v.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
         throw std::runtime_error("could not read shapeInfo from the device");
-    return g_shapeCache.emplace(arg, std::move(v)).first->second.data();
+    return v.data();
 }
 
+// The dimension list lives on the device in the reference's CUDA build; TAD geometry is decoded on the host, so
+// it is read back on every call (dimension buffers are routinely reused with other contents).
 const int *host_dims(const int *dimension, int n) {
     if (dimension == nullptr || n <= 0) return nullptr;
     if (!is_device_pointer(dimension)) return dimension;
-    std::lock_guard<std::mutex> lock(g_mu);
-    auto key = std::make_pair(static_cast<const void *>(dimension), n);
-    auto it = g_dimCache.find(key);
-    if (it != g_dimCache.end()) return it->second.data();
-    std::vector<int> v(n);
+    thread_local std::vector<int> v;
+    v.resize(n);
     if (cudaMemcpy(v.data(), dimension, sizeof(int) * n, cudaMemcpyDeviceToHost) != cudaSuccess)
         throw std::runtime_error("could not read the dimension array from the device");
-    return g_dimCache.emplace(key, std::move(v)).first->second.data();
+    return v.data();
 }
 
 template <class T> struct TypeCode;

@@ -77,6 +77,31 @@ int main() {
     }
     expect(std::fabs(total - all) <= 1e-4 * rows * cols, "whole-array sum");
 
+    // no host copies in extraPointers, and the same device buffers reused with other contents: the dimension
+    // buffer now says {0} and the result descriptor [1, cols]; nothing may be remembered from the calls above
+    {
+        std::vector<int> dim0 = {0};
+        std::vector<Nd4jLong> ci = info2(1, cols);
+        ops.memcpyAsync(ddim, dim0.data(), 4, 1, stream);
+        ops.memcpyAsync(dzi, ci.data(), (Nd4jLong) (ci.size() * sizeof(Nd4jLong)), 1, stream);
+        ops.streamSynchronize(stream);
+        float *dcol = static_cast<float *>(ops.mallocDevice(cols * 4, nullptr, 0));
+        Nd4jPointer bare[16] = {nullptr};
+        bare[1] = stream;
+        ops.execReduceFloat(bare, 1, t3, dxi, nullptr, dcol, dzi, ddim, 1);
+        std::vector<float> gcol = to_host(dcol, cols);
+        for (Nd4jLong c = 0; c < cols; c++) {
+            double s = 0, mag = 0;
+            for (Nd4jLong r = 0; r < rows; r++) { s += g3[r * cols + c]; mag += std::fabs(g3[r * cols + c]); }
+            expect(std::fabs(gcol[c] - s) <= 1e-5 * mag + 1e-12, "column sum after the buffers were reused");
+        }
+        ops.freeDevice(dcol, nullptr);
+        // restore what the rest of the program expects
+        ops.memcpyAsync(ddim, dim.data(), 4, 1, stream);
+        ops.memcpyAsync(dzi, zi.data(), (Nd4jLong) (zi.size() * sizeof(Nd4jLong)), 1, stream);
+        ops.streamSynchronize(stream);
+    }
+
     // random: two identical states give identical draws, and the state advances
     Nd4jPointer rngExtras[2] = {nullptr, stream};
     Nd4jPointer s1 = ops.initRandom(rngExtras, 119, 100000, nullptr), s2 = ops.initRandom(rngExtras, 119, 100000, nullptr);
