@@ -249,7 +249,7 @@ Status random_common(void *stream, int dtype, int opNum, int arity, RandomState 
 extern "C" {
 
 const char *nd4jb200_last_error(void) { return last_error(); }
-unsigned long long nd4jb200_launch_count(void) { return g_launches; }
+unsigned long long nd4jb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int nd4jb200_set_tuning(int key, long long value) {
     if (key < 0 || key >= kTuneCount || value < (key == kTuneOverlapLaunch ? 0 : 1) || (key == kTuneMaxCluster && value > 8) ||

@@ -51,6 +51,15 @@ ND_D U64 rng_shift(U64 x, U64 y) {
 ND_D U64 rng_shift_pre(U64 x, U64 y, U64 thr) {
     if (y != 0ull && x > thr) {
         U64 q = __umul64hi(x, thr);
+        if (y < (1ull << 30)) {
+            // the remainder x - q*y is below 3y < 2^32, so its low 32 bits are all of it
+            const unsigned y32 = (unsigned) y;
+            unsigned rem = (unsigned) x - (unsigned) q * y32;
+            unsigned up = 0;
+            if (rem >= y32) { up = 1; rem -= y32; }
+            if (rem >= y32) up++;
+            return q + (U64) (up + 11u);
+        }
         U64 rem = x - q * y;
         if (rem >= y) { q++; rem -= y; }
         if (rem >= y) q++;
@@ -67,10 +76,15 @@ ND_D U64 rng_finalise(U64 x) {
 ND_D U64 rotl64(U64 x, int k) { return (x << k) | (x >> (64 - k)); }
 // s mod (2^31 - 1) by folding 31-bit digits (2^31 = 1 mod m)
 ND_D U64 mod_mersenne31(U64 s) {
-    const U64 m = 2147483647ull;
-    U64 t = (s & m) + ((s >> 31) & m) + (s >> 62);   // < 2^32 + 3
-    t = (t & m) + (t >> 31);                         // <= m + 2
-    return t >= m ? t - m : t;
+    // three 31-bit digits in 32-bit arithmetic: lo 31 bits, the next 31, the top 2
+    const unsigned m = 2147483647u;
+    const unsigned lo = (unsigned) s, hi = (unsigned) (s >> 32);
+    const unsigned d0 = lo & m;
+    const unsigned d1 = __funnelshift_r(lo, hi, 31) & m;        // bits 31..61
+    const unsigned d2 = hi >> 30;                               // bits 62..63
+    unsigned t = d0 + d1;                                       // <= 2^32 - 2
+    t = (t & m) + (t >> 31) + d2;                               // <= m + 4
+    return (U64) (t >= m ? t - m : t);
 }
 ND_D U64 rng_mix(U64 s0) {
     U64 s1 = mod_mersenne31(s0) + 11ull;

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
+#include <atomic>
 #include <string>
 #include "common.h"
 #include "shape_host.h"
@@ -28,8 +29,8 @@ Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot)
 void release_workspaces();
 
 // Counts kernel launches issued by this library since load (read by the benchmark).
-extern unsigned long long g_launches;
-inline void count_launch(int n = 1) { g_launches += n; }
+extern std::atomic<unsigned long long> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add((unsigned long long) n, std::memory_order_relaxed); }
 
 // Launch heuristics that may be overridden at run time (nd4jb200_set_tuning); defaults in runtime.cu.
 enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneMaxCluster = 4, kTuneCount = 5 };

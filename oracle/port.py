@@ -247,8 +247,26 @@ class Port:
         return self.reduce3(op, x, x_info, y, y_info, out, np.array([2, 1, 1, 1, 1, 0, 1, 99]), None, extra)[0]
 
     # ---- elementwise ---------------------------------------------------------------------------
+    def _softmax(self, op, x, x_info, z, z_info):
+        """SoftMax (38), SoftMaxDerivative (39), LogSoftMax (40) on matrices (row-wise) and vectors
+        (include/ops/special_ops.h:1484-1940): max, subtract, exp, sequential float row sum, divide, then
+        y (1 - y) or log."""
+        shp = _parts(x_info)[1]
+        rows, cols = (1, int(np.prod(shp))) if 1 in shp else (int(shp[0]), int(shp[1]))
+        offs = coord_offsets(*_parts(x_info)[1:3])
+        m = np.ascontiguousarray(x[offs]).reshape(rows, cols).astype(np.float32)
+        e = np.exp((m - m.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float32)
+        sums = np.cumsum(e, axis=1, dtype=np.float32)[:, -1:]
+        yv = (e / sums).astype(np.float32)
+        with np.errstate(divide="ignore"):
+            out = yv if op == 38 else ((yv * (np.float32(1) - yv)).astype(np.float32) if op == 39 else np.log(yv).astype(np.float32))
+        z[coord_offsets(*_parts(z_info)[1:3])] = out.ravel()
+        return z
+
     def transform(self, op, x, x_info, z, z_info, extra=None):
         self._need_f32(x)
+        if op in (38, 39, 40):
+            return self._softmax(op, x, x_info, z, z_info)
         xo, zo = linear_offsets(x_info), linear_offsets(z_info)
         if _parts(x_info)[4] != _parts(z_info)[4] and _parts(x_info)[0] > 1:
             xo, zo = coord_offsets(*_parts(x_info)[1:3]), coord_offsets(*_parts(z_info)[1:3])
@@ -368,7 +386,51 @@ class Port:
     def random_x(self, op, state, x, x_info, z, z_info, extra):
         return self._random(op, 1, state, x, None, False, z, z_info, extra, x_info)
 
+    def _unit(self, state, indices):
+        """relativeT<float>: (float) element / (float) MAX, with the float of 2^64 - 1 being 2^64 (helper_generator.h:481-486)."""
+        raw = np.array([self.rng_element(state, int(i)) & 0xFFFFFFFFFFFFFFFF for i in indices], dtype=np.uint64)
+        return raw.astype(np.float32) * np.float32(2.0 ** -64)
+
+    def _special_random(self, op, state, x, x_info, y, y_info, z, z_info, extra):
+        """Choice (5), BinomialDistribution (8), BinomialDistributionEx (9): special_random_ops.h:153-245, 474-650,
+        operands addressed by their elementWiseStride."""
+        self._need_f32(z)
+        g, _ = self._rng[state]
+        n = int(np.prod(_parts(z_info)[1], dtype=np.int64))
+        zews = max(_parts(z_info)[3], 1)
+        if op == 5:
+            k = int(np.prod(_parts(y_info)[1], dtype=np.int64))
+            xs = x[::max(_parts(x_info)[3], 1)][:k]
+            sums = np.zeros(k, np.float32)
+            acc = np.float32(0)
+            for f in range(k):                       # running sums in float, in order
+                acc = np.float32(acc + y[f * max(_parts(y_info)[3], 1)])
+                sums[f] = acc
+            u = self._unit(state, range(n))
+            hit = np.array([int(np.argmax(u[e] <= sums)) if (u[e] <= sums).any() else k - 1 for e in range(n)])
+            z[:n * zews:zews] = xs[hit]
+            self.lib.port_rng_rewind(ctypes.byref(g), ctypes.c_longlong(n))
+            return z
+        trials = int(extra[0])
+        out = np.zeros(n, np.float32)
+        e1 = np.arange(1, n + 1, dtype=np.int64)
+        for t in range(1, trials + 1):
+            u = self._unit(state, e1 * t)
+            if y is z:
+                prob = np.float32(extra[1])
+            elif op == 8:
+                prob = y[(t - 1) * max(_parts(y_info)[3], 1)]
+            else:
+                prob = y[:n * max(_parts(y_info)[3], 1):max(_parts(y_info)[3], 1)]
+            out += (u < prob).astype(np.float32)
+        z[:n * zews:zews] = out
+        if trials > 0:
+            self.lib.port_rng_rewind(ctypes.byref(g), ctypes.c_longlong(n * trials))
+        return z
+
     def random_xy(self, op, state, x, x_info, y, y_info, z, z_info, extra):
+        if op in (5, 8, 9):
+            return self._special_random(op, state, x, x_info, y, y_info, z, z_info, extra)
         y_is_z = y is z
         xs = None if x is z else x
         return self._random(op, 2, state, x if xs is not None else np.array(z), None if y_is_z else y, y_is_z, z, z_info,

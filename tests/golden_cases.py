@@ -49,11 +49,10 @@ def cases():
     yield "random/sequence", dict(fam="random", seed=119, table=100000, n=70001, calls=seq)
     for op in (0, 1, 2, 3, 5, 6, 7):
         yield "reduce3_all/%d" % op, dict(fam="reduce3_all", op=op, seed=9000 + op, xshape=(9, 37), yshape=(5, 37), dims=[1])
-    # families the port does not restate (port=False): held against the CUDA path only
     for op in (38, 39, 40):
         for shape in ((12, 10), (5, 700)):
-            yield "softmax/%d/%dx%d" % (op, shape[0], shape[1]), dict(fam="softmax", op=op, seed=9100 + op, shape=shape, port=False)
-    yield "random/special", dict(fam="random_special", seed=119, table=100000, n=3001, trials=5, choices=23, port=False)
+            yield "softmax/%d/%dx%d" % (op, shape[0], shape[1]), dict(fam="softmax", op=op, seed=9100 + op, shape=shape)
+    yield "random/special", dict(fam="random_special", seed=119, table=100000, n=3001, trials=5, choices=23)
 
 
 def _inputs(case):
