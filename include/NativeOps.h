@@ -167,6 +167,8 @@ public:
     int memcpyAsync(Nd4jPointer dst, Nd4jPointer src, Nd4jLong size, int flags, Nd4jPointer reserved);
     int memset(Nd4jPointer dst, int value, Nd4jLong size, int flags, Nd4jPointer reserved);
     int memsetAsync(Nd4jPointer dst, int value, Nd4jLong size, int flags, Nd4jPointer reserved);
+    /* nd4jb200_convert_types (NativeOps.h:2144) */
+    void convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z);
     int getAvailableDevices();
     void enableDebugMode(bool reallyEnable);
     void enableVerboseMode(bool reallyEnable);

@@ -207,6 +207,9 @@ int nd4jb200_concat(void *stream, int dtype, int dimension, int numArrays, const
 int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong n, const Nd4jLong *indexes,
                        const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets, const Nd4jLong *zTadShapeInfo,
                        const Nd4jLong *zTadOffsets);
+/* NativeOps::convertTypes among ND4J_FLOAT16 (3), ND4J_FLOAT32 (6) and ND4J_DOUBLE (7): z[i] = (D)(float) x[i]
+ * (blas/NativeOps.h:2144; include/loops/type_conversions.h:592-610). Other encodings: ND4JB200_EUNSUPPORTED. */
+int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z);
 /* NativeOps::average{Float,Double,Half}: z[i] = sum_k sources[k][i] / n (z == NULL: into sources[0]); with
  * `propagate` the result is also written over every source (blas/NativeOps.h:1996-2025;
  * include/ops/impl/specials.cpp:374-433). At most 128 sources, all on this device or peer-mapped. */

@@ -267,6 +267,10 @@ ND4JB200_DEFINE_SCALAR(double, Double, double)
 ND4JB200_DEFINE_SCALAR(float, Float, float)
 ND4JB200_DEFINE_SCALAR(float16, Half, float)
 
+void NativeOps::convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z) {
+    check(nd4jb200_convert_types(stream_of(extras), srcType, x, N, dstType, z), "convertTypes");
+}
+
 Nd4jPointer NativeOps::initRandom(Nd4jPointer *extraPointers, long seed, long bufferSize, Nd4jPointer ptrToBuffer) {
     Nd4jPointer state = nd4jb200_init_random(stream_of(extraPointers), seed, bufferSize,
                                              extraPointers ? extraPointers[0] : nullptr, ptrToBuffer);

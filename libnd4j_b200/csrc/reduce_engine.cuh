@@ -89,8 +89,8 @@ ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, 
 template <class P, class = void> struct HasTile { static constexpr bool value = false; };
 template <class P> struct HasTile<P, decltype((void) P::kTile)> { static constexpr bool value = true; };
 
-// CTAs per SM the along-TAD kernel is compiled for. A budget of 64 registers lets the compiler keep
-// all loads of a trip in flight; a policy may name another budget for half precision (kHalfRowCtas).
+// CTAs per SM the along-TAD kernel is compiled for. An allowance of 64 registers lets the compiler keep
+// all loads of a trip in flight; a policy may name another allowance for half precision (kHalfRowCtas).
 template <class T, class P, class = void> struct RowBudget { static constexpr int v = 4; };
 template <class P> struct RowBudget<__half, P, decltype((void) P::kHalfRowCtas)> { static constexpr int v = P::kHalfRowCtas; };
 

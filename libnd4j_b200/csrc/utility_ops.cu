@@ -10,6 +10,7 @@
 //   pullRows   TAD number indexes[k] of x is copied onto TAD k of z (blas/cpu/NativeOps.cpp:2045-2104)
 //   average    z[i] = sum_k x_k[i] / n, then (optionally) every x_k = z  (specials.cpp:374-433)
 //   accumulate z[i] += sum_k x_k[i]  (onto what z already holds)          (specials.cpp:343-359)
+//   convertTypes  z[i] = (D)(float) x[i] among float16 / float32 / double  (type_conversions.h:592-610)
 //
 // Copies move raw 2-, 4- or 8-byte elements; only average / accumulate look at the values.
 #include "../../include/nd4j_b200.h"
@@ -237,6 +238,51 @@ Status sum_sources(void *stream, int dtype, const void *const *sources, void *z,
     return kOk;
 }
 
+// ---- convertTypes (float16 / float32 / double) -----------------------------------------------------
+// z[i] = (D) ((float) x[i]): every conversion goes through float, as the reference's convertGeneric does
+// (include/loops/type_conversions.h:592-610), so double -> double also rounds to float on the way.
+template <class S> ND_D float as_float(S v);
+template <> ND_D float as_float<__half>(__half v) { return __half2float(v); }
+template <> ND_D float as_float<float>(float v) { return v; }
+template <> ND_D float as_float<double>(double v) { return (float) v; }
+template <class D> ND_D D from_float(float v);
+template <> ND_D __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> ND_D float from_float<float>(float v) { return v; }
+template <> ND_D double from_float<double>(float v) { return (double) v; }
+
+template <class S, class D>
+__global__ void __launch_bounds__(kCopyBlock) k_convert(const S *x, D *z, LL n) {
+    grid_dependency_sync();
+    const LL tid = (LL) blockIdx.x * kCopyBlock + threadIdx.x, nthreads = (LL) gridDim.x * kCopyBlock;
+    LL i = tid;
+    for (; i + 3 * nthreads < n; i += 4 * nthreads) {
+        const S a = x[i], b = x[i + nthreads], c = x[i + 2 * nthreads], d = x[i + 3 * nthreads];
+        z[i] = from_float<D>(as_float<S>(a));
+        z[i + nthreads] = from_float<D>(as_float<S>(b));
+        z[i + 2 * nthreads] = from_float<D>(as_float<S>(c));
+        z[i + 3 * nthreads] = from_float<D>(as_float<S>(d));
+    }
+    for (; i < n; i += nthreads) z[i] = from_float<D>(as_float<S>(x[i]));
+}
+
+template <class S, class D>
+Status launch_convert(const void *x, void *z, LL n, cudaStream_t stream) {
+    LL blocks = ceil_div(ceil_div(n, 4), kCopyBlock);
+    const LL cap = (LL) kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    launch_kernel(k_convert<S, D>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, static_cast<const S *>(x), static_cast<D *>(z), n);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+template <class S>
+Status convert_from(int dstType, const void *x, void *z, LL n, cudaStream_t stream) {
+    if (dstType == 3) return launch_convert<S, __half>(x, z, n, stream);
+    if (dstType == 6) return launch_convert<S, float>(x, z, n, stream);
+    return launch_convert<S, double>(x, z, n, stream);
+}
+
 }  // namespace
 }  // namespace nd4jb200
 
@@ -321,6 +367,19 @@ int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong
     else launch_kernel(k_pull_rows<8>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
     ND_CUDA(cudaGetLastError());
     return kOk;
+}
+
+int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z) {
+    if (!x || !z) return bad_arg("convertTypes: null operand");
+    if (n < 0) return bad_arg("convertTypes: negative length");
+    auto served = [](int t) { return t == 3 || t == 6 || t == 7; };      // ND4J_FLOAT16, ND4J_FLOAT32, ND4J_DOUBLE
+    if (!served(srcType) || !served(dstType))
+        return unsupported("convertTypes serves float16 (3), float32 (6) and double (7); the 8- and 16-bit integer, "
+                           "float8 and threshold encodings are not built");
+    if (n == 0) return kOk;
+    if (srcType == 3) return convert_from<__half>(dstType, x, z, n, as_stream(stream));
+    if (srcType == 6) return convert_from<float>(dstType, x, z, n, as_stream(stream));
+    return convert_from<double>(dstType, x, z, n, as_stream(stream));
 }
 
 int nd4jb200_average(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length, int propagate) {

@@ -73,6 +73,7 @@ def load_library(path=None):
     sig = {
         "nd4jb200_last_error": (ctypes.c_char_p, []),
         "nd4jb200_launch_count": (ctypes.c_ulonglong, []),
+        "nd4jb200_convert_types": (i, [vp, i, vp, ll, i, vp]),
         "nd4jb200_flatten": (i, [vp, i, ll, ctypes.c_char, vp, llp, vp, llp]),
         "nd4jb200_concat": (i, [vp, i, i, i, vp, vp, vp, llp]),
         "nd4jb200_pull_rows": (i, [vp, i, vp, vp, ll, vp, llp, vp, llp, vp]),
@@ -493,6 +494,10 @@ class NativeOps:
     def _accumulate(self, dt, extras, dx, dz, n, length):
         ptrs = (ctypes.c_void_p * n)(*[_ptr(d).value for d in dx])
         self._check(self.lib.nd4jb200_accumulate(self._stream(extras), dt, ptrs, _ptr(dz), n, length))
+
+    def convertTypes(self, extras, srcType, x, N, dstType, z):
+        """ND4J_FLOAT16 = 3, ND4J_FLOAT32 = 6, ND4J_DOUBLE = 7 (NativeOps.h:2144)."""
+        self._check(self.lib.nd4jb200_convert_types(self._stream(extras), srcType, _ptr(x), N, dstType, _ptr(z)))
 
     def memcpyAsync(self, dst, src, size, flags, reserved=None):
         self._check(self.lib.nd4jb200_memcpy_async(_ptr(dst), _ptr(src), size, flags, _ptr(reserved)))

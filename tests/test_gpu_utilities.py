@@ -129,3 +129,24 @@ def test_average_into_first_source_and_limits(ops):
         np.testing.assert_array_equal(host(d), np.full(1000, 3.0, np.float32))
     with pytest.raises(RuntimeError):
         ops.averageFloat(None, [dxs[0]] * 129, None, 129, 1000, False)
+
+
+CODES = {np.float16: 3, np.float32: 6, np.float64: 7}
+
+
+@pytest.mark.parametrize("src", [np.float16, np.float32, np.float64])
+@pytest.mark.parametrize("dst", [np.float16, np.float32, np.float64])
+def test_convert_types_goes_through_float(ops, src, dst):
+    """z = (D)(float) x (include/loops/type_conversions.h:592-610): bit-exact against numpy's IEEE conversions,
+    including overflow to infinity, subnormal halves and the float rounding of double -> double."""
+    rng = np.random.default_rng(1)
+    x = np.concatenate([rng.standard_normal(10001) * 100, [0.0, -0.0, 65504.0, 70000.0, 1e-7, 6e-8, 1e300, -1e300, 1 / 3]])
+    with np.errstate(over="ignore"):
+        x = x.astype(src)
+        want = x.astype(np.float32).astype(dst)
+    dz = dev(np.zeros(x.size, dst))
+    ops.convertTypes(None, CODES[src], dev(x), x.size, CODES[dst], dz)
+    got = host(dz)
+    assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+    with pytest.raises(RuntimeError):
+        ops.convertTypes(None, 1, dev(x), x.size, CODES[dst], dz)      # ND4J_INT8 is not served
