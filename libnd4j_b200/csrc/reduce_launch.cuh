@@ -20,16 +20,20 @@ struct ReduceCall {
 // Workspace layout: [256-byte result slot][kCounterSlots arrival counters][partial states]. The
 // counter region is never used for anything else; the workspace is zero-filled when it is
 // allocated and every launch re-zeroes the counters it used. Merging inside the launch pays off
-// when a TAD has few segments; with many segments per TAD only a few CTAs would do all the
-// merging, so those cases (and calls that need more counters than the region holds) leave the
-// partials to the separate, fully parallel finalize launch.
+// when a TAD has few segments, or when there are only a few TADs worked on by whole CTAs (whole-array
+// reductions); with many segments of many TADs only a few CTAs would do all the merging, so those
+// cases (and calls that need more counters than the region holds) leave the partials to the separate,
+// fully parallel finalize launch.
 constexpr size_t kCounterSlots = 65536;
 template <class State>
 Status split_scratch(cudaStream_t stream, ReduceArgs &a, size_t counters) {
     const size_t counterBytes = kCounterSlots * sizeof(unsigned);
     void *ws = nullptr;
     ND_TRY(workspace(stream, 256 + counterBytes + sizeof(State) * (size_t) a.numTads * a.splits, &ws, nullptr));
-    a.counters = (a.splits <= g_tuning[kTuneMaxInKernelMerge] && counters <= kCounterSlots)
+    // a handful of TADs that each take whole CTAs (whole-array reductions): the last CTA of a TAD folds all of
+    // its segments with 256 threads, however many there are
+    const bool fewWide = a.group == kBlock && a.numTads <= 8;
+    a.counters = ((a.splits <= g_tuning[kTuneMaxInKernelMerge] || fewWide) && counters <= kCounterSlots)
                      ? reinterpret_cast<unsigned *>(static_cast<char *>(ws) + 256) : nullptr;
     a.partials = static_cast<char *>(ws) + 256 + counterBytes;
     return kOk;
