@@ -160,11 +160,16 @@ def make_inputs(rows):
 
 
 # ------------------------------------------------------------------------------------------------
-def cpu_reference_chain(rows, repeats, threads=None):
-    """Times the reference's CPU loops on `rows` rows of the workload. Returns (Gelem/s, cores)."""
-    from oracle import reference
+def cpu_reference_chain(rows, repeats, threads=None, use_port=False):
+    """Times the reference's CPU loops (or, with use_port, the oracle's C restatement of them) on `rows` rows of
+    the workload. Returns (Gelem/s, cores, seconds of the best pass)."""
     from libnd4j_b200 import shape as S
-    ref = reference.Reference()
+    if use_port:
+        from oracle import port
+        ref = port.Port()
+    else:
+        from oracle import reference
+        ref = reference.Reference()
     if threads:
         ref.set_threads(threads)
     cores = ref.threads()
@@ -188,12 +193,16 @@ def run_reference_arm(args):
     if rank != 0:
         return
     from oracle import reference
-    if not reference.available():
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libnd4jref.so was not built"}))
-        return
     rows = 2048   # bounded sample: 1/8 of the rows, same row width
     from libnd4j_b200 import shape as S
-    ref = reference.Reference()
+    if reference.available():
+        ref, kind = reference.Reference(), "reference"
+        what = "reference CPU loops (OpenMP)"
+    else:
+        # the reference's own build is absent: time the oracle's C restatement of the same loops instead
+        from oracle import port
+        ref, kind = port.Port(), "port"
+        what = "oracle port of the reference CPU loops"
     cores = ref.threads()
     x, b, y = make_inputs(rows)
     xi, bi = S.shape_info([rows, COLS]), S.shape_info([1, COLS])
@@ -212,13 +221,13 @@ def run_reference_arm(args):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     value = rows * COLS / dt / 1e9
-    sample = "%d of %d rows per step, reference CPU loops (OpenMP), %d threads" % (rows, ROWS, cores)
+    sample = "%d of %d rows per step, %s, %d threads" % (rows, ROWS, what, cores)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "elementwise chain f32 [16384,4096] (sampled: %d rows)" % rows},
-        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": "reference", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -607,7 +616,10 @@ def run_ours(args):
             cpu = {"value": round(gel, 4), "unit": "Gelem/s", "cores": cores, "kind": "reference",
                    "sample": "%d of %d rows (same row width), best of 2 after one warm-up pass, %.1f ms" % (rows, ROWS, secs * 1e3)}
         else:
-            cpu = {"value": None, "unit": "Gelem/s", "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+            rows = 512      # the scalar port: a smaller sample keeps this leg at a few seconds
+            gel, cores, secs = cpu_reference_chain(rows, repeats=1, use_port=True)
+            cpu = {"value": round(gel, 4), "unit": "Gelem/s", "cores": cores, "kind": "port",
+                   "sample": "%d of %d rows (same row width), oracle port, best of 1 after one warm-up pass, %.1f ms" % (rows, ROWS, secs * 1e3)}
 
     if rank == 0:
         print(json.dumps({
