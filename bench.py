@@ -552,7 +552,7 @@ def run_ours(args):
     # cut into row blocks; block k's chain runs while block k+1 is copied in and block k-1 is copied
     # out (three streams, the same exec* calls on [rows/blocks, COLS] shapeInfos), so the step costs
     # about max(H2D, D2H) on a full-duplex link instead of their sum.
-    NBLK = 16
+    NBLK = args.e2e_blocks
     brow = ROWS // NBLK
     bbytes = brow * COLS * 4
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -699,6 +699,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller sizes for the families table")
     ap.add_argument("--no-families", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-blocks", type=int, default=16, help="row blocks of the pipelined end-to-end step (divides 16384)")
     ap.add_argument("--only", default=None, help="run only the families whose name contains one of these comma-separated texts")
     ap.add_argument("--profile", action="store_true", help="profiling aid: three plain timed launches per family, no graph")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
