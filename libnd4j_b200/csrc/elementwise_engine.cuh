@@ -39,9 +39,14 @@ template <class Op, int ARITY, class C> ND_D C ew_apply(C x, C y, C sc, const C 
     else if constexpr (ARITY == 2) return Op::template f<C>(x, y, p);
     else return Op::template f<C>(x, sc, p);
 }
+// Functors that keep a table in shared memory declare kPrepare and a prepare() every thread of the CTA calls.
+template <class Op, class = void> struct HasPrepare { static constexpr bool value = false; };
+template <class Op> struct HasPrepare<Op, decltype((void) Op::kPrepare)> { static constexpr bool value = true; };
+
 template <class T, class Op, int ARITY>
 __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
     grid_dependency_sync();
+    if constexpr (HasPrepare<Op>::value) Op::prepare();
     typedef typename Elem<T>::C C;
     constexpr int V = Elem<T>::kVec;
     const T *ax = static_cast<const T *>(a.x);

@@ -53,7 +53,21 @@ ND_D float rcp_fast(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
-ND_D float tanh_accurate(float x) {
+// kShared: T (hi, lo) comes from the CTA's shared-memory copy of the table (tanh_table_to_shared must have
+// run) and 1 - T^2 is recomputed (one FMA; its cancellation error near T = 1 scales a term below 1e-6).
+// The global table is read through L1 as a 16-byte gather that costs up to one wavefront per distinct row
+// and made the L1 data pipe, not the arithmetic, the limit of the Tanh transform (84 % busy in ncu).
+ND_D float2 *tanh_shared_table() {
+    __shared__ float2 table[144];
+    return table;
+}
+ND_D void tanh_table_to_shared() {
+    float2 *t = tanh_shared_table();
+    const int tid = threadIdx.x + threadIdx.y * blockDim.x, n = blockDim.x * blockDim.y;
+    for (int i = tid; i < 141; i += n) { const float4 e = kTanhTable[i]; t[i] = make_float2(e.x, e.y); }
+    __syncthreads();
+}
+template <bool kShared> ND_D float tanh_core(float x) {
     const float ax = fabsf(x);
     // |x| < 11/32: odd polynomial x + x^3 P(x^2), P fitted to (tanh x - x) / x^3 (error 8e-10 relative)
     const float z = ax * ax;
@@ -69,15 +83,24 @@ ND_D float tanh_accurate(float x) {
     const float ac = fminf(fmaxf(ax, 0.34375f), 9.125f);
     const float kb = fmaf(ac, 16.0f, magic);
     const float kf = kb - magic;
-    const float4 e = __ldg(&kTanhTable[(__float_as_int(kb) & 0xff) - 6]);   // {T hi, T lo, 1 - T^2, 0}
+    const int k = (__float_as_int(kb) & 0xff) - 6;
+    float th, tl, c;
+    if (kShared) {
+        const float2 e = tanh_shared_table()[k];
+        th = e.x; tl = e.y; c = fmaf(-th, th, 1.0f);
+    } else {
+        const float4 e = __ldg(&kTanhTable[k]);                               // {T hi, T lo, 1 - T^2, 0}
+        th = e.x; tl = e.y; c = e.z;
+    }
     const float d = fmaf(-kf, 0.0625f, ac);                                  // exact, |d| <= 1/32
     const float d2 = d * d;
     const float td = fmaf(d * d2, fmaf(0.13333333f, d2, -0.33333334f), d);   // tanh(d)
-    const float corr = (e.z * td) * rcp_fast(fmaf(e.x, td, 1.0f));
-    const float tb = e.x + (e.y + corr);
+    const float corr = (c * td) * rcp_fast(fmaf(th, td, 1.0f));
+    const float tb = th + (tl + corr);
     const float t = copysignf(ax < 0.34375f ? ts : tb, x);
     return x != x ? x : t;
 }
+ND_D float tanh_accurate(float x) { return tanh_core<false>(x); }
 // exp for float with error close to half an ulp (the host libm's expf is nearly correctly
 // rounded, the CUDA library's is within 2 ulp): same range reduction and (hi, lo) bookkeeping as
 // tanh_accurate, with the scaling by 2^n split in two so that subnormal results round once more.
@@ -164,7 +187,14 @@ ND_UNARY(Sign, 0, return C((x > C(0)) - (x < C(0)));)
 ND_UNARY(Sin, 0, return sin(x);)
 ND_UNARY(SoftPlus, 0, return log(C(1) + expv(x));)
 ND_UNARY(Sqrt, 0, return sqrt(x);)
-ND_UNARY(Tanh, 0, return tanhv(x);)
+// Tanh keeps its table in shared memory: kernels that apply it call prepare() once per CTA (all threads).
+struct Tanh {
+    static constexpr int kParams = 0;
+    static constexpr bool kPrepare = true;
+    ND_D static void prepare() { tanh_table_to_shared(); }
+    template <class C> ND_D static C f(C x, const C *) { return tanh(x); }
+};
+template <> ND_D float Tanh::f<float>(float x, const float *) { return tanh_core<true>(x); }
 ND_UNARY(ACos, 0, return acos(x);)
 ND_UNARY(ASin, 0, return asin(x);)
 ND_UNARY(ATan, 0, return atan(x);)
