@@ -46,6 +46,7 @@ unsigned long long nd4jb200_launch_count(void);
  * launches kernels with programmatic stream serialisation so that a kernel's launch overlaps the
  * tail of the previous kernel on the stream, 0 launches them plainly; key 4: largest thread-block cluster
  * (1, 2, 4 or 8, default 4) the across-TAD reduction uses to merge segments in distributed shared memory.
+ * key 5: CTAs per SM the along-TAD reduction launches at most (default 16; 8 for half precision).
  * Results do not
  * depend on these values beyond the summation order of floating-point reductions. */
 int nd4jb200_set_tuning(int key, long long value);

@@ -148,7 +148,9 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) a.numTads));
         const LL totalSegs = a.numTads * a.splits;
         LL blocks = ceil_div(totalSegs, kBlock / a.group);
-        const LL cap = (LL) kNumSMs * 64;
+        // the grid is capped so that CTAs loop over several TADs instead of being launched once per handful of
+        // TADs (measured: IMax 0.91 -> 0.95 at 16 per SM; half-precision reduce3 0.70 -> 0.75 at 8 per SM)
+        const LL cap = (LL) kNumSMs * (sizeof(T) == 2 && g_tuning[kTuneRowCtasPerSm] > 8 ? 8 : g_tuning[kTuneRowCtasPerSm]);
         if (blocks > cap) blocks = cap;
         launch_kernel(k_reduce_tads<T, P>, dim3((unsigned) blocks), dim3(kBlock), stream, a);
     }

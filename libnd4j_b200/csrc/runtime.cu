@@ -7,7 +7,7 @@
 namespace nd4jb200 {
 
 std::atomic<unsigned long long> g_launches{0};
-long long g_tuning[kTuneCount] = {3, 1024, 32, 1, 4};
+long long g_tuning[kTuneCount] = {3, 1024, 32, 1, 4, 16};
 
 Status cuda_fail(cudaError_t e, const char *where) {
     std::ostringstream os;

@@ -33,7 +33,7 @@ extern std::atomic<unsigned long long> g_launches;
 inline void count_launch(int n = 1) { g_launches.fetch_add((unsigned long long) n, std::memory_order_relaxed); }
 
 // Launch heuristics that may be overridden at run time (nd4jb200_set_tuning); defaults in runtime.cu.
-enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneMaxCluster = 4, kTuneCount = 5 };
+enum Tuning { kTuneColCtasPerSm = 0, kTuneRowThreadsPerSm = 1, kTuneMaxInKernelMerge = 2, kTuneOverlapLaunch = 3, kTuneMaxCluster = 4, kTuneRowCtasPerSm = 5, kTuneCount = 6 };
 extern long long g_tuning[kTuneCount];
 
 // Every kernel of the library starts with grid_dependency_sync() (device_utils.cuh): it lets the
