@@ -12,7 +12,7 @@ using namespace fn;
 template <class Op, class C> struct Reduce {
     struct State { C v; };
     static constexpr int kInputs = 1;
-    static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = Op::kParams;
     ND_D static void init(State &s) { s.v = Op::template identity<C>(); }
     ND_D static void accum(State &s, C x, C, LL, const C *p) { s.v = Op::template combine<C>(s.v, Op::template map<C>(x, p)); }
@@ -30,7 +30,7 @@ template <class Op, class C> struct Reduce {
 template <class C> struct LogSumExp {
     struct State { C m; C s; };
     static constexpr int kInputs = 1;
-    static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 0;
     ND_D static void init(State &s) { s.m = -ND_INF(C); s.s = C(0); }
     ND_D static void accum(State &s, C x, C, LL, const C *) {
@@ -58,7 +58,7 @@ template <class C> struct LogSumExp {
 template <int kind, class C> struct Reduce3 {
     struct State { C acc; C e0; C e1; };
     static constexpr int kInputs = 2;
-    static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = kind == 4 ? 1 : 0;   // EqualsWithEps: p[0] = eps
     // the cosine kinds convert and multiply 16 half values per pack pair: 80 registers instead of 64
     static constexpr int kHalfRowCtas = (kind == 2 || kind == 5 || kind == 6) ? 3 : 4;
@@ -100,7 +100,7 @@ template <int kind, class C> struct Reduce3 {
 template <int kind, class C> struct IndexExtreme {
     struct State { C v; int pad; LL i; };
     static constexpr int kInputs = 1;
-    static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 0;
     ND_D static void init(State &s) {
         s.v = kind == 0 ? C(-ND_MAX_FLOAT) : (kind == 2 ? C(ND_MIN_FLOAT) : C(ND_MAX_FLOAT));
@@ -154,7 +154,7 @@ template <int kind, class C> struct IndexExtreme {
 template <int kind, class C> struct IndexMatch {
     struct State { LL i; };
     static constexpr int kInputs = 1;
-    static constexpr int kColBytes = 16;   // bytes one lane loads per row in the across-TAD kernel
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 3;
     ND_D static void init(State &s) { s.i = -1; }
     ND_D static void take(State &s, LL j) {
@@ -184,7 +184,7 @@ template <int kind, class C> struct IndexMatch {
 template <int kind, class C> struct Stats {
     struct State { double n, s1, s2, k; };
     static constexpr int kInputs = 1;
-    static constexpr int kColBytes = 8;    // four double words of state per TAD: fewer TADs per lane
+    static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 0;
     ND_D static void init(State &s) { s.n = 0; s.s1 = 0; s.s2 = 0; s.k = 0; }
     ND_D static void accum(State &s, C x, C, LL, const C *) {

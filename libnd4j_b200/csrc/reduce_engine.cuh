@@ -274,9 +274,13 @@ __global__ void __launch_bounds__(kBlock, RowBudget<T, P>::v) k_reduce_tads(cons
 // per row. R rows per operand are in flight per thread.
 constexpr int kColRows = 8;
 
+// bytes one lane loads per row: the policy's kColBytes, or its kHalfColBytes for half precision when it names one
+template <class T, class P, class = void> struct ColBytes { static constexpr int v = P::kColBytes; };
+template <class P> struct ColBytes<__half, P, decltype((void) P::kHalfColBytes)> { static constexpr int v = P::kHalfColBytes; };
+
 // rows in flight per thread: 128 bytes over all operands, at most 8 rows
 template <class T, class P> struct ColUnroll {
-    static constexpr int kLane = P::kColBytes < (int) sizeof(T) ? (int) sizeof(T) : P::kColBytes;
+    static constexpr int kLane = ColBytes<T, P>::v < (int) sizeof(T) ? (int) sizeof(T) : ColBytes<T, P>::v;
     static constexpr int kFull = 128 / (kLane * P::kInputs);
     static constexpr int v = kFull > 8 ? 8 : kFull;
 };

@@ -84,7 +84,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         a.yOuterHi = yo; a.yOuterHi.rank = yo.rank - 1;
         const LL hiCount = a.numTads / a.colLo;
         // vector loads across neighbouring TADs need every TAD row to start on a vector boundary
-        constexpr int W = P::kColBytes / (int) sizeof(T) > 0 ? P::kColBytes / (int) sizeof(T) : 1;
+        constexpr int W = ColBytes<T, P>::v / (int) sizeof(T) > 0 ? ColBytes<T, P>::v / (int) sizeof(T) : 1;
         constexpr size_t WB = (size_t) W * sizeof(T);
         bool vec = W > 1 && a.colLo % W == 0 && reinterpret_cast<uintptr_t>(a.x) % WB == 0 && a.colStrideX % W == 0 &&
                    view_strides_multiple_of(a.xOuterHi, W);
