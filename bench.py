@@ -396,7 +396,25 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
     ti_, zi_ = calls.longs(tinfo_), calls.longs(zinfo_)
     record("pull_rows_f32_32768_of_65536x1024", 2 * 32768 * 1024 * 4, 32768 * 1024,
            lambda: calls.check(lib.nd4jb200_pull_rows(st, 0, P(src_), P(out_), 32768, P(pick_), ti_, P(toffs_d), zi_, P(zoffs_d))))
-    del src_, out_
+    # shuffle: the 32768 row pairs of [65536,1024] change places (every element read and written once); tear: the
+    # 65536 rows go to 65536 separate arrays. Both upload an index / pointer list per call, so they are timed as
+    # plain back-to-back calls, not as a graph.
+    half_ = np.full(65536, -1, np.int32)
+    half_[:32768] = 32768 + np.random.default_rng(0).permutation(32768)
+    xp_ = (ctypes.c_void_p * 1)(src_.data_ptr())
+    xinfo_ = calls.longs(S.shape_info([65536, 1024]))
+    xinfos_ = (ctypes.c_void_p * 1)(ctypes.cast(xinfo_, ctypes.c_void_p).value)
+    tinfos_ = (ctypes.c_void_p * 1)(ctypes.cast(ti_, ctypes.c_void_p).value)
+    offp_ = (ctypes.c_void_p * 1)(toffs_d.data_ptr())
+    map_ = calls.ints(half_)
+    record("shuffle_f32_65536x1024", 2 * 65536 * 1024 * 4, 65536 * 1024,
+           lambda: calls.check(lib.nd4jb200_shuffle(st, 0, 1, xp_, xinfos_, map_, tinfos_, offp_)), graph=False)
+    pieces_ = torch.empty(65536, 1024, device=dev)
+    tp_ = (ctypes.c_void_p * 65536)(*[pieces_.data_ptr() + 4096 * r_ for r_ in range(65536)])
+    pinfo_ = calls.longs(S.shape_info([1, 1024]))
+    record("tear_f32_65536x1024", 2 * 65536 * 1024 * 4, 65536 * 1024,
+           lambda: calls.check(lib.nd4jb200_tear(st, 0, P(src_), xinfo_, tp_, pinfo_, ti_, P(toffs_d))), graph=False)
+    del src_, out_, pieces_
     blocks_ = [torch.randn(4096, 4096, device=dev, generator=g) for _ in range(4)]
     cat_ = torch.empty(16384, 4096, device=dev)
     ptrs_ = (ctypes.c_void_p * 4)(*[b_.data_ptr() for b_ in blocks_])

@@ -73,6 +73,12 @@ struct float16 {
     void pullRows##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, T *z, Nd4jLong *zShapeInfo,            \
                      Nd4jLong n, Nd4jLong *indexes, Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets,                   \
                      Nd4jLong *zTadShapeInfo, Nd4jLong *zTadOffsets);                                               \
+    /* nd4jb200_tear / nd4jb200_shuffle (NativeOps.h:2076-2129, 2876-2899); pointer arrays are host arrays */       \
+    void tear##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, Nd4jPointer *targets,                      \
+                 Nd4jLong *zShapeInfo, Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets);                               \
+    void shuffle##S(Nd4jPointer *extras, Nd4jPointer *dx, Nd4jPointer *xShapeInfo, Nd4jPointer *dz,                 \
+                    Nd4jPointer *zShapeInfo, int N, int *shuffleMap, Nd4jPointer *tadShapeInfo,                     \
+                    Nd4jPointer *tadOffsets);                                                                       \
     void average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length, bool propagate);           \
     void accumulate##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length);                        \
     /* nd4jb200_exec_scalar_along_dimension (NativeOps.h:1160-1214) */                                              \

@@ -208,6 +208,17 @@ int nd4jb200_concat(void *stream, int dtype, int dimension, int numArrays, const
 int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong n, const Nd4jLong *indexes,
                        const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets, const Nd4jLong *zTadShapeInfo,
                        const Nd4jLong *zTadOffsets);
+/* NativeOps::tear{Float,Double,Half}: TAD k of x is copied into the array targets[k], all of shape zShapeInfo
+ * (blas/NativeOps.h:2876-2899; blas/cpu/NativeOps.cpp:2119-2162). `targets` is a host array of device
+ * pointers, `tadOffsets` a device array. */
+int nd4jb200_tear(void *stream, int dtype, const void *x, const Nd4jLong *xShapeInfo, void *const *targets,
+                  const Nd4jLong *zShapeInfo, const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets);
+/* NativeOps::shuffle{Float,Double}: in every array x[f], for r = 0, 1, ... in this order, TAD r changes places
+ * with TAD shuffleMap[r] unless shuffleMap[r] < 0 (blas/NativeOps.h:2076-2129; blas/cpu/NativeOps.cpp:2266-2326;
+ * the reference's result arrays are not used by it and are not part of this call). `x`, `xShapeInfo`,
+ * `tadShapeInfo`, `tadOffsets` and `shuffleMap` are host arrays; tadOffsets[f] is a device array. */
+int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, const Nd4jLong *const *xShapeInfo,
+                     const int *shuffleMap, const Nd4jLong *const *tadShapeInfo, const Nd4jLong *const *tadOffsets);
 /* NativeOps::convertTypes among ND4J_FLOAT16 (3), ND4J_FLOAT32 (6) and ND4J_DOUBLE (7): z[i] = (D)(float) x[i]
  * (blas/NativeOps.h:2144; include/loops/type_conversions.h:592-610). Other encodings: ND4JB200_EUNSUPPORTED. */
 int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z);

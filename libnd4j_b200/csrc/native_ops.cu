@@ -60,6 +60,14 @@ const int *host_dims(const int *dimension, int n) {
     return v.data();
 }
 
+// A host copy the caller owns: calls that take many descriptors (concat, shuffle) would outrun the ring.
+std::vector<Nd4jLong> owned_info(const void *arg) {
+    const Nd4jLong *h = host_info(nullptr, -1, static_cast<const Nd4jLong *>(arg));
+    if (!h) return std::vector<Nd4jLong>();
+    const Nd4jLong rank = h[0] < 0 || h[0] > 32 ? 0 : h[0];
+    return std::vector<Nd4jLong>(h, h + 2 * rank + 4);
+}
+
 template <class T> struct TypeCode;
 template <> struct TypeCode<float> { static constexpr int v = ND4JB200_FLOAT; };
 template <> struct TypeCode<double> { static constexpr int v = ND4JB200_DOUBLE; };
@@ -166,9 +174,12 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     void NativeOps::concat##S(Nd4jPointer *extraPointers, int dimension, int numArrays, Nd4jPointer *data,            \
                               Nd4jPointer *inputShapeInfo, T *result, Nd4jLong *resultShapeInfo, Nd4jPointer *,       \
                               Nd4jPointer *) {                                                                        \
-        std::vector<const Nd4jLong *> infos(numArrays > 0 ? numArrays : 0);                                           \
-        for (int k = 0; k < numArrays; k++)                                                                            \
-            infos[k] = host_info(nullptr, -1, static_cast<const Nd4jLong *>(inputShapeInfo[k]));                       \
+        std::vector<std::vector<Nd4jLong> > keep(numArrays > 0 ? numArrays : 0);                                      \
+        std::vector<const Nd4jLong *> infos(keep.size());                                                              \
+        for (size_t k = 0; k < keep.size(); k++) {                                                                     \
+            keep[k] = owned_info(inputShapeInfo[k]);                                                                   \
+            infos[k] = keep[k].empty() ? nullptr : keep[k].data();                                                     \
+        }                                                                                                              \
         check(nd4jb200_concat(STREAM, TypeCode<T>::v, dimension, numArrays, data, infos.data(), result,               \
                               host_info(nullptr, -1, resultShapeInfo)), "concat" #S);                                  \
     }                                                                                                                  \
@@ -177,6 +188,28 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
                                 Nd4jLong *zTadShapeInfo, Nd4jLong *zTadOffsets) {                                     \
         check(nd4jb200_pull_rows(STREAM, TypeCode<T>::v, x, z, n, indexes, host_info(nullptr, -1, tadShapeInfo),      \
                                  tadOffsets, host_info(nullptr, -1, zTadShapeInfo), zTadOffsets), "pullRows" #S);      \
+    }                                                                                                                  \
+    void NativeOps::tear##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, Nd4jPointer *targets,             \
+                            Nd4jLong *zShapeInfo, Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets) {                     \
+        const Nd4jLong *xi = host_info(nullptr, -1, xShapeInfo);                                                      \
+        const Nd4jLong *zi = host_info(nullptr, -1, zShapeInfo);                                                      \
+        check(nd4jb200_tear(STREAM, TypeCode<T>::v, x, xi, targets, zi, host_info(nullptr, -1, tadShapeInfo),         \
+                            tadOffsets), "tear" #S);                                                                   \
+    }                                                                                                                  \
+    void NativeOps::shuffle##S(Nd4jPointer *extras, Nd4jPointer *dx, Nd4jPointer *xShapeInfo, Nd4jPointer *,          \
+                               Nd4jPointer *, int N, int *shuffleMap, Nd4jPointer *tadShapeInfo,                      \
+                               Nd4jPointer *tadOffsets) {                                                             \
+        std::vector<std::vector<Nd4jLong> > keepX(N > 0 ? N : 0), keepT(keepX.size());                                \
+        std::vector<const Nd4jLong *> infos(keepX.size()), tads(keepX.size()), offs(keepX.size());                     \
+        for (size_t k = 0; k < keepX.size(); k++) {                                                                    \
+            keepX[k] = owned_info(xShapeInfo[k]);                                                                      \
+            keepT[k] = owned_info(tadShapeInfo[k]);                                                                    \
+            infos[k] = keepX[k].empty() ? nullptr : keepX[k].data();                                                   \
+            tads[k] = keepT[k].empty() ? nullptr : keepT[k].data();                                                    \
+            offs[k] = static_cast<const Nd4jLong *>(tadOffsets[k]);                                                    \
+        }                                                                                                              \
+        check(nd4jb200_shuffle(stream_of(extras), TypeCode<T>::v, N, dx, infos.data(), shuffleMap, tads.data(),       \
+                               offs.data()), "shuffle" #S);                                                            \
     }                                                                                                                  \
     void NativeOps::average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length,                   \
                                bool propagate) {                                                                      \

@@ -24,7 +24,6 @@ struct ReduceCall {
 // reductions); with many segments of many TADs only a few CTAs would do all the merging, so those
 // cases (and calls that need more counters than the region holds) leave the partials to the separate,
 // fully parallel finalize launch.
-constexpr size_t kCounterSlots = 65536;
 template <class State>
 Status split_scratch(cudaStream_t stream, ReduceArgs &a, size_t counters) {
     const size_t counterBytes = kCounterSlots * sizeof(unsigned);

@@ -26,6 +26,10 @@ Status cuda_fail(cudaError_t e, const char *where);
 // different streams never share it. The block only ever grows; growing synchronises the device.
 // `hostSlot`, when requested, is a 64-byte pinned buffer used to bring scalar results back.
 Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot);
+// Layout of a workspace block: [256-byte result slot][kCounterSlots arrival counters, always left zero]
+// [scratch: partial states, index lists]. Only the part from kWorkspaceScratch on is free for a call to use.
+constexpr size_t kCounterSlots = 65536;
+constexpr size_t kWorkspaceScratch = 256 + kCounterSlots * sizeof(unsigned);
 void release_workspaces();
 
 // Counts kernel launches issued by this library since load (read by the benchmark).

@@ -17,6 +17,7 @@
 #include "device_utils.cuh"
 #include "runtime.h"
 #include <sstream>
+#include <vector>
 
 namespace nd4jb200 {
 namespace {
@@ -95,43 +96,122 @@ inline Status check_dtype(int dtype) {
 }
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
 
-// ---- pullRows ----------------------------------------------------------------------------------
+// ---- pullRows / tear ----------------------------------------------------------------------------
+// A unit of work is one chunk of one TAD; a warp takes units grid-stride. TADs of up to kPullChunk
+// bytes are one unit (a warp per TAD); longer ones are cut so that a few long TADs still fill the device.
+constexpr LL kPullChunk = 16384;
 struct PullArgs {
     const void *x;
     void *z;
-    LL n, tadLen;
-    const LL *indexes, *xOffsets, *zOffsets;   // device arrays
+    void *const *targets;                      // tear: TAD k goes to the array targets[k] (device array of pointers)
+    LL n, tadLen, chunkLen, chunks;            // chunks per TAD, chunkLen elements each (a multiple of 16 bytes)
+    const LL *indexes, *xOffsets, *zOffsets;   // device arrays; indexes == nullptr: TAD k itself
     View xInner, zInner;
-    int dense;        // unit-stride TADs whose bases and length keep 16-byte alignment
+    int dense;        // unit-stride TADs whose length keeps 16-byte alignment (bases are checked per TAD)
 };
 
 template <int BYTES>
 __global__ void __launch_bounds__(kCopyBlock) k_pull_rows(const PullArgs a) {
     grid_dependency_sync();
     typedef typename Raw<BYTES>::T E;
-    const E *ax = static_cast<const E *>(a.x);
-    E *az = static_cast<E *>(a.z);
-    // one warp per pulled TAD (grid-stride), four 16-byte packs in flight per lane
     const int lane = threadIdx.x & 31;
-    const LL warps = (LL) gridDim.x * (kCopyBlock / 32);
-    for (LL k = (LL) blockIdx.x * (kCopyBlock / 32) + (threadIdx.x >> 5); k < a.n; k += warps) {
-        const LL xo = __ldg(a.xOffsets + __ldg(a.indexes + k)), zo = __ldg(a.zOffsets + k);
-        const bool vec = a.dense && ((xo * BYTES) & 15) == 0 && ((zo * BYTES) & 15) == 0;
+    const LL warps = (LL) gridDim.x * (kCopyBlock / 32), units = a.n * a.chunks;
+    for (LL u = (LL) blockIdx.x * (kCopyBlock / 32) + (threadIdx.x >> 5); u < units; u += warps) {
+        const LL k = u / a.chunks, first = (u - k * a.chunks) * a.chunkLen;
+        const LL len = min(a.chunkLen, a.tadLen - first);
+        const E *src = static_cast<const E *>(a.x) + __ldg(a.xOffsets + (a.indexes ? __ldg(a.indexes + k) : k));
+        E *dst = a.targets ? static_cast<E *>(a.targets[k]) : static_cast<E *>(a.z) + __ldg(a.zOffsets + k);
+        const bool vec = a.dense && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
         if (vec) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(ax + xo);
-            uint4 *dst = reinterpret_cast<uint4 *>(az + zo);
-            const LL packs = a.tadLen * BYTES / 16;
+            // four 16-byte packs in flight per lane
+            const uint4 *s4 = reinterpret_cast<const uint4 *>(src + first);
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst + first);
+            const LL packs = len * BYTES / 16;
             LL i = lane;
             for (; i + 96 < packs; i += 128) {
-                const uint4 p0 = __ldg(src + i), p1 = __ldg(src + i + 32), p2 = __ldg(src + i + 64), p3 = __ldg(src + i + 96);
-                dst[i] = p0; dst[i + 32] = p1; dst[i + 64] = p2; dst[i + 96] = p3;
+                const uint4 p0 = __ldg(s4 + i), p1 = __ldg(s4 + i + 32), p2 = __ldg(s4 + i + 64), p3 = __ldg(s4 + i + 96);
+                d4[i] = p0; d4[i + 32] = p1; d4[i + 64] = p2; d4[i + 96] = p3;
             }
-            for (; i < packs; i += 32) dst[i] = __ldg(src + i);
+            for (; i < packs; i += 32) d4[i] = __ldg(s4 + i);
         } else {
-            for (LL i = lane; i < a.tadLen; i += 32)
-                az[zo + view_offset(a.zInner, i)] = ax[xo + view_offset(a.xInner, i)];
+            for (LL i = first + lane; i < first + len; i += 32)
+                dst[view_offset(a.zInner, i)] = src[view_offset(a.xInner, i)];
         }
     }
+}
+
+Status launch_pull(int bytes, PullArgs a, cudaStream_t st) {
+    const LL perChunk = kPullChunk / bytes;
+    a.chunkLen = a.tadLen < perChunk ? a.tadLen : perChunk;
+    a.chunks = ceil_div(a.tadLen, a.chunkLen);
+    LL blocks = ceil_div(a.n * a.chunks, kCopyBlock / 32);
+    const LL cap = (LL) kNumSMs * 16;
+    if (blocks > cap) blocks = cap;
+    if (bytes == 2) launch_kernel(k_pull_rows<2>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else if (bytes == 4) launch_kernel(k_pull_rows<4>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    else launch_kernel(k_pull_rows<8>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+// ---- shuffle -------------------------------------------------------------------------------------
+// TAD pairs[p].x and TAD pairs[p].y of one array change places; the pairs of one launch are disjoint.
+struct SwapArgs {
+    void *x;
+    const LL *offsets;        // device array of TAD offsets
+    const int2 *pairs;        // device array
+    LL n, tadLen, chunkLen, chunks;
+    View inner;
+    int dense;
+};
+
+template <int BYTES>
+__global__ void __launch_bounds__(kCopyBlock) k_swap_tads(const SwapArgs a) {
+    grid_dependency_sync();
+    typedef typename Raw<BYTES>::T E;
+    const int lane = threadIdx.x & 31;
+    const LL warps = (LL) gridDim.x * (kCopyBlock / 32), units = a.n * a.chunks;
+    for (LL u = (LL) blockIdx.x * (kCopyBlock / 32) + (threadIdx.x >> 5); u < units; u += warps) {
+        const LL k = u / a.chunks, first = (u - k * a.chunks) * a.chunkLen;
+        const LL len = min(a.chunkLen, a.tadLen - first);
+        const int2 pr = a.pairs[k];
+        E *p = static_cast<E *>(a.x) + __ldg(a.offsets + pr.x);
+        E *q = static_cast<E *>(a.x) + __ldg(a.offsets + pr.y);
+        const bool vec = a.dense && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+        if (vec) {
+            uint4 *p4 = reinterpret_cast<uint4 *>(p + first), *q4 = reinterpret_cast<uint4 *>(q + first);
+            const LL packs = len * BYTES / 16;
+            LL i = lane;
+            for (; i + 32 < packs; i += 64) {
+                const uint4 a0 = p4[i], a1 = p4[i + 32], b0 = q4[i], b1 = q4[i + 32];
+                p4[i] = b0; p4[i + 32] = b1; q4[i] = a0; q4[i + 32] = a1;
+            }
+            for (; i < packs; i += 32) { const uint4 a0 = p4[i], b0 = q4[i]; p4[i] = b0; q4[i] = a0; }
+        } else {
+            for (LL i = first + lane; i < first + len; i += 32) {
+                const LL o = view_offset(a.inner, i);
+                const E t = p[o]; p[o] = q[o]; q[o] = t;
+            }
+        }
+    }
+}
+
+// The reference applies the swaps one after another (r = 0, 1, ...; blas/cpu/NativeOps.cpp:2289-2324), so a
+// map whose swaps share TADs depends on that order. The swaps are sorted into rounds: a swap goes one round
+// after the latest earlier swap that touches either of its TADs. The swaps of a round are disjoint and run
+// as one launch; the usual map (disjoint pairs) is a single round.
+Status shuffle_rounds(const int *map, LL numTads, std::vector<std::vector<int2> > *rounds) {
+    std::vector<int> last((size_t) numTads, 0);
+    for (LL r = 0; r < numTads; r++) {
+        const int m = map[r];
+        if (m < 0 || m == r) continue;
+        if (m >= numTads) return bad_arg("shuffle: the map names a TAD past the last one");
+        const int round = (last[r] > last[m] ? last[r] : last[m]) + 1;
+        last[r] = last[m] = round;
+        if ((size_t) round > rounds->size()) rounds->resize(round);
+        (*rounds)[round - 1].push_back(make_int2((int) r, m));
+    }
+    return kOk;
 }
 
 // ---- average / accumulate -----------------------------------------------------------------------
@@ -352,20 +432,101 @@ int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong
     if (xt.length != zt.length) return bad_arg("pullRows: source and target TADs differ in length");
     if (n == 0 || xt.length == 0) return kOk;
     PullArgs a;
-    a.x = x; a.z = z; a.n = n; a.tadLen = xt.length;
+    a.x = x; a.z = z; a.targets = nullptr; a.n = n; a.tadLen = xt.length;
     a.indexes = indexes; a.xOffsets = tadOffsets; a.zOffsets = zTadOffsets;
     ND_TRY(linear_view(xt, &a.xInner));
     ND_TRY(linear_view(zt, &a.zInner));
     const int bytes = dtype_bytes(dtype);
-    a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0 && aligned16(x) && aligned16(z);
-    LL blocks = ceil_div(n, kCopyBlock / 32);
-    const LL cap = (LL) kNumSMs * 16;
-    if (blocks > cap) blocks = cap;
+    a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0;
+    return launch_pull(bytes, a, as_stream(stream));
+}
+
+int nd4jb200_tear(void *stream, int dtype, const void *x, const Nd4jLong *xShapeInfo, void *const *targets,
+                  const Nd4jLong *zShapeInfo, const Nd4jLong *tadShapeInfo, const Nd4jLong *tadOffsets) {
+    ND_TRY(check_dtype(dtype));
+    if (!x || !targets || !tadOffsets) return bad_arg("tear: null argument");
+    ShapeDesc xd, zd, xt;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    ND_TRY(parse_shape(tadShapeInfo, "tadShapeInfo", &xt));
+    if (xt.length != zd.length) return bad_arg("tear: the targets and the TADs differ in length");
+    if (xt.length == 0 || xd.length == 0) return kOk;
+    PullArgs a;
+    a.x = x; a.z = nullptr; a.n = xd.length / xt.length; a.tadLen = xt.length;
+    // `targets` is a host array like the other pointer arrays of this boundary: the kernel reads a copy
     const cudaStream_t st = as_stream(stream);
-    if (bytes == 2) launch_kernel(k_pull_rows<2>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
-    else if (bytes == 4) launch_kernel(k_pull_rows<4>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
-    else launch_kernel(k_pull_rows<8>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
-    ND_CUDA(cudaGetLastError());
+    void *ws = nullptr;
+    ND_TRY(workspace(st, kWorkspaceScratch + sizeof(void *) * (size_t) a.n, &ws, nullptr));
+    void **devTargets = reinterpret_cast<void **>(static_cast<char *>(ws) + kWorkspaceScratch);
+    for (LL k = 0; k < a.n; k++)
+        if (!targets[k]) return bad_arg("tear: null target array");
+    ND_CUDA(cudaMemcpyAsync(devTargets, targets, sizeof(void *) * (size_t) a.n, cudaMemcpyHostToDevice, st));
+    a.targets = devTargets;
+    a.indexes = nullptr; a.xOffsets = tadOffsets; a.zOffsets = nullptr;
+    if (zd.ews > 0 && xt.ews > 0) {
+        LL len[1] = {xt.length}, sx[1] = {xt.ews}, sz[1] = {zd.ews};
+        ND_TRY(collapse_view(1, len, sx, &a.xInner));
+        ND_TRY(collapse_view(1, len, sz, &a.zInner));
+    } else {
+        // element j of a TAD in f-order goes to element j of its target in f-order (blas/cpu/NativeOps.cpp:2147-2158)
+        ND_TRY(forder_traversal(xt, &a.xInner));
+        ND_TRY(forder_traversal(zd, &a.zInner));
+    }
+    const int bytes = dtype_bytes(dtype);
+    a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0;
+    return launch_pull(bytes, a, st);
+}
+
+int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, const Nd4jLong *const *xShapeInfo,
+                     const int *shuffleMap, const Nd4jLong *const *tadShapeInfo, const Nd4jLong *const *tadOffsets) {
+    ND_TRY(check_dtype(dtype));
+    if (!x || !xShapeInfo || !shuffleMap || !tadShapeInfo || !tadOffsets) return bad_arg("shuffle: null argument");
+    if (numArrays < 0) return bad_arg("shuffle: negative array count");
+    const int bytes = dtype_bytes(dtype);
+    const cudaStream_t st = as_stream(stream);
+    size_t used = 0;          // bytes of pair lists already placed in the workspace by this call
+    for (int f = 0; f < numArrays; f++) {
+        if (!x[f] || !tadOffsets[f]) return bad_arg("shuffle: null array or TAD offsets");
+        ShapeDesc xd, xt;
+        ND_TRY(parse_shape(xShapeInfo[f], "xShapeInfo", &xd));
+        ND_TRY(parse_shape(tadShapeInfo[f], "tadShapeInfo", &xt));
+        if (xt.length == 0) continue;
+        const LL numTads = xd.length / xt.length;
+        if (numTads > 0x7fffffffLL) return bad_arg("shuffle: more TADs than an int map can name");
+        std::vector<std::vector<int2> > rounds;
+        ND_TRY(shuffle_rounds(shuffleMap, numTads, &rounds));
+        size_t total = 0;
+        for (size_t r = 0; r < rounds.size(); r++) total += rounds[r].size();
+        if (total == 0) continue;
+        std::vector<int2> flat;
+        flat.reserve(total);
+        for (size_t r = 0; r < rounds.size(); r++) flat.insert(flat.end(), rounds[r].begin(), rounds[r].end());
+        // every array's lists get their own part of the workspace: an earlier array's launches may still read theirs
+        void *ws = nullptr;
+        ND_TRY(workspace(st, kWorkspaceScratch + used + total * sizeof(int2), &ws, nullptr));
+        int2 *dev = reinterpret_cast<int2 *>(static_cast<char *>(ws) + kWorkspaceScratch + used);
+        ND_CUDA(cudaMemcpyAsync(dev, flat.data(), total * sizeof(int2), cudaMemcpyHostToDevice, st));
+        used += total * sizeof(int2);
+        SwapArgs a;
+        a.x = x[f]; a.offsets = tadOffsets[f]; a.tadLen = xt.length;
+        ND_TRY(linear_view(xt, &a.inner));
+        a.dense = unit_run(a.inner) && (xt.length * bytes) % 16 == 0;
+        const LL perChunk = kPullChunk / bytes;
+        a.chunkLen = a.tadLen < perChunk ? a.tadLen : perChunk;
+        a.chunks = ceil_div(a.tadLen, a.chunkLen);
+        size_t at = 0;
+        for (size_t r = 0; r < rounds.size(); r++) {
+            a.pairs = dev + at; a.n = (LL) rounds[r].size();
+            at += rounds[r].size();
+            LL blocks = ceil_div(a.n * a.chunks, kCopyBlock / 32);
+            const LL cap = (LL) kNumSMs * 16;
+            if (blocks > cap) blocks = cap;
+            if (bytes == 2) launch_kernel(k_swap_tads<2>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+            else if (bytes == 4) launch_kernel(k_swap_tads<4>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+            else launch_kernel(k_swap_tads<8>, dim3((unsigned) blocks), dim3(kCopyBlock), st, a);
+            ND_CUDA(cudaGetLastError());
+        }
+    }
     return kOk;
 }
 

@@ -77,6 +77,8 @@ def load_library(path=None):
         "nd4jb200_flatten": (i, [vp, i, ll, ctypes.c_char, vp, llp, vp, llp]),
         "nd4jb200_concat": (i, [vp, i, i, i, vp, vp, vp, llp]),
         "nd4jb200_pull_rows": (i, [vp, i, vp, vp, ll, vp, llp, vp, llp, vp]),
+        "nd4jb200_tear": (i, [vp, i, vp, llp, vp, llp, llp, vp]),
+        "nd4jb200_shuffle": (i, [vp, i, i, vp, vp, ip, vp, vp]),
         "nd4jb200_average": (i, [vp, i, vp, vp, i, ll, i]),
         "nd4jb200_accumulate": (i, [vp, i, vp, vp, i, ll]),
         "nd4jb200_set_tuning": (ctypes.c_int, [ctypes.c_int, ctypes.c_longlong]),
@@ -487,6 +489,26 @@ class NativeOps:
         self._check(self.lib.nd4jb200_pull_rows(self._stream(extraPointers), dt, _ptr(x), _ptr(z), n, _ptr(indexes), tsp,
                                                 _ptr(tadOffsets), ztsp, _ptr(zTadOffsets)))
 
+    def _tear(self, dt, extraPointers, x, xShapeInfo, targets, zShapeInfo, tadShapeInfo, tadOffsets):
+        """`targets`: sequence of device arrays, one per TAD of x; `tadOffsets`: device array."""
+        xs, xsp = _longs(xShapeInfo)
+        zs, zsp = _longs(zShapeInfo)
+        ts, tsp = _longs(tadShapeInfo)
+        ptrs = (ctypes.c_void_p * len(targets))(*[_ptr(t).value for t in targets])
+        self._check(self.lib.nd4jb200_tear(self._stream(extraPointers), dt, _ptr(x), xsp, ptrs, zsp, tsp, _ptr(tadOffsets)))
+
+    def _shuffle(self, dt, extras, dx, xShapeInfo, dz, zShapeInfo, N, shuffleMap, tadShapeInfo, tadOffsets):
+        """`dx`, `xShapeInfo`, `tadShapeInfo`, `tadOffsets`: sequences of N entries; `shuffleMap`: host ints.
+        The arrays are shuffled in place; `dz` / `zShapeInfo` are unused, as in the reference."""
+        ptrs = (ctypes.c_void_p * N)(*[_ptr(d).value for d in dx])
+        keepX = [_longs(s) for s in xShapeInfo]
+        keepT = [_longs(s) for s in tadShapeInfo]
+        infos = (ctypes.c_void_p * N)(*[ctypes.cast(k[1], ctypes.c_void_p).value for k in keepX])
+        tads = (ctypes.c_void_p * N)(*[ctypes.cast(k[1], ctypes.c_void_p).value for k in keepT])
+        offs = (ctypes.c_void_p * N)(*[_ptr(o).value for o in tadOffsets])
+        m, mp = _ints(shuffleMap)
+        self._check(self.lib.nd4jb200_shuffle(self._stream(extras), dt, N, ptrs, infos, mp, tads, offs))
+
     def _average(self, dt, extras, dx, dz, n, length, propagate):
         ptrs = (ctypes.c_void_p * n)(*[_ptr(d).value for d in dx])
         self._check(self.lib.nd4jb200_average(self._stream(extras), dt, ptrs, _ptr(dz), n, length, 1 if propagate else 0))
@@ -533,7 +555,7 @@ def _bind(generic, dt):
 for _fam in ("execReduce", "execReduceScalar", "execIndexReduce", "execIndexReduceScalar", "execSummaryStats",
              "execSummaryStatsScalar", "execReduce3", "execReduce3All", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
              "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom", "flatten", "concat", "pullRows",
-             "average", "accumulate"):
+             "tear", "shuffle", "average", "accumulate"):
     for _sfx, _dt in _SUFFIX.items():
         _m = _bind("_" + _fam, _dt)
         _m.__name__ = _fam + _sfx

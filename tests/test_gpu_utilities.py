@@ -150,3 +150,115 @@ def test_convert_types_goes_through_float(ops, src, dst):
     assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
     with pytest.raises(RuntimeError):
         ops.convertTypes(None, 1, dev(x), x.size, CODES[dst], dz)      # ND4J_INT8 is not served
+
+
+def _tad_view(x, lay, ops, dims):
+    """TAD descriptors of a laid-out array, plus a function giving TAD k of the logical array."""
+    tad_info, tad_offsets = ops.tadOnlyShapeInfo(lay.info, dims, len(dims))
+    return tad_info, np.asarray(tad_offsets, dtype=np.int64)
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("kind,dim,zorder", [("c", 1, "c"), ("f", 1, "c"), ("c", 0, "c"), ("cview2", 1, "c"), ("c", 1, "f")])
+def test_tear_rows_and_columns(ops, dt, name, kind, dim, zorder):
+    # TAD k of x lands in its own array (blas/cpu/NativeOps.cpp:2119-2162)
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((12, 40)).astype(dt)
+    lay = Layout(x, kind)
+    tad_info, tad_offsets = _tad_view(x, lay, ops, [dim])
+    pieces = [x[k] if dim == 1 else x[:, k] for k in range(len(tad_offsets))]
+    zshape = [1, pieces[0].size]
+    zinfo = S.shape_info(zshape, zorder)
+    targets = [dev(np.zeros(p.size, dt)) for p in pieces]
+    getattr(ops, "tear" + name)(None, dev(lay.buffer), lay.info, targets, zinfo, tad_info, dev(tad_offsets))
+    for t, p in zip(targets, pieces):
+        np.testing.assert_array_equal(host(t), p)
+
+
+def test_tear_matrices_in_f_order_enumeration(ops):
+    # neither side addressable by one stride: element j of a TAD in f-order goes to element j of the target in f-order
+    rng = np.random.default_rng(22)
+    x = rng.standard_normal((5, 6, 7)).astype(np.float32)
+    lay = Layout(x, "cview2")
+    tad_info, tad_offsets = _tad_view(x, lay, ops, [1, 2])
+    zlay = Layout(np.zeros((6, 7), np.float32), "fview2")
+    targets = [dev(zlay.buffer) for _ in range(5)]
+    ops.tearFloat(None, dev(lay.buffer), lay.info, targets, zlay.info, tad_info, dev(tad_offsets))
+    for k, t in enumerate(targets):
+        np.testing.assert_array_equal(zlay.read(host(t)), x[k])
+
+
+def test_tear_few_long_tads_are_cut_into_chunks(ops):
+    x = np.arange(3 * 100003, dtype=np.float32).reshape(3, 100003)      # odd length: no 16-byte rows
+    y = np.arange(4 * 65536, dtype=np.float64).reshape(4, 65536)
+    for a, name in ((x, "Float"), (y, "Double")):
+        info = S.shape_info(list(a.shape))
+        tad_info, tad_offsets = ops.tadOnlyShapeInfo(info, [1], 1)
+        targets = [dev(np.zeros(a.shape[1], a.dtype)) for _ in range(a.shape[0])]
+        getattr(ops, "tear" + name)(None, dev(a), info, targets, S.shape_info([1, a.shape[1]]), tad_info,
+                                    dev(np.asarray(tad_offsets, dtype=np.int64)))
+        for k, t in enumerate(targets):
+            np.testing.assert_array_equal(host(t), a[k])
+
+
+def _shuffled(x, axis, shuffle_map):
+    """The reference's loop: swaps applied one after another (blas/cpu/NativeOps.cpp:2289-2324)."""
+    out = np.moveaxis(x.copy(), axis, 0)
+    for r in range(out.shape[0]):
+        m = shuffle_map[r]
+        if m < 0:
+            continue
+        tmp = out[r].copy()
+        out[r] = out[m]
+        out[m] = tmp
+    return np.moveaxis(out, 0, axis)
+
+
+def _half_map(n, rng):
+    # the usual map: every TAD of the first half meets one of the second half, nothing else moves
+    m = np.full(n, -1, np.int32)
+    m[:n // 2] = n // 2 + rng.permutation(n // 2)
+    return m
+
+
+MAPS = {
+    "pairs": lambda n, rng: _half_map(n, rng),
+    "chain": lambda n, rng: np.array([r + 1 if r + 1 < n else -1 for r in range(n)], np.int32),
+    "random": lambda n, rng: rng.integers(-1, n, n).astype(np.int32),
+    "identity": lambda n, rng: np.arange(n, dtype=np.int32),
+}
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("which", sorted(MAPS))
+@pytest.mark.parametrize("kind,dim", [("c", 1), ("f", 1), ("c", 0)])
+def test_shuffle_features_and_labels_together(ops, dt, name, which, kind, dim):
+    rng = np.random.default_rng(31)
+    n = 21
+    feats = rng.standard_normal((n, 36) if dim == 1 else (36, n)).astype(dt)
+    labels = rng.standard_normal((n, 5) if dim == 1 else (5, n)).astype(dt)
+    shuffle_map = MAPS[which](n, rng)
+    lays = [Layout(feats, kind), Layout(labels, kind)]
+    bufs = [dev(l.buffer) for l in lays]
+    tads = [ops.tadOnlyShapeInfo(l.info, [dim], 1) for l in lays]
+    getattr(ops, "shuffle" + name)(None, bufs, [l.info for l in lays], None, None, 2, shuffle_map,
+                                   [t[0] for t in tads], [dev(np.asarray(t[1], dtype=np.int64)) for t in tads])
+    axis = 0 if dim == 1 else 1
+    for lay, buf, a in zip(lays, bufs, (feats, labels)):
+        np.testing.assert_array_equal(lay.read(host(buf)), _shuffled(a, axis, shuffle_map))
+
+
+def test_shuffle_long_rows_and_bad_map(ops):
+    rng = np.random.default_rng(32)
+    x = rng.standard_normal((64, 8192)).astype(np.float32)        # 32 KB rows: two chunks each, dense packs
+    info = S.shape_info([64, 8192])
+    tad_info, tad_offsets = ops.tadOnlyShapeInfo(info, [1], 1)
+    offs = dev(np.asarray(tad_offsets, dtype=np.int64))
+    shuffle_map = _half_map(64, rng)
+    dx = dev(x)
+    ops.shuffleFloat(None, [dx], [info], None, None, 1, shuffle_map, [tad_info], [offs])
+    np.testing.assert_array_equal(host(dx), _shuffled(x, 0, shuffle_map))
+    bad = shuffle_map.copy()
+    bad[3] = 64
+    with pytest.raises(RuntimeError):
+        ops.shuffleFloat(None, [dx], [info], None, None, 1, bad, [tad_info], [offs])
