@@ -4,8 +4,9 @@
 // The reference composes them from five to seven passes of the other families -- row max (reduce),
 // subtract (broadcast), Exp (transform), row sum (reduce), divide (broadcast), then Log or y(1-y)
 // -- each a full read and write of the matrix (special_ops.h:1490-1516). Here a row is read once,
-// kept in registers (rows up to 128 elements) or re-read from L1/L2 (a warp per row in two sweeps;
-// a CTA per row in three sweeps when there are only a few very long rows), and written once. The arithmetic per element is the reference's:
+// kept in registers (up to 1024 elements per warp, 8192 per CTA) or, for longer or unaligned rows, re-read
+// from L1/L2 (a warp per row in two sweeps; a CTA per row in three sweeps when there are only a few very
+// long rows), and written once. The arithmetic per element is the reference's:
 //   e = exp(x - max);  y = e / sum(e);  SoftMax: y;  LogSoftMax: log(y);  Derivative: y * (1 - y)
 // Two things differ from the reference's passes: the order of the row sum (a tree instead of its
 // sequential / OpenMP-chunked loop) and the last bits of exp (library exp, multiply by 1/sum), so
@@ -104,6 +105,67 @@ __global__ void __launch_bounds__(kSmBlock, 4) k_softmax_cached(const SoftmaxArg
         for (int k = 0; k < K; k++) {
             const int c = t + G * k;
             if (c < cols) Elem<T>::store(zr + c * a.zCol, softmax_finish<T, KIND, C>(v[k], inv));
+        }
+    }
+}
+
+// The same with 16-byte packs and up to 32 values (16 doubles) per thread: rows of up to 1024 elements per
+// warp (G = 32) or 8192 per CTA (G = 256) are read once, kept in registers, and need one exp per element
+// instead of the two of the sweeping kernels. Needs unit column strides and 16-byte aligned rows.
+template <class C> struct SmRegs { static constexpr int kVals = sizeof(C) == 8 ? 16 : 32; };
+
+template <class T, int KIND, int G>
+__global__ void __launch_bounds__(kSmBlock, 2) k_softmax_regs(const SoftmaxArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    constexpr int V = Elem<T>::kVec;
+    constexpr int NP = SmRegs<C>::kVals / V;
+    const T *ax = static_cast<const T *>(a.x);
+    T *az = static_cast<T *>(a.z);
+    __shared__ C slots[kSmBlock / 32];
+    constexpr int kRowsPerBlock = kSmBlock / G;
+    const int t = threadIdx.x % G;
+    const int packs = (int) (a.cols / V);      // at most G * NP
+    const LL stride = (LL) gridDim.x * kRowsPerBlock;
+    for (LL r = (LL) blockIdx.x * kRowsPerBlock + threadIdx.x / G; r < a.rows; r += stride) {
+        const T *xr = ax + r * a.xRow;
+        T *zr = az + r * a.zRow;
+        C v[NP][V];
+        C mx = -ND_INF(C);
+#pragma unroll
+        for (int j = 0; j < NP; j++) {
+            const int p = t + G * j;
+            if (p < packs) {
+                const Pack<T> pk = load_pack_rw(xr + (LL) p * V);
+#pragma unroll
+                for (int k = 0; k < V; k++) { v[j][k] = Elem<T>::to_c(pk.v[k]); mx = v[j][k] > mx ? v[j][k] : mx; }
+            }
+        }
+        mx = warp_max(mx);
+        if (G > 32) mx = block_combine(mx, slots, true);
+        C sum = C(0);
+#pragma unroll
+        for (int j = 0; j < NP; j++) {
+            if (t + G * j < packs) {
+#pragma unroll
+                for (int k = 0; k < V; k++) {
+                    v[j][k] = Elem<T>::to_c(Elem<T>::from_c(softmax_exp(Elem<T>::to_c(Elem<T>::from_c(v[j][k] - mx)))));
+                    sum += v[j][k];
+                }
+            }
+        }
+        sum = warp_sum(sum);
+        if (G > 32) sum = block_combine(sum, slots, false);
+        const C inv = C(1) / Elem<T>::to_c(Elem<T>::from_c(sum));
+#pragma unroll
+        for (int j = 0; j < NP; j++) {
+            const int p = t + G * j;
+            if (p < packs) {
+                Pack<T> o;
+#pragma unroll
+                for (int k = 0; k < V; k++) o.v[k] = Elem<T>::from_c(softmax_finish<T, KIND, C>(v[j][k], inv));
+                store_pack(zr + (LL) p * V, o);
+            }
         }
     }
 }
@@ -224,8 +286,13 @@ Status run_softmax(const SoftmaxArgs &a, cudaStream_t stream) {
         const dim3 grid((unsigned) blocks), block(kSmBlock);
         const bool vec = a.xCol == 1 && a.zCol == 1 && a.cols % V == 0 && a.xRow % V == 0 && a.zRow % V == 0 &&
                          aligned16(a.x) && aligned16(a.z);
+        constexpr LL kVals = SmRegs<typename Elem<T>::C>::kVals;
         if (a.cols <= 128) launch_kernel(k_softmax_cached<T, KIND, 32, 4>, grid, block, stream, a);
-        else if (vec) launch_kernel(k_softmax_online<T, KIND, true>, grid, block, stream, a);
+        else if (vec && a.cols <= 32 * kVals) launch_kernel(k_softmax_regs<T, KIND, 32>, grid, block, stream, a);
+        else if (vec && a.cols <= kSmBlock * kVals && a.rows >= kNumSMs) {
+            LL ctas = a.rows < cap ? a.rows : cap;
+            launch_kernel(k_softmax_regs<T, KIND, 256>, dim3((unsigned) ctas), block, stream, a);
+        } else if (vec) launch_kernel(k_softmax_online<T, KIND, true>, grid, block, stream, a);
         else launch_kernel(k_softmax_online<T, KIND, false>, grid, block, stream, a);
     } else {
         LL blocks = a.rows;

@@ -391,7 +391,7 @@ def _softmax_truth(op, x):
 
 
 @pytest.mark.parametrize("op", [38, 39, 40])
-@pytest.mark.parametrize("shape", [(64, 10), (300, 1000), (7, 3000), (1, 777), (513, 1)])
+@pytest.mark.parametrize("shape", [(64, 10), (300, 1000), (160, 4096), (150, 2052), (7, 3000), (1, 777), (513, 1)])
 @pytest.mark.parametrize("dt,name,tol", [(np.float32, "Float", 1e-5), (np.float64, "Double", 1e-12), (np.float16, "Half", 1e-2)])
 def test_softmax_family_rows(ops, real_ref, op, shape, dt, name, tol):
     """Fused row softmax against the reference's composite (include/ops/special_ops.h:1484-1940). The
