@@ -219,8 +219,10 @@ int nd4jb200_tear(void *stream, int dtype, const void *x, const Nd4jLong *xShape
  * `tadShapeInfo`, `tadOffsets` and `shuffleMap` are host arrays; tadOffsets[f] is a device array. */
 int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, const Nd4jLong *const *xShapeInfo,
                      const int *shuffleMap, const Nd4jLong *const *tadShapeInfo, const Nd4jLong *const *tadOffsets);
-/* NativeOps::convertTypes among ND4J_FLOAT16 (3), ND4J_FLOAT32 (6) and ND4J_DOUBLE (7): z[i] = (D)(float) x[i]
- * (blas/NativeOps.h:2144; include/loops/type_conversions.h:592-610). Other encodings: ND4JB200_EUNSUPPORTED. */
+/* NativeOps::convertTypes among ND4J_INT8 (1), UINT8 (2), FLOAT16 (3), INT16 (4), FLOAT32 (6), DOUBLE (7) and, as a
+ * result only, UINT16 (5): z[i] = (D)(float) x[i] with the reference's saturating integer wrappers
+ * (blas/NativeOps.h:2144; include/loops/type_conversions.h:592-610, 696-880; include/types/impl/). The pairs its
+ * dispatch leaves out (1->1, 6->6, 7->7) leave z untouched. FLOAT8 (0) and THRESHOLD (8): ND4JB200_EUNSUPPORTED. */
 int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z);
 /* NativeOps::average{Float,Double,Half}: z[i] = sum_k sources[k][i] / n (z == NULL: into sources[0]); with
  * `propagate` the result is also written over every source (blas/NativeOps.h:1996-2025;

@@ -10,7 +10,10 @@
 //   pullRows   TAD number indexes[k] of x is copied onto TAD k of z (blas/cpu/NativeOps.cpp:2045-2104)
 //   average    z[i] = sum_k x_k[i] / n, then (optionally) every x_k = z  (specials.cpp:374-433)
 //   accumulate z[i] += sum_k x_k[i]  (onto what z already holds)          (specials.cpp:343-359)
-//   convertTypes  z[i] = (D)(float) x[i] among float16 / float32 / double  (type_conversions.h:592-610)
+//   convertTypes  z[i] = (D)(float) x[i] among int8 / uint8 / int16 / uint16 / float16 / float32 / double
+//              (type_conversions.h:592-610, 696-880)
+//   tear       TAD k of x is copied into the array targets[k]               (blas/cpu/NativeOps.cpp:2119-2162)
+//   shuffle    TAD r and TAD map[r] of every array change places, r = 0, 1, ... (blas/cpu/NativeOps.cpp:2266-2326)
 //
 // Copies move raw 2-, 4- or 8-byte elements; only average / accumulate look at the values.
 #include "../../include/nd4j_b200.h"
@@ -318,49 +321,104 @@ Status sum_sources(void *stream, int dtype, const void *const *sources, void *z,
     return kOk;
 }
 
-// ---- convertTypes (float16 / float32 / double) -----------------------------------------------------
+// ---- convertTypes ------------------------------------------------------------------------------------
 // z[i] = (D) ((float) x[i]): every conversion goes through float, as the reference's convertGeneric does
-// (include/loops/type_conversions.h:592-610), so double -> double also rounds to float on the way.
-template <class S> ND_D float as_float(S v);
-template <> ND_D float as_float<__half>(__half v) { return __half2float(v); }
-template <> ND_D float as_float<float>(float v) { return v; }
-template <> ND_D float as_float<double>(double v) { return (float) v; }
-template <class D> ND_D D from_float(float v);
-template <> ND_D __half from_float<__half>(float v) { return __float2half_rn(v); }
-template <> ND_D float from_float<float>(float v) { return v; }
-template <> ND_D double from_float<double>(float v) { return (double) v; }
+// (include/loops/type_conversions.h:592-610). The 8- and 16-bit integer types are the reference's saturating
+// wrappers (include/types/impl/{int8,uint8,int16,uint16}.cpp): float -> int truncates like the x86 conversion
+// the reference is compiled to (anything outside int32, and NaN, gives INT_MIN) and is then clamped to the
+// type's range. Its uint16 wrapper clamps to 65536 and returns the value through a uint8_t, so only the low
+// byte survives; that is reproduced, not repaired.
+template <int CODE> struct ConvType;
+template <> struct ConvType<1> { typedef signed char T; };
+template <> struct ConvType<2> { typedef unsigned char T; };
+template <> struct ConvType<3> { typedef __half T; };
+template <> struct ConvType<4> { typedef short T; };
+template <> struct ConvType<5> { typedef unsigned short T; };
+template <> struct ConvType<6> { typedef float T; };
+template <> struct ConvType<7> { typedef double T; };
 
-template <class S, class D>
-__global__ void __launch_bounds__(kCopyBlock) k_convert(const S *x, D *z, LL n) {
+ND_D int x86_float_to_int(float v) {
+    return (v >= 2147483648.0f || v < -2147483648.0f || v != v) ? (int) 0x80000000 : __float2int_rz(v);
+}
+ND_D int clamp_int(int t, int lo, int hi) { return t > hi ? hi : (t < lo ? lo : t); }
+
+template <int CODE> ND_D float as_float(typename ConvType<CODE>::T v) { return (float) (int) v; }   // the integer types
+template <> ND_D float as_float<3>(__half v) { return __half2float(v); }
+template <> ND_D float as_float<6>(float v) { return v; }
+template <> ND_D float as_float<7>(double v) { return (float) v; }
+
+template <int CODE> ND_D typename ConvType<CODE>::T from_float(float v);
+template <> ND_D signed char from_float<1>(float v) { return (signed char) clamp_int(x86_float_to_int(v), -128, 127); }
+template <> ND_D unsigned char from_float<2>(float v) { return (unsigned char) clamp_int(x86_float_to_int(v), 0, 255); }
+template <> ND_D __half from_float<3>(float v) { return __float2half_rn(v); }
+template <> ND_D short from_float<4>(float v) { return (short) clamp_int(x86_float_to_int(v), -32768, 32767); }
+template <> ND_D unsigned short from_float<5>(float v) {
+    return (unsigned short) (unsigned char) (unsigned short) clamp_int(x86_float_to_int(v), 0, 65536);
+}
+template <> ND_D float from_float<6>(float v) { return v; }
+template <> ND_D double from_float<7>(float v) { return (double) v; }
+
+// four consecutive elements per thread as one (or two) vector accesses
+template <class E> struct alignas(sizeof(E) * 4 > 16 ? 16 : sizeof(E) * 4) Quad { E v[4]; };
+
+template <int SC, int DC>
+__global__ void __launch_bounds__(kCopyBlock) k_convert(const void *x, void *z, LL n, int quads) {
     grid_dependency_sync();
+    typedef typename ConvType<SC>::T S;
+    typedef typename ConvType<DC>::T D;
     const LL tid = (LL) blockIdx.x * kCopyBlock + threadIdx.x, nthreads = (LL) gridDim.x * kCopyBlock;
-    LL i = tid;
-    for (; i + 3 * nthreads < n; i += 4 * nthreads) {
-        const S a = x[i], b = x[i + nthreads], c = x[i + 2 * nthreads], d = x[i + 3 * nthreads];
-        z[i] = from_float<D>(as_float<S>(a));
-        z[i + nthreads] = from_float<D>(as_float<S>(b));
-        z[i + 2 * nthreads] = from_float<D>(as_float<S>(c));
-        z[i + 3 * nthreads] = from_float<D>(as_float<S>(d));
+    const S *sx = static_cast<const S *>(x);
+    D *dz = static_cast<D *>(z);
+    LL done = 0;
+    if (quads) {
+        const Quad<S> *qx = static_cast<const Quad<S> *>(x);
+        Quad<D> *qz = static_cast<Quad<D> *>(z);
+        const LL nq = n / 4;
+        LL i = tid;
+        for (; i + nthreads < nq; i += 2 * nthreads) {
+            const Quad<S> a = qx[i], b = qx[i + nthreads];
+            Quad<D> oa, ob;
+#pragma unroll
+            for (int k = 0; k < 4; k++) { oa.v[k] = from_float<DC>(as_float<SC>(a.v[k])); ob.v[k] = from_float<DC>(as_float<SC>(b.v[k])); }
+            qz[i] = oa; qz[i + nthreads] = ob;
+        }
+        for (; i < nq; i += nthreads) {
+            const Quad<S> a = qx[i];
+            Quad<D> oa;
+#pragma unroll
+            for (int k = 0; k < 4; k++) oa.v[k] = from_float<DC>(as_float<SC>(a.v[k]));
+            qz[i] = oa;
+        }
+        done = nq * 4;
     }
-    for (; i < n; i += nthreads) z[i] = from_float<D>(as_float<S>(x[i]));
+    for (LL i = done + tid; i < n; i += nthreads) dz[i] = from_float<DC>(as_float<SC>(sx[i]));
 }
 
-template <class S, class D>
+template <int SC, int DC>
 Status launch_convert(const void *x, void *z, LL n, cudaStream_t stream) {
-    LL blocks = ceil_div(ceil_div(n, 4), kCopyBlock);
+    typedef typename ConvType<SC>::T S;
+    typedef typename ConvType<DC>::T D;
+    const bool quads = reinterpret_cast<uintptr_t>(x) % alignof(Quad<S>) == 0 && reinterpret_cast<uintptr_t>(z) % alignof(Quad<D>) == 0;
+    LL blocks = ceil_div(ceil_div(n, quads ? 8 : 1), kCopyBlock);
     const LL cap = (LL) kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    launch_kernel(k_convert<S, D>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, static_cast<const S *>(x), static_cast<D *>(z), n);
+    launch_kernel(k_convert<SC, DC>, dim3((unsigned) blocks), dim3(kCopyBlock), stream, x, z, n, quads ? 1 : 0);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }
 
-template <class S>
+template <int SC>
 Status convert_from(int dstType, const void *x, void *z, LL n, cudaStream_t stream) {
-    if (dstType == 3) return launch_convert<S, __half>(x, z, n, stream);
-    if (dstType == 6) return launch_convert<S, float>(x, z, n, stream);
-    return launch_convert<S, double>(x, z, n, stream);
+    switch (dstType) {
+        case 1: return launch_convert<SC, 1>(x, z, n, stream);
+        case 2: return launch_convert<SC, 2>(x, z, n, stream);
+        case 3: return launch_convert<SC, 3>(x, z, n, stream);
+        case 4: return launch_convert<SC, 4>(x, z, n, stream);
+        case 5: return launch_convert<SC, 5>(x, z, n, stream);
+        case 6: return launch_convert<SC, 6>(x, z, n, stream);
+        default: return launch_convert<SC, 7>(x, z, n, stream);
+    }
 }
 
 }  // namespace
@@ -533,14 +591,25 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
 int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z) {
     if (!x || !z) return bad_arg("convertTypes: null operand");
     if (n < 0) return bad_arg("convertTypes: negative length");
-    auto served = [](int t) { return t == 3 || t == 6 || t == 7; };      // ND4J_FLOAT16, ND4J_FLOAT32, ND4J_DOUBLE
-    if (!served(srcType) || !served(dstType))
-        return unsupported("convertTypes serves float16 (3), float32 (6) and double (7); the 8- and 16-bit integer, "
-                           "float8 and threshold encodings are not built");
+    // ND4J_INT8 1, UINT8 2, FLOAT16 3, INT16 4, UINT16 5, FLOAT32 6, DOUBLE 7 (type_conversions.h:11-19)
+    const bool srcServed = srcType == 1 || srcType == 2 || srcType == 3 || srcType == 4 || srcType == 6 || srcType == 7;
+    if (!srcServed || dstType < 1 || dstType > 7)
+        return unsupported("convertTypes serves int8 (1), uint8 (2), float16 (3), int16 (4), float32 (6) and double (7) sources "
+                           "and the same plus uint16 (5) as results; the float8 and threshold encodings are not built, and "
+                           "the reference has no conversion from uint16");
+    // pairs the reference's dispatch leaves out: the result is not touched (type_conversions.h:725-727, 853-854;
+    // there is no float32 -> float32 branch at all)
+    if (srcType == dstType && (srcType == 1 || srcType == 6 || srcType == 7)) return kOk;
     if (n == 0) return kOk;
-    if (srcType == 3) return convert_from<__half>(dstType, x, z, n, as_stream(stream));
-    if (srcType == 6) return convert_from<float>(dstType, x, z, n, as_stream(stream));
-    return convert_from<double>(dstType, x, z, n, as_stream(stream));
+    const cudaStream_t st = as_stream(stream);
+    switch (srcType) {
+        case 1: return convert_from<1>(dstType, x, z, n, st);
+        case 2: return convert_from<2>(dstType, x, z, n, st);
+        case 3: return convert_from<3>(dstType, x, z, n, st);
+        case 4: return convert_from<4>(dstType, x, z, n, st);
+        case 6: return convert_from<6>(dstType, x, z, n, st);
+        default: return convert_from<7>(dstType, x, z, n, st);
+    }
 }
 
 int nd4jb200_average(void *stream, int dtype, const void *const *sources, void *z, int n, Nd4jLong length, int propagate) {

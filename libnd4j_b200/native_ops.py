@@ -518,7 +518,8 @@ class NativeOps:
         self._check(self.lib.nd4jb200_accumulate(self._stream(extras), dt, ptrs, _ptr(dz), n, length))
 
     def convertTypes(self, extras, srcType, x, N, dstType, z):
-        """ND4J_FLOAT16 = 3, ND4J_FLOAT32 = 6, ND4J_DOUBLE = 7 (NativeOps.h:2144)."""
+        """ND4J_INT8 = 1, UINT8 = 2, FLOAT16 = 3, INT16 = 4, UINT16 = 5 (result only), FLOAT32 = 6, DOUBLE = 7
+        (NativeOps.h:2144; include/loops/type_conversions.h:11-19)."""
         self._check(self.lib.nd4jb200_convert_types(self._stream(extras), srcType, _ptr(x), N, dstType, _ptr(z)))
 
     def memcpyAsync(self, dst, src, size, flags, reserved=None):

@@ -58,6 +58,11 @@ class Reference:
         L.ref_rng_relative_f64.restype = ctypes.c_double
         L.ref_rng_relative_f64.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
 
+    def convert_types(self, src_type, x, dst_type, z):
+        """NativeOps::convertTypes (include/loops/type_conversions.h:696-880); z is written in place."""
+        self.lib.ref_convertTypes(int(src_type), _p(x), ctypes.c_longlong(x.size), int(dst_type), _p(z))
+        return z
+
     def threads(self):
         return self.lib.ref_omp_max_threads()
 

@@ -131,25 +131,44 @@ def test_average_into_first_source_and_limits(ops):
         ops.averageFloat(None, [dxs[0]] * 129, None, 129, 1000, False)
 
 
-CODES = {np.float16: 3, np.float32: 6, np.float64: 7}
+from tests.convert_truth import CODES, SOURCES, RESULTS, convert_truth, convert_inputs
 
 
-@pytest.mark.parametrize("src", [np.float16, np.float32, np.float64])
-@pytest.mark.parametrize("dst", [np.float16, np.float32, np.float64])
-def test_convert_types_goes_through_float(ops, src, dst):
-    """z = (D)(float) x (include/loops/type_conversions.h:592-610): bit-exact against numpy's IEEE conversions,
-    including overflow to infinity, subnormal halves and the float rounding of double -> double."""
-    rng = np.random.default_rng(1)
-    x = np.concatenate([rng.standard_normal(10001) * 100, [0.0, -0.0, 65504.0, 70000.0, 1e-7, 6e-8, 1e300, -1e300, 1 / 3]])
-    with np.errstate(over="ignore"):
-        x = x.astype(src)
-        want = x.astype(np.float32).astype(dst)
-    dz = dev(np.zeros(x.size, dst))
-    ops.convertTypes(None, CODES[src], dev(x), x.size, CODES[dst], dz)
+@pytest.mark.parametrize("src", SOURCES)
+@pytest.mark.parametrize("dst", RESULTS)
+@pytest.mark.parametrize("misalign", [0, 1])
+def test_convert_types_goes_through_float(ops, src, dst, misalign):
+    """z = (D)(float) x (include/loops/type_conversions.h:592-610, 696-880): bit-exact against numpy's IEEE
+    conversions (overflow to infinity, subnormal halves) and the saturating integer wrappers. The pairs the
+    reference's dispatch leaves out (int8 -> int8, float32 -> float32, double -> double) leave z untouched."""
+    x = convert_inputs(src)
+    untouched = src == dst and src in (np.int8, np.float32, np.float64)
+    # `misalign` shifts both buffers by one element so that the four-element vector path cannot be taken
+    dx = dev(np.concatenate([x[:1], x]))[misalign:]
+    dz = dev(np.full(x.size + 1, 7, dst))[misalign:]
+    n = x.size + 1 - misalign
+    xs = host(dx)
+    ops.convertTypes(None, CODES[src], dx, n, CODES[dst], dz)
     got = host(dz)
-    assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
-    with pytest.raises(RuntimeError):
-        ops.convertTypes(None, 1, dev(x), x.size, CODES[dst], dz)      # ND4J_INT8 is not served
+    if untouched:
+        assert (got == 7).all()
+    else:
+        want = convert_truth(xs, dst)
+        if np.issubdtype(dst, np.floating):
+            # a NaN stays a NaN; its payload bits are not compared (the reference's float16 class and IEEE
+            # hardware conversions pick different ones)
+            nan = np.isnan(want)
+            assert np.array_equal(np.isnan(got), nan)
+            got, want = np.where(nan, 0, got).astype(dst), np.where(nan, 0, want).astype(dst)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+def test_convert_types_unserved_encodings(ops):
+    x = dev(np.zeros(16, np.float32))
+    z = dev(np.zeros(16, np.float32))
+    for src, dst in ((0, 6), (6, 0), (8, 6), (6, 8), (5, 6)):      # float8, threshold; no conversion from uint16
+        with pytest.raises(RuntimeError):
+            ops.convertTypes(None, src, x, 16, dst, z)
 
 
 def _tad_view(x, lay, ops, dims):

@@ -151,3 +151,22 @@ def test_port_vs_live_reference_random_states(port, real_ref):
     b = real_ref.random(0, rs, np.zeros(17003, np.float32), zi, np.array([0, 1], np.float32))
     np.testing.assert_array_equal(a, b)
     assert port.rng_position(ps) == real_ref.rng_position(rs) and port.rng_generation(ps) == real_ref.rng_generation(rs)
+
+
+def test_convert_types_restatement_matches_reference(real_ref):
+    """The numpy restatement the GPU tests use, against NativeOps::convertTypes of the reference itself: every
+    served pair, including the out-of-range, NaN and uint16 low-byte cases, and the pairs it leaves untouched."""
+    from tests.convert_truth import CODES, SOURCES, RESULTS, convert_truth, convert_inputs
+    for src in SOURCES:
+        x = convert_inputs(src)
+        for dst in RESULTS:
+            z = real_ref.convert_types(CODES[src], x, CODES[dst], np.full(x.size, 7, dst))
+            if src == dst and src in (np.int8, np.float32, np.float64):
+                assert (z == 7).all()
+                continue
+            want = convert_truth(x, dst)
+            if np.issubdtype(dst, np.floating):
+                nan = np.isnan(want)
+                assert np.array_equal(np.isnan(z), nan)
+                z, want = np.where(nan, 0, z).astype(dst), np.where(nan, 0, want).astype(dst)
+            assert np.array_equal(z.view(np.uint8), want.view(np.uint8)), (src, dst)
