@@ -415,6 +415,27 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
     record("tear_f32_65536x1024", 2 * 65536 * 1024 * 4, 65536 * 1024,
            lambda: calls.check(lib.nd4jb200_tear(st, 0, P(src_), xinfo_, tp_, pinfo_, ti_, P(toffs_d))), graph=False)
     del src_, out_, pieces_
+    # sort: every row of [65536,1024] (one pass through shared memory) and a whole array of 2^24 floats (12 stages
+    # beyond the shared-memory chunks). Each timed call first refills the array from an unsorted copy (a device
+    # copy inside the timed region), because sorted input would skip the network's stores.
+    with torch.cuda.stream(stream):
+        unsorted_ = torch.randn(65536, 1024, device=dev, generator=g)
+        work_ = torch.empty_like(unsorted_)
+    winfo_ = calls.longs(S.shape_info([65536, 1024]))
+    flat_ = calls.longs(S.shape_info([1, 1 << 24]))
+
+    def f_rows():
+        with torch.cuda.stream(stream):
+            work_.copy_(unsorted_)
+        calls.check(lib.nd4jb200_sort_tad(st, 0, P(work_), winfo_, d1, 1, 0))
+
+    def f_all():
+        with torch.cuda.stream(stream):
+            work_[:16384].copy_(unsorted_[:16384])
+        calls.check(lib.nd4jb200_sort(st, 0, P(work_), flat_, 0))
+    record("sort_rows_f32_65536x1024_incl_refill", 4 * 65536 * 1024 * 4, 65536 * 1024, f_rows, iters=10, graph=False)
+    record("sort_f32_2p24_incl_refill", 4 * (1 << 24) * 4, 1 << 24, f_all, iters=5, graph=False)
+    del unsorted_, work_
     blocks_ = [torch.randn(4096, 4096, device=dev, generator=g) for _ in range(4)]
     cat_ = torch.empty(16384, 4096, device=dev)
     ptrs_ = (ctypes.c_void_p * 4)(*[b_.data_ptr() for b_ in blocks_])

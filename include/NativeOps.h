@@ -79,6 +79,10 @@ struct float16 {
     void shuffle##S(Nd4jPointer *extras, Nd4jPointer *dx, Nd4jPointer *xShapeInfo, Nd4jPointer *dz,                 \
                     Nd4jPointer *zShapeInfo, int N, int *shuffleMap, Nd4jPointer *tadShapeInfo,                     \
                     Nd4jPointer *tadOffsets);                                                                       \
+    /* nd4jb200_sort / nd4jb200_sort_tad (NativeOps.h:2940-2952) */                                                 \
+    void sort##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, bool descending);                          \
+    void sortTad##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, int *dimension, int dimensionLength,    \
+                    Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets, bool descending);                                 \
     void average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length, bool propagate);           \
     void accumulate##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length);                        \
     /* nd4jb200_exec_scalar_along_dimension (NativeOps.h:1160-1214) */                                              \

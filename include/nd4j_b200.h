@@ -224,6 +224,14 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
  * (blas/NativeOps.h:2144; include/loops/type_conversions.h:592-610, 696-880; include/types/impl/). The pairs its
  * dispatch leaves out (1->1, 6->6, 7->7) leave z untouched. FLOAT8 (0) and THRESHOLD (8): ND4JB200_EUNSUPPORTED. */
 int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z);
+/* NativeOps::sort{Float,Double,Half}: the whole array sorted in place over its linear positions (i * ews, or c-order
+ * coordinates), ascending or descending (blas/NativeOps.h:2940-2944; include/ops/impl/specials.cpp:457-549) */
+int nd4jb200_sort(void *stream, int dtype, void *x, const Nd4jLong *xShapeInfo, int descending);
+/* NativeOps::sortTad{Float,Double,Half}: every TAD along `dimension` sorted in place
+ * (blas/NativeOps.h:2948-2952; include/ops/impl/specials.cpp:551-564). The TAD descriptors are derived from
+ * xShapeInfo and the dimension list on the host. */
+int nd4jb200_sort_tad(void *stream, int dtype, void *x, const Nd4jLong *xShapeInfo, const int *dimension,
+                      int dimensionLength, int descending);
 /* NativeOps::average{Float,Double,Half}: z[i] = sum_k sources[k][i] / n (z == NULL: into sources[0]); with
  * `propagate` the result is also written over every source (blas/NativeOps.h:1996-2025;
  * include/ops/impl/specials.cpp:374-433). At most 128 sources, all on this device or peer-mapped. */

@@ -211,6 +211,14 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
         check(nd4jb200_shuffle(stream_of(extras), TypeCode<T>::v, N, dx, infos.data(), shuffleMap, tads.data(),       \
                                offs.data()), "shuffle" #S);                                                            \
     }                                                                                                                  \
+    void NativeOps::sort##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, bool descending) {                \
+        check(nd4jb200_sort(STREAM, TypeCode<T>::v, x, X_INFO, descending ? 1 : 0), "sort" #S);                       \
+    }                                                                                                                  \
+    void NativeOps::sortTad##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, int *dimension,                \
+                               int dimensionLength, Nd4jLong *, Nd4jLong *, bool descending) {                        \
+        check(nd4jb200_sort_tad(STREAM, TypeCode<T>::v, x, X_INFO, host_dims(dimension, dimensionLength),             \
+                                dimensionLength, descending ? 1 : 0), "sortTad" #S);                                   \
+    }                                                                                                                  \
     void NativeOps::average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length,                   \
                                bool propagate) {                                                                      \
         check(nd4jb200_average(stream_of(extras), TypeCode<T>::v, dx, dz, n, length, propagate ? 1 : 0),              \

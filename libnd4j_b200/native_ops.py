@@ -79,6 +79,8 @@ def load_library(path=None):
         "nd4jb200_pull_rows": (i, [vp, i, vp, vp, ll, vp, llp, vp, llp, vp]),
         "nd4jb200_tear": (i, [vp, i, vp, llp, vp, llp, llp, vp]),
         "nd4jb200_shuffle": (i, [vp, i, i, vp, vp, ip, vp, vp]),
+        "nd4jb200_sort": (i, [vp, i, vp, llp, i]),
+        "nd4jb200_sort_tad": (i, [vp, i, vp, llp, ip, i, i]),
         "nd4jb200_average": (i, [vp, i, vp, vp, i, ll, i]),
         "nd4jb200_accumulate": (i, [vp, i, vp, vp, i, ll]),
         "nd4jb200_set_tuning": (ctypes.c_int, [ctypes.c_int, ctypes.c_longlong]),
@@ -509,6 +511,17 @@ class NativeOps:
         m, mp = _ints(shuffleMap)
         self._check(self.lib.nd4jb200_shuffle(self._stream(extras), dt, N, ptrs, infos, mp, tads, offs))
 
+    def _sort(self, dt, extraPointers, x, xShapeInfo, descending):
+        xs, xsp = _longs(xShapeInfo)
+        self._check(self.lib.nd4jb200_sort(self._stream(extraPointers), dt, _ptr(x), xsp, 1 if descending else 0))
+
+    def _sortTad(self, dt, extraPointers, x, xShapeInfo, dimension, dimensionLength, tadShapeInfo=None, tadOffsets=None,
+                 descending=False):
+        xs, xsp = _longs(xShapeInfo)
+        d, dp = _ints(dimension)
+        self._check(self.lib.nd4jb200_sort_tad(self._stream(extraPointers), dt, _ptr(x), xsp, dp, dimensionLength,
+                                               1 if descending else 0))
+
     def _average(self, dt, extras, dx, dz, n, length, propagate):
         ptrs = (ctypes.c_void_p * n)(*[_ptr(d).value for d in dx])
         self._check(self.lib.nd4jb200_average(self._stream(extras), dt, ptrs, _ptr(dz), n, length, 1 if propagate else 0))
@@ -556,7 +569,7 @@ def _bind(generic, dt):
 for _fam in ("execReduce", "execReduceScalar", "execIndexReduce", "execIndexReduceScalar", "execSummaryStats",
              "execSummaryStatsScalar", "execReduce3", "execReduce3All", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
              "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom", "flatten", "concat", "pullRows",
-             "tear", "shuffle", "average", "accumulate"):
+             "tear", "shuffle", "sort", "sortTad", "average", "accumulate"):
     for _sfx, _dt in _SUFFIX.items():
         _m = _bind("_" + _fam, _dt)
         _m.__name__ = _fam + _sfx

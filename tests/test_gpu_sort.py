@@ -1,0 +1,95 @@
+"""sort / sortTad on the GPU (NativeOps.h:2940-2952; include/ops/impl/specials.cpp:457-564). A sorted
+sequence does not depend on the sorting algorithm, so the expectation is numpy's sort of the same values laid
+out over the same positions; inputs have no NaN, and equal values are interchangeable."""
+import numpy as np
+import pytest
+import torch
+
+from libnd4j_b200 import shape as S
+from tests.cases import Layout
+
+pytestmark = pytest.mark.gpu
+
+NAMES = [(np.float32, "Float"), (np.float64, "Double"), (np.float16, "Half")]
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def _values(rng, n, dt):
+    x = (rng.standard_normal(n) * 100).astype(dt)
+    if n > 8:
+        x[:4] = [np.inf, -np.inf, 0.0, x[5]]          # infinities (the padding value) and a duplicate
+    return x
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("n", [1, 2, 3, 31, 256, 257, 2048, 2049, 8192, 8193, 20000, 65536, 100003])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_whole_array(ops, dt, name, n, descending):
+    rng = np.random.default_rng(n)
+    x = _values(rng, n, dt)
+    dx = dev(x)
+    getattr(ops, "sort" + name)(None, dx, S.shape_info([1, n]), descending)
+    want = np.sort(x)[::-1] if descending else np.sort(x)
+    np.testing.assert_array_equal(host(dx), want)
+
+
+def test_sort_small_known_answer(ops):
+    x = np.array([5, 2, 4, 7, 1, 3, 6, 9, 8, 0], np.float32)
+    dx = dev(x)
+    ops.sortFloat(None, dx, S.shape_info([1, 10]), False)
+    np.testing.assert_array_equal(host(dx), np.arange(10, dtype=np.float32))
+    ops.sortFloat(None, dx, S.shape_info([1, 10]), True)
+    np.testing.assert_array_equal(host(dx), np.arange(10, dtype=np.float32)[::-1])
+
+
+@pytest.mark.parametrize("kind", ["c", "f", "cview2"])
+def test_sort_walks_linear_positions(ops, kind):
+    # positions are i * ews, or c-order coordinates where there is no element-wise stride
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((37, 53)).astype(np.float32)
+    lay = Layout(x, kind)
+    dx = dev(lay.buffer)
+    ops.sortFloat(None, dx, lay.info, False)
+    got = lay.read(host(dx))
+    flat = got.ravel(order="F" if kind == "f" else "C")
+    np.testing.assert_array_equal(flat, np.sort(x.ravel()))
+
+
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("shape,dim", [((64, 10), 1), ((64, 10), 0), ((33, 300), 1), ((7, 3000), 1), ((3, 9000), 1),
+                                       ((2, 20001), 1), ((5, 6, 7), 2), ((5, 6, 7), 0)])
+@pytest.mark.parametrize("kind", ["c", "f"])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_tad(ops, dt, name, shape, dim, kind, descending):
+    rng = np.random.default_rng(sum(shape) + dim)
+    x = (rng.standard_normal(shape) * 50).astype(dt)
+    lay = Layout(x, kind)
+    dx = dev(lay.buffer)
+    getattr(ops, "sortTad" + name)(None, dx, lay.info, [dim], 1, None, None, descending)
+    want = np.sort(x, axis=dim)
+    if descending:
+        want = np.flip(want, axis=dim)
+    np.testing.assert_array_equal(lay.read(host(dx)), want)
+
+
+def test_sort_large_is_sorted_and_a_permutation(ops):
+    # 2^24 + 5 floats: 12 stages beyond the shared-memory chunks; sortedness plus an order-independent checksum
+    n = (1 << 24) + 5
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    x = torch.randn(n, device="cuda", generator=g)
+    before = (x.double().sum().item(), x.double().abs().sum().item(), x.max().item(), x.min().item())
+    ops.sortFloat(None, x, S.shape_info([1, n]), False)
+    assert bool((x[1:] >= x[:-1]).all())
+    after = (x.double().sum().item(), x.double().abs().sum().item(), x.max().item(), x.min().item())
+    assert before[2:] == after[2:]
+    assert abs(before[0] - after[0]) <= 1e-6 * before[1] and abs(before[1] - after[1]) <= 1e-9 * before[1]
+    want = torch.sort(torch.randn(n, device="cuda", generator=g.manual_seed(5)))[0]
+    assert torch.equal(x, want)
