@@ -112,10 +112,13 @@ __global__ void __launch_bounds__(kSmBlock, 4) k_softmax_cached(const SoftmaxArg
 // The same with 16-byte packs and up to 32 values (16 doubles) per thread: rows of up to 1024 elements per
 // warp (G = 32) or 8192 per CTA (G = 256) are read once, kept in registers, and need one exp per element
 // instead of the two of the sweeping kernels. Needs unit column strides and 16-byte aligned rows.
-template <class C> struct SmRegs { static constexpr int kVals = sizeof(C) == 8 ? 16 : 32; };
+template <class C> struct SmRegs {
+    static constexpr int kVals = sizeof(C) == 8 ? 16 : 32;
+    static constexpr int kCtas = sizeof(C) == 8 ? 2 : 4;      // resident CTAs per SM the register budget is set for
+};
 
 template <class T, int KIND, int G>
-__global__ void __launch_bounds__(kSmBlock, 2) k_softmax_regs(const SoftmaxArgs a) {
+__global__ void __launch_bounds__(kSmBlock, SmRegs<typename Elem<T>::C>::kCtas) k_softmax_regs(const SoftmaxArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
     constexpr int V = Elem<T>::kVec;

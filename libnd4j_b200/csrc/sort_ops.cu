@@ -9,11 +9,12 @@
 // with its mirror image k-1-i, then runs half-cleaners with strides k/4 ... 1 -- in which every comparator
 // puts the earlier value at the lower position. Positions past the end behave like values that sort last
 // and are never moved by such a comparator, so any length works without padding in memory.
-//   * chunks of CN elements (8192 four-byte or 4096 eight-byte keys, 32 KB) are sorted entirely in shared
-//     memory: one read and one write of the data for the first log2(CN) stages;
+//   * chunks of CN elements (8192 four-byte or 4096 eight-byte keys) are sorted on chip, eight keys per
+//     thread in registers, exchanged by warp shuffles and, beyond a warp, through shared memory: one read
+//     and one write of the data for the first log2(CN) stages;
 //   * every later stage k runs its strides >= CN as passes over global memory (coalesced: neighbouring
-//     threads own neighbouring comparators) and its strides < CN again in shared memory, one pass.
-// TADs of up to CN elements take a single launch with one CTA per TAD.
+//     threads own neighbouring comparators) and its strides < CN again on chip, one pass.
+// TADs of up to CN elements take a single launch (a warp per TAD up to 256 keys, a CTA per TAD above).
 #include "../../include/nd4j_b200.h"
 #include "device_utils.cuh"
 #include "runtime.h"
@@ -38,57 +39,121 @@ template <class C> ND_D void order_pair(C &lo, C &hi, int descending) {
     if (sorts_before(hi, lo, descending)) { const C t = lo; lo = hi; hi = t; }
 }
 
-// The comparators of one step over a chunk held in shared memory. q numbers the CN/2 comparators.
-template <class C, int CN, int THREADS> ND_D void mirror_step(C *s, int k, int descending) {
-    const int half = k >> 1;
-    for (int q = threadIdx.x; q < CN / 2; q += THREADS) {
-        const int block = q / half, r = q - block * half;
-        const int lo = block * k + r, hi = block * k + (k - 1 - r);
-        order_pair(s[lo], s[hi], descending);
-    }
-    __syncthreads();
+// ---- chunks in registers ------------------------------------------------------------------------------
+// A chunk of CN = 8 G keys is held by G threads, thread t owning positions 8 t ... 8 t + 7. The partner of
+// position i is i ^ m in every step (m = k - 1 for the mirror step of stage k, m = j for a half-cleaner), so
+// a step is one of three kinds: m < 8 stays inside a thread's registers; a partner thread t ^ (m >> 3) in
+// the same warp is reached with shuffles; anything further goes through shared memory. The member of a
+// pair at the lower position keeps the value that sorts earlier; with equal (or unordered) values both
+// keep their own, so the keys stay a permutation of the input whatever they are.
+constexpr int kKeys = 8;
+
+template <class C> ND_D void order_regs(C &lo, C &hi, int descending) {
+    if (sorts_before(hi, lo, descending)) { const C t = lo; lo = hi; hi = t; }
 }
-template <class C, int CN, int THREADS> ND_D void stride_steps(C *s, int jFirst, int descending) {
-    for (int j = jFirst; j > 0; j >>= 1) {
-        for (int q = threadIdx.x; q < CN / 2; q += THREADS) {
-            const int lo = ((q & ~(j - 1)) << 1) | (q & (j - 1));
-            order_pair(s[lo], s[lo + j], descending);
+// stages 2, 4 and 8 of a thread's own eight keys
+template <class C> ND_D void head_stages(C (&v)[kKeys], int d) {
+#pragma unroll
+    for (int k = 2; k <= kKeys; k <<= 1) {
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) {
+            const int partner = e ^ (k - 1);
+            if (e < partner) order_regs(v[e], v[partner], d);
         }
-        __syncthreads();
+#pragma unroll
+        for (int j = k >> 2; j > 0; j >>= 1)
+#pragma unroll
+            for (int e = 0; e < kKeys; e++)
+                if ((e & j) == 0) order_regs(v[e], v[e + j], d);
+    }
+}
+// half-cleaners of stride 4, 2, 1
+template <class C> ND_D void tail_steps(C (&v)[kKeys], int d) {
+#pragma unroll
+    for (int j = kKeys >> 1; j > 0; j >>= 1)
+#pragma unroll
+        for (int e = 0; e < kKeys; e++)
+            if ((e & j) == 0) order_regs(v[e], v[e + j], d);
+}
+
+template <int G> ND_D void group_sync() {
+    if (G == 32) __syncwarp(); else __syncthreads();
+}
+// shared-memory slot of key e of thread t: rows of G + 4 so that both the per-thread and the linear access
+// patterns are free of bank conflicts
+template <int G> ND_D int slot(int e, int t) { return e * (G + 4) + t; }
+
+// partner thread t ^ mt; MIRROR: the partner's keys are taken in reverse order (m = k - 1 flips the low bits)
+template <class C, int G, bool MIRROR>
+ND_D void cross_step(C (&v)[kKeys], C *s, int t, int mt, int highT, int d) {
+    C p[kKeys];
+    if (mt < 32) {
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) p[e] = __shfl_xor_sync(0xffffffffu, v[MIRROR ? kKeys - 1 - e : e], mt);
+    } else {
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) s[slot<G>(e, t)] = v[e];
+        group_sync<G>();
+        const int pt = t ^ mt;
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) p[e] = s[slot<G>(MIRROR ? kKeys - 1 - e : e, pt)];
+        group_sync<G>();
+    }
+    const bool lower = (t & highT) == 0;
+#pragma unroll
+    for (int e = 0; e < kKeys; e++) {
+        const bool take = lower ? sorts_before(p[e], v[e], d) : sorts_before(v[e], p[e], d);
+        v[e] = take ? p[e] : v[e];
     }
 }
 
 // fullSort: sorts every chunk (stages 2 ... CN). Otherwise: the strides CN/2 ... 1 of a later stage.
-template <class T, int CN, int THREADS>
+// THREADS / G chunks are worked on by one CTA at a time (G = 32: a warp per chunk, no CTA barriers).
+template <class T, int G, int THREADS>
 __global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int fullSort) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
-    __shared__ C s[CN];
+    constexpr int CN = G * kKeys, kGroups = THREADS / G;
+    __shared__ C shared[kGroups * kKeys * (G + 4)];
+    const int t = threadIdx.x % G, group = threadIdx.x / G;
+    C *s = shared + group * kKeys * (G + 4);
     T *ax = static_cast<T *>(a.x);
     const C inf = sizeof(C) == 8 ? C(CUDART_INF) : C(CUDART_INF_F);
     const C last = a.descending ? -inf : inf;
+    const int d = a.descending;
     const LL chunks = (a.n + CN - 1) / CN, units = a.numTads * chunks;
-    for (LL u = blockIdx.x; u < units; u += gridDim.x) {
+    for (LL u = (LL) blockIdx.x * kGroups + group; u < units; u += (LL) gridDim.x * kGroups) {
         const LL tad = u / chunks, first = (u - tad * chunks) * CN;
         T *base = ax + view_offset(a.outer, tad);
-        for (int t = threadIdx.x; t < CN; t += THREADS) {
-            const LL i = first + t;
-            s[t] = i < a.n ? Elem<T>::load(base + view_offset(a.inner, i)) : last;
+        // coalesced over linear positions, then every thread picks up its eight keys
+        for (int idx = t; idx < CN; idx += G) {
+            const LL i = first + idx;
+            s[slot<G>(idx & (kKeys - 1), idx / kKeys)] = i < a.n ? Elem<T>::load(base + view_offset(a.inner, i)) : last;
         }
-        __syncthreads();
+        group_sync<G>();
+        C v[kKeys];
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) v[e] = s[slot<G>(e, t)];
+        group_sync<G>();
         if (fullSort) {
-            for (int k = 2; k <= CN; k <<= 1) {
-                mirror_step<C, CN, THREADS>(s, k, a.descending);
-                stride_steps<C, CN, THREADS>(s, k >> 2, a.descending);
+            head_stages(v, d);
+            for (int k = 2 * kKeys; k <= CN; k <<= 1) {
+                cross_step<C, G, true>(v, s, t, k / kKeys - 1, k / (2 * kKeys), d);
+                for (int j = k >> 2; j >= kKeys; j >>= 1) cross_step<C, G, false>(v, s, t, j / kKeys, j / kKeys, d);
+                tail_steps(v, d);
             }
         } else {
-            stride_steps<C, CN, THREADS>(s, CN / 2, a.descending);
+            for (int j = CN >> 1; j >= kKeys; j >>= 1) cross_step<C, G, false>(v, s, t, j / kKeys, j / kKeys, d);
+            tail_steps(v, d);
         }
-        for (int t = threadIdx.x; t < CN; t += THREADS) {
-            const LL i = first + t;
-            if (i < a.n) Elem<T>::store(base + view_offset(a.inner, i), s[t]);
+#pragma unroll
+        for (int e = 0; e < kKeys; e++) s[slot<G>(e, t)] = v[e];
+        group_sync<G>();
+        for (int idx = t; idx < CN; idx += G) {
+            const LL i = first + idx;
+            if (i < a.n) Elem<T>::store(base + view_offset(a.inner, i), s[slot<G>(idx & (kKeys - 1), idx / kKeys)]);
         }
-        __syncthreads();
+        group_sync<G>();
     }
 }
 
@@ -117,22 +182,25 @@ __global__ void __launch_bounds__(256) k_sort_global_step(const SortArgs a, LL h
     }
 }
 
-template <class T, int CN, int THREADS>
+template <class T, int G, int THREADS>
 void launch_chunks(const SortArgs &a, int fullSort, cudaStream_t st) {
-    LL blocks = a.numTads * ceil_div(a.n, CN);
+    LL blocks = ceil_div(a.numTads * ceil_div(a.n, G * kKeys), THREADS / G);
     const LL cap = (LL) kNumSMs * 32;
     if (blocks > cap) blocks = cap;
-    launch_kernel(k_sort_chunks<T, CN, THREADS>, dim3((unsigned) blocks), dim3(THREADS), st, a, fullSort);
+    launch_kernel(k_sort_chunks<T, G, THREADS>, dim3((unsigned) blocks), dim3(THREADS), st, a, fullSort);
 }
 
 template <class T>
 Status run_sort(SortArgs a, cudaStream_t st) {
     if (a.numTads <= 0 || a.n <= 1) return kOk;
-    constexpr int kChunk = sizeof(typename Elem<T>::C) == 8 ? 4096 : 8192;
+    // threads per full-size chunk: 8192 four-byte or 4096 eight-byte keys
+    constexpr int kBig = sizeof(typename Elem<T>::C) == 8 ? 512 : 1024;
+    constexpr int kChunk = kBig * kKeys;
     // short TADs: the smallest chunk that holds one
-    if (a.n <= 256) { launch_chunks<T, 256, 128>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
-    if (a.n <= 2048) { launch_chunks<T, 2048, 512>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
-    launch_chunks<T, kChunk, 512>(a, 1, st);
+    if (a.n <= 256) { launch_chunks<T, 32, 256>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
+    if (a.n <= 1024) { launch_chunks<T, 128, 128>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
+    if (a.n <= 2048) { launch_chunks<T, 256, 256>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
+    launch_chunks<T, kBig, kBig>(a, 1, st);
     ND_CUDA(cudaGetLastError());
     LL padded = kChunk;
     while (padded < a.n) padded <<= 1;
@@ -147,7 +215,7 @@ Status run_sort(SortArgs a, cudaStream_t st) {
             a.j = j;
             launch_kernel(k_sort_global_step<T>, dim3((unsigned) blocks), dim3(256), st, a, half);
         }
-        launch_chunks<T, kChunk, 512>(a, 0, st);
+        launch_chunks<T, kBig, kBig>(a, 0, st);
         ND_CUDA(cudaGetLastError());
     }
     return kOk;
