@@ -2,8 +2,8 @@
 // sortTad{Float,Double,Half}; blas/NativeOps.h:2940-2952). The reference's CPU build runs a quicksort over
 // getPosition(shapeInfo, i) (include/ops/impl/specials.cpp:457-564); a sorted sequence does not depend on the
 // algorithm, so the result is the reference's bit for bit wherever the values are distinct (equal values,
-// such as -0 and +0, may come out in either order, as with any unstable sort; NaNs have no defined place in
-// either implementation).
+// such as -0 and +0, may come out in either order there, as with any unstable sort, and NaNs have no defined
+// place in it; here the order is total: -0 before +0, NaNs at the two ends by their sign).
 //
 // Here: a bitonic network in its "mirror" form -- stage k first compares element i of every block of k
 // with its mirror image k-1-i, then runs half-cleaners with strides k/4 ... 1 -- in which every comparator
@@ -12,8 +12,8 @@
 //   * chunks of CN elements (8192 four-byte or 4096 eight-byte keys) are sorted on chip, eight keys per
 //     thread in registers, exchanged by warp shuffles and, beyond a warp, through shared memory: one read
 //     and one write of the data for the first log2(CN) stages;
-//   * every later stage k runs its strides >= CN as passes over global memory (coalesced: neighbouring
-//     threads own neighbouring comparators) and its strides < CN again on chip, one pass.
+//   * every later stage k runs its strides >= 2048 as passes over global memory, three steps per pass (a
+//     thread orders the eight positions those steps connect), and its strides < 2048 again on chip, one pass.
 // TADs of up to CN elements take a single launch (a warp per TAD up to 256 keys, a CTA per TAD above).
 #include "../../include/nd4j_b200.h"
 #include "device_utils.cuh"
@@ -33,47 +33,68 @@ struct SortArgs {
     LL j;                 // stride of a global half-cleaner pass (0: the mirror step of stage k)
 };
 
-template <class C> ND_D bool sorts_before(C a, C b, int descending) { return descending ? a > b : a < b; }
-
-template <class C> ND_D void order_pair(C &lo, C &hi, int descending) {
-    if (sorts_before(hi, lo, descending)) { const C t = lo; lo = hi; hi = t; }
-}
 
 // ---- chunks in registers ------------------------------------------------------------------------------
 // A chunk of CN = 8 G keys is held by G threads, thread t owning positions 8 t ... 8 t + 7. The partner of
 // position i is i ^ m in every step (m = k - 1 for the mirror step of stage k, m = j for a half-cleaner), so
 // a step is one of three kinds: m < 8 stays inside a thread's registers; a partner thread t ^ (m >> 3) in
 // the same warp is reached with shuffles; anything further goes through shared memory. The member of a
-// pair at the lower position keeps the value that sorts earlier; with equal (or unordered) values both
-// keep their own, so the keys stay a permutation of the input whatever they are.
+// pair at the lower position keeps the smaller key.
 constexpr int kKeys = 8;
 
-template <class C> ND_D void order_regs(C &lo, C &hi, int descending) {
-    if (sorts_before(hi, lo, descending)) { const C t = lo; lo = hi; hi = t; }
+// On chip the keys are integers whose signed order is the order wanted: the IEEE bit pattern with the
+// magnitude bits of negative values flipped (so -0 sorts before +0 and NaNs sort to the ends by sign), and
+// all bits inverted for a descending sort. Comparators are then an integer min and max, and no key can be
+// lost or duplicated whatever its value. The transform is its own inverse.
+template <class C> struct SortKey;
+template <> struct SortKey<float> {
+    typedef int K;
+    static constexpr K kLast = 0x7fffffff;
+    static ND_D K flip(K b, int descending) { b ^= (b >> 31) & 0x7fffffff; return descending ? ~b : b; }
+    static ND_D K to_key(float v, int descending) { return flip(__float_as_int(v), descending); }
+    static ND_D float from_key(K k, int descending) { if (descending) k = ~k; return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+};
+template <> struct SortKey<double> {
+    typedef long long K;
+    static constexpr K kLast = 0x7fffffffffffffffll;
+    static ND_D K to_key(double v, int descending) {
+        K b = __double_as_longlong(v);
+        b ^= (b >> 63) & 0x7fffffffffffffffll;
+        return descending ? ~b : b;
+    }
+    static ND_D double from_key(K k, int descending) {
+        if (descending) k = ~k;
+        return __longlong_as_double(k ^ ((k >> 63) & 0x7fffffffffffffffll));
+    }
+};
+
+template <class K> ND_D void order_regs(K &lo, K &hi) {
+    const K a = min(lo, hi), b = max(lo, hi);
+    lo = a; hi = b;
 }
 // stages 2, 4 and 8 of a thread's own eight keys
-template <class C> ND_D void head_stages(C (&v)[kKeys], int d) {
+template <class K> ND_D void head_stages(K (&v)[kKeys]) {
 #pragma unroll
     for (int k = 2; k <= kKeys; k <<= 1) {
 #pragma unroll
         for (int e = 0; e < kKeys; e++) {
             const int partner = e ^ (k - 1);
-            if (e < partner) order_regs(v[e], v[partner], d);
+            if (e < partner) order_regs(v[e], v[partner]);
         }
 #pragma unroll
         for (int j = k >> 2; j > 0; j >>= 1)
 #pragma unroll
             for (int e = 0; e < kKeys; e++)
-                if ((e & j) == 0) order_regs(v[e], v[e + j], d);
+                if ((e & j) == 0) order_regs(v[e], v[e + j]);
     }
 }
 // half-cleaners of stride 4, 2, 1
-template <class C> ND_D void tail_steps(C (&v)[kKeys], int d) {
+template <class K> ND_D void tail_steps(K (&v)[kKeys]) {
 #pragma unroll
     for (int j = kKeys >> 1; j > 0; j >>= 1)
 #pragma unroll
         for (int e = 0; e < kKeys; e++)
-            if ((e & j) == 0) order_regs(v[e], v[e + j], d);
+            if ((e & j) == 0) order_regs(v[e], v[e + j]);
 }
 
 template <int G> ND_D void group_sync() {
@@ -84,9 +105,9 @@ template <int G> ND_D void group_sync() {
 template <int G> ND_D int slot(int e, int t) { return e * (G + 4) + t; }
 
 // partner thread t ^ mt; MIRROR: the partner's keys are taken in reverse order (m = k - 1 flips the low bits)
-template <class C, int G, bool MIRROR>
-ND_D void cross_step(C (&v)[kKeys], C *s, int t, int mt, int highT, int d) {
-    C p[kKeys];
+template <class K, int G, bool MIRROR>
+ND_D void cross_step(K (&v)[kKeys], K *s, int t, int mt, int highT) {
+    K p[kKeys];
     if (mt < 32) {
 #pragma unroll
         for (int e = 0; e < kKeys; e++) p[e] = __shfl_xor_sync(0xffffffffu, v[MIRROR ? kKeys - 1 - e : e], mt);
@@ -102,8 +123,8 @@ ND_D void cross_step(C (&v)[kKeys], C *s, int t, int mt, int highT, int d) {
     const bool lower = (t & highT) == 0;
 #pragma unroll
     for (int e = 0; e < kKeys; e++) {
-        const bool take = lower ? sorts_before(p[e], v[e], d) : sorts_before(v[e], p[e], d);
-        v[e] = take ? p[e] : v[e];
+        const K a = min(v[e], p[e]), b = max(v[e], p[e]);
+        v[e] = lower ? a : b;
     }
 }
 
@@ -113,13 +134,13 @@ template <class T, int G, int THREADS>
 __global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int fullSort) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
+    typedef SortKey<C> Key;
+    typedef typename Key::K K;
     constexpr int CN = G * kKeys, kGroups = THREADS / G;
-    __shared__ C shared[kGroups * kKeys * (G + 4)];
+    __shared__ K shared[kGroups * kKeys * (G + 4)];
     const int t = threadIdx.x % G, group = threadIdx.x / G;
-    C *s = shared + group * kKeys * (G + 4);
+    K *s = shared + group * kKeys * (G + 4);
     T *ax = static_cast<T *>(a.x);
-    const C inf = sizeof(C) == 8 ? C(CUDART_INF) : C(CUDART_INF_F);
-    const C last = a.descending ? -inf : inf;
     const int d = a.descending;
     const LL chunks = (a.n + CN - 1) / CN, units = a.numTads * chunks;
     for (LL u = (LL) blockIdx.x * kGroups + group; u < units; u += (LL) gridDim.x * kGroups) {
@@ -128,58 +149,98 @@ __global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int f
         // coalesced over linear positions, then every thread picks up its eight keys
         for (int idx = t; idx < CN; idx += G) {
             const LL i = first + idx;
-            s[slot<G>(idx & (kKeys - 1), idx / kKeys)] = i < a.n ? Elem<T>::load(base + view_offset(a.inner, i)) : last;
+            s[slot<G>(idx & (kKeys - 1), idx / kKeys)] =
+                i < a.n ? Key::to_key(Elem<T>::load(base + view_offset(a.inner, i)), d) : Key::kLast;
         }
         group_sync<G>();
-        C v[kKeys];
+        K v[kKeys];
 #pragma unroll
         for (int e = 0; e < kKeys; e++) v[e] = s[slot<G>(e, t)];
         group_sync<G>();
         if (fullSort) {
-            head_stages(v, d);
+            head_stages(v);
             for (int k = 2 * kKeys; k <= CN; k <<= 1) {
-                cross_step<C, G, true>(v, s, t, k / kKeys - 1, k / (2 * kKeys), d);
-                for (int j = k >> 2; j >= kKeys; j >>= 1) cross_step<C, G, false>(v, s, t, j / kKeys, j / kKeys, d);
-                tail_steps(v, d);
+                cross_step<K, G, true>(v, s, t, k / kKeys - 1, k / (2 * kKeys));
+                for (int j = k >> 2; j >= kKeys; j >>= 1) cross_step<K, G, false>(v, s, t, j / kKeys, j / kKeys);
+                tail_steps(v);
             }
         } else {
-            for (int j = CN >> 1; j >= kKeys; j >>= 1) cross_step<C, G, false>(v, s, t, j / kKeys, j / kKeys, d);
-            tail_steps(v, d);
+            for (int j = CN >> 1; j >= kKeys; j >>= 1) cross_step<K, G, false>(v, s, t, j / kKeys, j / kKeys);
+            tail_steps(v);
         }
 #pragma unroll
         for (int e = 0; e < kKeys; e++) s[slot<G>(e, t)] = v[e];
         group_sync<G>();
         for (int idx = t; idx < CN; idx += G) {
             const LL i = first + idx;
-            if (i < a.n) Elem<T>::store(base + view_offset(a.inner, i), s[slot<G>(idx & (kKeys - 1), idx / kKeys)]);
+            if (i < a.n)
+                Elem<T>::store(base + view_offset(a.inner, i), Key::from_key(s[slot<G>(idx & (kKeys - 1), idx / kKeys)], d));
         }
         group_sync<G>();
     }
 }
 
-// One step of stage a.k over global memory: the mirror step (a.j == 0) or the half-cleaner of stride a.j.
-// `half` = comparators per TAD (half of the length rounded up to a power of two), a power of two.
-template <class T>
-__global__ void __launch_bounds__(256) k_sort_global_step(const SortArgs a, LL half) {
+// L consecutive steps of stage a.k in one pass over global memory: the mirror step (MIRROR) or the
+// half-cleaner of stride a.j, followed by the next L - 1 half-cleaners. The 2^L positions that those steps
+// connect (a position and its images under every combination of the steps' masks) are loaded by one thread,
+// ordered in registers and written back, so a stage with s strides beyond the chunk size costs ceil(s / 3)
+// passes instead of s. Neighbouring threads own neighbouring positions in each of the 2^L loads.
+template <class T, int L, bool MIRROR>
+__global__ void __launch_bounds__(256) k_sort_global_pass(const SortArgs a, LL padded) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
+    typedef SortKey<C> Key;
+    typedef typename Key::K K;
+    constexpr int N = 1 << L;
     T *ax = static_cast<T *>(a.x);
-    const LL total = a.numTads * half, nthreads = (LL) gridDim.x * 256;
+    const LL high = MIRROR ? a.k >> 1 : a.j;          // the highest position bit these steps act on
+    LL mask[L];
+    mask[0] = MIRROR ? a.k - 1 : a.j;
+#pragma unroll
+    for (int l = 1; l < L; l++) mask[l] = high >> l;
+    const LL low = (high >> (L - 1)) - 1;             // position bits below the L bits a thread spans
+    const LL per = padded >> L, total = a.numTads * per, nthreads = (LL) gridDim.x * 256;
+    const int d = a.descending;
     for (LL u = (LL) blockIdx.x * 256 + threadIdx.x; u < total; u += nthreads) {
-        const LL tad = u / half, q = u - tad * half;
-        LL lo, hi;
-        if (a.j == 0) {
-            const LL hk = a.k >> 1, block = q / hk, r = q - block * hk;
-            lo = block * a.k + r; hi = block * a.k + (a.k - 1 - r);
-        } else {
-            lo = ((q & ~(a.j - 1)) << 1) | (q & (a.j - 1)); hi = lo + a.j;
-        }
-        if (hi >= a.n) continue;      // the partner lies past the end: it sorts last and stays
+        const LL tad = u / per, q = u - tad * per;
+        const LL first = ((q & ~low) << L) | (q & low);
         T *base = ax + view_offset(a.outer, tad);
-        T *pl = base + view_offset(a.inner, lo), *ph = base + view_offset(a.inner, hi);
-        const C vl = Elem<T>::load(pl), vh = Elem<T>::load(ph);
-        if (sorts_before(vh, vl, a.descending)) { Elem<T>::store(pl, vh); Elem<T>::store(ph, vl); }
+        LL idx[N];
+        K key[N];
+#pragma unroll
+        for (int c = 0; c < N; c++) {
+            LL i = first;
+#pragma unroll
+            for (int l = 0; l < L; l++)
+                if ((c >> l) & 1) i ^= mask[l];
+            idx[c] = i;
+            key[c] = i < a.n ? Key::to_key(Elem<T>::load(base + view_offset(a.inner, i)), d) : Key::kLast;
+        }
+#pragma unroll
+        for (int l = 0; l < L; l++) {
+#pragma unroll
+            for (int c = 0; c < N; c++) {
+                if ((c >> l) & 1) continue;
+                // the mirror image has the lower position bits flipped, which turns the later pairs around
+                if (MIRROR && l > 0 && (c & 1)) order_regs(key[c | (1 << l)], key[c]);
+                else order_regs(key[c], key[c | (1 << l)]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < N; c++)
+            if (idx[c] < a.n) Elem<T>::store(base + view_offset(a.inner, idx[c]), Key::from_key(key[c], d));
     }
+}
+
+template <class T, bool MIRROR>
+void launch_global(const SortArgs &a, int levels, LL padded, cudaStream_t st) {
+    LL blocks = ceil_div(a.numTads * (padded >> levels), 256);
+    const LL cap = (LL) kNumSMs * 32;
+    if (blocks > cap) blocks = cap;
+    const dim3 grid((unsigned) blocks), block(256);
+    if (levels == 1) launch_kernel(k_sort_global_pass<T, 1, MIRROR>, grid, block, st, a, padded);
+    else if (levels == 2) launch_kernel(k_sort_global_pass<T, 2, MIRROR>, grid, block, st, a, padded);
+    else launch_kernel(k_sort_global_pass<T, 3, MIRROR>, grid, block, st, a, padded);
 }
 
 template <class T, int G, int THREADS>
@@ -202,20 +263,27 @@ Status run_sort(SortArgs a, cudaStream_t st) {
     if (a.n <= 2048) { launch_chunks<T, 256, 256>(a, 1, st); ND_CUDA(cudaGetLastError()); return kOk; }
     launch_chunks<T, kBig, kBig>(a, 1, st);
     ND_CUDA(cudaGetLastError());
+    // The later stages finish on chip in chunks of 2048 keys: CTAs of 256 threads, several of which fit an SM
+    // and overlap their loads with each other's exchanges (one CTA of 1024 threads per SM cannot).
+    constexpr int kMergeThreads = 256, kMerge = kMergeThreads * kKeys;
     LL padded = kChunk;
     while (padded < a.n) padded <<= 1;
-    const LL half = padded >> 1, total = a.numTads * half;
-    LL blocks = ceil_div(total, 256);
-    const LL cap = (LL) kNumSMs * 32;
-    if (blocks > cap) blocks = cap;
     for (LL k = 2 * (LL) kChunk; k <= padded; k <<= 1) {
-        a.k = k; a.j = 0;
-        launch_kernel(k_sort_global_step<T>, dim3((unsigned) blocks), dim3(256), st, a, half);
-        for (LL j = k >> 2; j >= kChunk; j >>= 1) {
+        a.k = k;
+        // steps of this stage beyond a merge chunk: the mirror step, then strides k/4 ... kMerge; three per pass
+        int steps = 1;
+        for (LL j = k >> 2; j >= kMerge; j >>= 1) steps++;
+        int levels = steps < 3 ? steps : 3;
+        a.j = 0;
+        launch_global<T, true>(a, levels, padded, st);
+        LL j = k >> (1 + levels);          // the next stride after `levels` steps (k/2 is the mirror's high bit)
+        for (int left = steps - levels; left > 0; left -= levels) {
+            levels = left < 3 ? left : 3;
             a.j = j;
-            launch_kernel(k_sort_global_step<T>, dim3((unsigned) blocks), dim3(256), st, a, half);
+            launch_global<T, false>(a, levels, padded, st);
+            j >>= levels;
         }
-        launch_chunks<T, kBig, kBig>(a, 0, st);
+        launch_chunks<T, kMergeThreads, kMergeThreads>(a, 0, st);
         ND_CUDA(cudaGetLastError());
     }
     return kOk;

@@ -93,3 +93,23 @@ def test_sort_large_is_sorted_and_a_permutation(ops):
     assert abs(before[0] - after[0]) <= 1e-6 * before[1] and abs(before[1] - after[1]) <= 1e-9 * before[1]
     want = torch.sort(torch.randn(n, device="cuda", generator=g.manual_seed(5)))[0]
     assert torch.equal(x, want)
+
+
+@pytest.mark.parametrize("n", [40, 5000, 30000])
+def test_sort_total_order_of_zeros_and_nans(ops, n):
+    # on-chip keys are totally ordered: -0 before +0, NaNs (sign bit clear) after +inf; nothing is lost
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal(n).astype(np.float32)
+    x[rng.choice(n, 12, replace=False)] = [0.0, -0.0, 0.0, -0.0, np.nan, np.nan, np.inf, -np.inf, 0.0, -0.0, np.nan, 1.0]
+    for descending in (False, True):
+        dx = dev(x)
+        ops.sortFloat(None, dx, S.shape_info([1, n]), descending)
+        got = host(dx)
+        if descending:
+            got = got[::-1]
+        want = np.sort(x)                          # numpy: NaNs last
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = ~np.isnan(want)
+        np.testing.assert_array_equal(got[ok], want[ok])
+        zeros = got[got == 0]
+        assert len(zeros) == 6 and np.signbit(zeros[:3]).all() and not np.signbit(zeros[3:]).any()
