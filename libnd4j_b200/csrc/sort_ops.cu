@@ -232,12 +232,106 @@ __global__ void __launch_bounds__(256) k_sort_global_pass(const SortArgs a, LL p
     }
 }
 
+// The same pass for dense data, VK neighbouring positions per access: the steps treat neighbouring positions
+// alike (all strides are far larger than VK), so lane e of every access is an independent instance of the
+// scalar pass at position first + e. The mirror image of VK neighbouring positions is again VK neighbouring
+// positions, in reverse order: those vectors are reversed after loading and before storing.
+template <class T> struct SortVec {
+    static constexpr int VK = sizeof(T) == 8 ? 2 : 4;
+    struct alignas(sizeof(T) * VK) V { T v[VK]; };
+};
+
+template <class T, int L, bool MIRROR>
+__global__ void __launch_bounds__(256) k_sort_global_pass_vec(const SortArgs a, LL padded) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    typedef SortKey<C> Key;
+    typedef typename Key::K K;
+    typedef typename SortVec<T>::V V;
+    constexpr int N = 1 << L, VK = SortVec<T>::VK;
+    T *ax = static_cast<T *>(a.x);
+    const LL high = MIRROR ? a.k >> 1 : a.j;
+    LL mask[L];
+    mask[0] = MIRROR ? a.k - 1 : a.j;
+#pragma unroll
+    for (int l = 1; l < L; l++) mask[l] = high >> l;
+    const LL low = (high >> (L - 1)) - 1;
+    const LL per = (padded >> L) / VK, total = a.numTads * per, nthreads = (LL) gridDim.x * 256;
+    const int d = a.descending;
+    for (LL u = (LL) blockIdx.x * 256 + threadIdx.x; u < total; u += nthreads) {
+        const LL tad = u / per, q = (u - tad * per) * VK;
+        const LL first = ((q & ~low) << L) | (q & low);
+        T *base = ax + view_offset(a.outer, tad);
+        LL start[N];
+        K key[N][VK];
+#pragma unroll
+        for (int c = 0; c < N; c++) {
+            LL i = first;
+#pragma unroll
+            for (int l = 0; l < L; l++)
+                if ((c >> l) & 1) i ^= mask[l];
+            const bool reversed = MIRROR && (c & 1);
+            start[c] = reversed ? i - (VK - 1) : i;         // the lowest of the VK positions
+            if (start[c] + VK <= a.n) {
+                const V pack = *reinterpret_cast<const V *>(base + start[c]);
+#pragma unroll
+                for (int e = 0; e < VK; e++) key[c][reversed ? VK - 1 - e : e] = Key::to_key(Elem<T>::to_c(pack.v[e]), d);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VK; e++) {
+                    const LL pos = start[c] + e;
+                    key[c][reversed ? VK - 1 - e : e] = pos < a.n ? Key::to_key(Elem<T>::load(base + pos), d) : Key::kLast;
+                }
+            }
+        }
+#pragma unroll
+        for (int l = 0; l < L; l++) {
+#pragma unroll
+            for (int c = 0; c < N; c++) {
+                if ((c >> l) & 1) continue;
+                const bool turned = MIRROR && l > 0 && (c & 1);
+#pragma unroll
+                for (int e = 0; e < VK; e++) {
+                    if (turned) order_regs(key[c | (1 << l)][e], key[c][e]);
+                    else order_regs(key[c][e], key[c | (1 << l)][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < N; c++) {
+            const bool reversed = MIRROR && (c & 1);
+            if (start[c] + VK <= a.n) {
+                V pack;
+#pragma unroll
+                for (int e = 0; e < VK; e++) pack.v[e] = Elem<T>::from_c(Key::from_key(key[c][reversed ? VK - 1 - e : e], d));
+                *reinterpret_cast<V *>(base + start[c]) = pack;
+            } else {
+#pragma unroll
+                for (int e = 0; e < VK; e++) {
+                    const LL pos = start[c] + e;
+                    if (pos < a.n) Elem<T>::store(base + pos, Key::from_key(key[c][reversed ? VK - 1 - e : e], d));
+                }
+            }
+        }
+    }
+}
+
 template <class T, bool MIRROR>
 void launch_global(const SortArgs &a, int levels, LL padded, cudaStream_t st) {
-    LL blocks = ceil_div(a.numTads * (padded >> levels), 256);
+    constexpr int VK = SortVec<T>::VK;
+    const bool dense = (a.inner.rank == 0 || (a.inner.rank == 1 && a.inner.stride[0] == 1)) &&
+                       reinterpret_cast<uintptr_t>(a.x) % (sizeof(T) * VK) == 0 && view_strides_multiple_of(a.outer, VK);
+    LL blocks = ceil_div(a.numTads * (padded >> levels) / (dense ? VK : 1), 256);
     const LL cap = (LL) kNumSMs * 32;
     if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
     const dim3 grid((unsigned) blocks), block(256);
+    if (dense) {
+        if (levels == 1) launch_kernel(k_sort_global_pass_vec<T, 1, MIRROR>, grid, block, st, a, padded);
+        else if (levels == 2) launch_kernel(k_sort_global_pass_vec<T, 2, MIRROR>, grid, block, st, a, padded);
+        else launch_kernel(k_sort_global_pass_vec<T, 3, MIRROR>, grid, block, st, a, padded);
+        return;
+    }
     if (levels == 1) launch_kernel(k_sort_global_pass<T, 1, MIRROR>, grid, block, st, a, padded);
     else if (levels == 2) launch_kernel(k_sort_global_pass<T, 2, MIRROR>, grid, block, st, a, padded);
     else launch_kernel(k_sort_global_pass<T, 3, MIRROR>, grid, block, st, a, padded);

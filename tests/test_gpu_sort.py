@@ -64,7 +64,7 @@ def test_sort_walks_linear_positions(ops, kind):
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("shape,dim", [((64, 10), 1), ((64, 10), 0), ((33, 300), 1), ((7, 3000), 1), ((3, 9000), 1),
-                                       ((2, 20001), 1), ((5, 6, 7), 2), ((5, 6, 7), 0)])
+                                       ((2, 20001), 1), ((3, 20000), 1), ((5, 6, 7), 2), ((5, 6, 7), 0)])
 @pytest.mark.parametrize("kind", ["c", "f"])
 @pytest.mark.parametrize("descending", [False, True])
 def test_sort_tad(ops, dt, name, shape, dim, kind, descending):
