@@ -131,7 +131,7 @@ ND_D void cross_step(K (&v)[kKeys], K *s, int t, int mt, int highT) {
 // fullSort: sorts every chunk (stages 2 ... CN). Otherwise: the strides CN/2 ... 1 of a later stage.
 // THREADS / G chunks are worked on by one CTA at a time (G = 32: a warp per chunk, no CTA barriers).
 template <class T, int G, int THREADS>
-__global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int fullSort) {
+__global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int fullSort, int dense) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
     typedef SortKey<C> Key;
@@ -146,17 +146,31 @@ __global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int f
     for (LL u = (LL) blockIdx.x * kGroups + group; u < units; u += (LL) gridDim.x * kGroups) {
         const LL tad = u / chunks, first = (u - tad * chunks) * CN;
         T *base = ax + view_offset(a.outer, tad);
-        // coalesced over linear positions, then every thread picks up its eight keys
-        for (int idx = t; idx < CN; idx += G) {
-            const LL i = first + idx;
-            s[slot<G>(idx & (kKeys - 1), idx / kKeys)] =
-                i < a.n ? Key::to_key(Elem<T>::load(base + view_offset(a.inner, i)), d) : Key::kLast;
-        }
-        group_sync<G>();
+        // dense chunks that lie wholly inside the TAD: a thread's eight keys are 16-byte packs of its own
+        const bool direct = dense && first + CN <= a.n;
         K v[kKeys];
+        if (direct) {
+            constexpr int PER = 16 / sizeof(T), PACKS = kKeys / PER;
+            struct alignas(16) Pack16 { T v[PER]; };
+            const Pack16 *src = reinterpret_cast<const Pack16 *>(base + first + (LL) t * kKeys);
 #pragma unroll
-        for (int e = 0; e < kKeys; e++) v[e] = s[slot<G>(e, t)];
-        group_sync<G>();
+            for (int p = 0; p < PACKS; p++) {
+                const Pack16 pk = src[p];
+#pragma unroll
+                for (int e = 0; e < PER; e++) v[p * PER + e] = Key::to_key(Elem<T>::to_c(pk.v[e]), d);
+            }
+        } else {
+            // coalesced over linear positions through shared memory, then every thread picks up its eight keys
+            for (int idx = t; idx < CN; idx += G) {
+                const LL i = first + idx;
+                s[slot<G>(idx & (kKeys - 1), idx / kKeys)] =
+                    i < a.n ? Key::to_key(Elem<T>::load(base + view_offset(a.inner, i)), d) : Key::kLast;
+            }
+            group_sync<G>();
+#pragma unroll
+            for (int e = 0; e < kKeys; e++) v[e] = s[slot<G>(e, t)];
+            group_sync<G>();
+        }
         if (fullSort) {
             head_stages(v);
             for (int k = 2 * kKeys; k <= CN; k <<= 1) {
@@ -167,6 +181,21 @@ __global__ void __launch_bounds__(THREADS) k_sort_chunks(const SortArgs a, int f
         } else {
             for (int j = CN >> 1; j >= kKeys; j >>= 1) cross_step<K, G, false>(v, s, t, j / kKeys, j / kKeys);
             tail_steps(v);
+        }
+        if (direct) {
+            constexpr int PER = 16 / sizeof(T), PACKS = kKeys / PER;
+            struct alignas(16) Pack16 { T v[PER]; };
+            Pack16 *dst = reinterpret_cast<Pack16 *>(base + first + (LL) t * kKeys);
+#pragma unroll
+            for (int p = 0; p < PACKS; p++) {
+                Pack16 pk;
+#pragma unroll
+                for (int e = 0; e < PER; e++) pk.v[e] = Elem<T>::from_c(Key::from_key(v[p * PER + e], d));
+                dst[p] = pk;
+            }
+            // the exchanges of the next chunk reuse the shared-memory slots this one may still be reading
+            group_sync<G>();
+            continue;
         }
 #pragma unroll
         for (int e = 0; e < kKeys; e++) s[slot<G>(e, t)] = v[e];
@@ -342,7 +371,11 @@ void launch_chunks(const SortArgs &a, int fullSort, cudaStream_t st) {
     LL blocks = ceil_div(a.numTads * ceil_div(a.n, G * kKeys), THREADS / G);
     const LL cap = (LL) kNumSMs * 32;
     if (blocks > cap) blocks = cap;
-    launch_kernel(k_sort_chunks<T, G, THREADS>, dim3((unsigned) blocks), dim3(THREADS), st, a, fullSort);
+    // unit-stride TADs whose starts keep 16-byte alignment
+    constexpr int PER = 16 / sizeof(T);
+    const int dense = (a.inner.rank == 0 || (a.inner.rank == 1 && a.inner.stride[0] == 1)) && aligned16(a.x) &&
+                      view_strides_multiple_of(a.outer, PER);
+    launch_kernel(k_sort_chunks<T, G, THREADS>, dim3((unsigned) blocks), dim3(THREADS), st, a, fullSort, dense);
 }
 
 template <class T>
