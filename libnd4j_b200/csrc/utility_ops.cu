@@ -203,17 +203,34 @@ __global__ void __launch_bounds__(kCopyBlock) k_swap_tads(const SwapArgs a) {
 // map whose swaps share TADs depends on that order. The swaps are sorted into rounds: a swap goes one round
 // after the latest earlier swap that touches either of its TADs. The swaps of a round are disjoint and run
 // as one launch; the usual map (disjoint pairs) is a single round.
-Status shuffle_rounds(const int *map, LL numTads, std::vector<std::vector<int2> > *rounds) {
-    std::vector<int> last((size_t) numTads, 0);
+// `flat` receives the swaps grouped by round (in map order inside a round), `counts` the swaps per round.
+Status shuffle_rounds(const int *map, LL numTads, std::vector<int2> *flat, std::vector<size_t> *counts) {
+    std::vector<int> last((size_t) numTads, 0), roundOf;
+    std::vector<int2> swaps;
+    swaps.reserve((size_t) numTads);
+    roundOf.reserve((size_t) numTads);
+    int rounds = 0;
     for (LL r = 0; r < numTads; r++) {
         const int m = map[r];
         if (m < 0 || m == r) continue;
         if (m >= numTads) return bad_arg("shuffle: the map names a TAD past the last one");
         const int round = (last[r] > last[m] ? last[r] : last[m]) + 1;
         last[r] = last[m] = round;
-        if ((size_t) round > rounds->size()) rounds->resize(round);
-        (*rounds)[round - 1].push_back(make_int2((int) r, m));
+        if (round > rounds) rounds = round;
+        swaps.push_back(make_int2((int) r, m));
+        roundOf.push_back(round);
     }
+    counts->assign((size_t) rounds, 0);
+    if (rounds <= 1) {          // the usual map: disjoint pairs, one launch
+        if (rounds == 1) (*counts)[0] = swaps.size();
+        flat->swap(swaps);
+        return kOk;
+    }
+    for (size_t i = 0; i < swaps.size(); i++) (*counts)[roundOf[i] - 1]++;
+    std::vector<size_t> at((size_t) rounds, 0);
+    for (int k = 1; k < rounds; k++) at[k] = at[k - 1] + (*counts)[k - 1];
+    flat->resize(swaps.size());
+    for (size_t i = 0; i < swaps.size(); i++) (*flat)[at[roundOf[i] - 1]++] = swaps[i];
     return kOk;
 }
 
@@ -551,14 +568,11 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
         if (xt.length == 0) continue;
         const LL numTads = xd.length / xt.length;
         if (numTads > 0x7fffffffLL) return bad_arg("shuffle: more TADs than an int map can name");
-        std::vector<std::vector<int2> > rounds;
-        ND_TRY(shuffle_rounds(shuffleMap, numTads, &rounds));
-        size_t total = 0;
-        for (size_t r = 0; r < rounds.size(); r++) total += rounds[r].size();
-        if (total == 0) continue;
         std::vector<int2> flat;
-        flat.reserve(total);
-        for (size_t r = 0; r < rounds.size(); r++) flat.insert(flat.end(), rounds[r].begin(), rounds[r].end());
+        std::vector<size_t> rounds;         // swaps per round
+        ND_TRY(shuffle_rounds(shuffleMap, numTads, &flat, &rounds));
+        const size_t total = flat.size();
+        if (total == 0) continue;
         // every array's lists get their own part of the workspace: an earlier array's launches may still read theirs
         void *ws = nullptr;
         ND_TRY(workspace(st, kWorkspaceScratch + used + total * sizeof(int2), &ws, nullptr));
@@ -574,8 +588,8 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
         a.chunks = ceil_div(a.tadLen, a.chunkLen);
         size_t at = 0;
         for (size_t r = 0; r < rounds.size(); r++) {
-            a.pairs = dev + at; a.n = (LL) rounds[r].size();
-            at += rounds[r].size();
+            a.pairs = dev + at; a.n = (LL) rounds[r];
+            at += rounds[r];
             LL blocks = ceil_div(a.n * a.chunks, kCopyBlock / 32);
             const LL cap = (LL) kNumSMs * 16;
             if (blocks > cap) blocks = cap;
