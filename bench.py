@@ -152,6 +152,18 @@ class ClockSampler:
                 "source": self.source}
 
 
+def host_threads():
+    """Threads for the CPU arms: the physical cores this process may run on (hyper-threads add nothing to
+    these streaming loops). Set explicitly because launchers such as torchrun export OMP_NUM_THREADS=1."""
+    allowed = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        import psutil
+        physical = psutil.cpu_count(logical=False) or allowed
+    except Exception:
+        physical = allowed
+    return max(1, min(allowed, physical))
+
+
 def make_inputs(rows):
     x = np.random.default_rng(1).standard_normal((rows, COLS), dtype=np.float32)
     b = np.random.default_rng(2).standard_normal(COLS, dtype=np.float32)
@@ -193,16 +205,19 @@ def run_reference_arm(args):
     if rank != 0:
         return
     from oracle import reference
-    rows = 2048   # bounded sample: 1/8 of the rows, same row width
     from libnd4j_b200 import shape as S
     if reference.available():
+        rows = ROWS   # the whole configured array: about 0.1 s per step on a multi-core host
         ref, kind = reference.Reference(), "reference"
         what = "reference CPU loops (OpenMP)"
     else:
-        # the reference's own build is absent: time the oracle's C restatement of the same loops instead
+        # the reference's own build is absent: time the oracle's scalar C restatement of the same loops on a
+        # bounded sample instead
+        rows = 2048
         from oracle import port
         ref, kind = port.Port(), "port"
         what = "oracle port of the reference CPU loops"
+    ref.set_threads(host_threads())
     cores = ref.threads()
     x, b, y = make_inputs(rows)
     xi, bi = S.shape_info([rows, COLS]), S.shape_info([1, COLS])
@@ -226,7 +241,8 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "elementwise chain f32 [16384,4096] (sampled: %d rows)" % rows},
+        "config": {"workload": "elementwise chain f32 [16384,4096]: execBroadcast Add(dim 1) -> execTransform Tanh -> "
+                               "execPairwiseTransform Multiply" + ("" if rows == ROWS else " (sampled: %d rows)" % rows)},
         "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -650,13 +666,13 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import reference
         if reference.available():
-            rows = 2048
-            gel, cores, secs = cpu_reference_chain(rows, repeats=2)
+            rows = ROWS
+            gel, cores, secs = cpu_reference_chain(rows, repeats=3, threads=host_threads())
             cpu = {"value": round(gel, 4), "unit": "Gelem/s", "cores": cores, "kind": "reference",
-                   "sample": "%d of %d rows (same row width), best of 2 after one warm-up pass, %.1f ms" % (rows, ROWS, secs * 1e3)}
+                   "sample": "all %d rows, best of 3 after one warm-up pass, %.1f ms" % (rows, secs * 1e3)}
         else:
             rows = 512      # the scalar port: a smaller sample keeps this leg at a few seconds
-            gel, cores, secs = cpu_reference_chain(rows, repeats=1, use_port=True)
+            gel, cores, secs = cpu_reference_chain(rows, repeats=1, threads=host_threads(), use_port=True)
             cpu = {"value": round(gel, 4), "unit": "Gelem/s", "cores": cores, "kind": "port",
                    "sample": "%d of %d rows (same row width), oracle port, best of 1 after one warm-up pass, %.1f ms" % (rows, ROWS, secs * 1e3)}
 

@@ -253,7 +253,8 @@ unsigned long long nd4jb200_launch_count(void) { return g_launches.load(std::mem
 
 int nd4jb200_set_tuning(int key, long long value) {
     if (key < 0 || key >= kTuneCount || value < (key == kTuneOverlapLaunch ? 0 : 1) || (key == kTuneMaxCluster && value > 8) ||
-        (key == kTuneRowThreadsPerSm && value > kMaxRowThreadsPerSm)) {
+        (key == kTuneRowThreadsPerSm && value > kMaxRowThreadsPerSm) ||
+        ((key == kTuneColCtasPerSm || key == kTuneRowCtasPerSm) && value > 64)) {
         set_error("nd4jb200_set_tuning: unknown key or value out of range");
         return kBadArgument;
     }
@@ -459,9 +460,10 @@ int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, c
         }
         // the positions go behind everything a split reduction may use of the workspace
         void *ws = nullptr;
-        ND_TRY(workspace(as_stream(stream), kScalarWorkspace + dtype_size(dtype) * (size_t) c.xPlan.numTads, &ws, nullptr));
-        void *positions = static_cast<char *>(ws) + kScalarWorkspace;
-        c.x = x; c.extra = nullptr; c.z = positions; c.finishLen = c.xPlan.tadLen;
+        ND_TRY(workspace(as_stream(stream), kScalarWorkspace + sizeof(LL) * (size_t) c.xPlan.numTads, &ws, nullptr));
+        LL *positions = reinterpret_cast<LL *>(static_cast<char *>(ws) + kScalarWorkspace);
+        // exact 64-bit positions: the element type cannot hold them (half beyond 2048, float beyond 2^24)
+        c.x = x; c.extra = nullptr; c.z = positions; c.zIndex = positions; c.finishLen = c.xPlan.tadLen;
         ND_TRY(BY_DTYPE(dtype, index_reduce, 0, c, as_stream(stream)));
         IsMaxArgs m;
         m.index = positions; m.z = z; m.numTads = zPlan.numTads; m.tadLen = zPlan.tadLen;

@@ -99,6 +99,7 @@ template <int kind, class C> struct Reduce3 {
 // -1e37 / 1e37 for max / min, 1e-37 for absolute max (ops.h:3075, 3290, 3345, 3410).
 template <int kind, class C> struct IndexExtreme {
     struct State { C v; int pad; LL i; };
+    static constexpr bool kIndexResult = true;
     static constexpr int kInputs = 1;
     static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 0;
@@ -153,6 +154,7 @@ template <int kind, class C> struct IndexExtreme {
 // extraParams {compare, eps, mode}; -1 when none does (ops.h:3079-3200).
 template <int kind, class C> struct IndexMatch {
     struct State { LL i; };
+    static constexpr bool kIndexResult = true;
     static constexpr int kInputs = 1;
     static constexpr int kColBytes = 8;    // bytes one lane loads per row in the across-TAD kernel
     static constexpr int kParams = 3;

@@ -58,6 +58,9 @@ struct ReduceArgs {
     LL colStrideX, colStrideY;   // across-TAD: element stride between consecutive elements of a TAD
     View xOuterHi, yOuterHi;     // across-TAD: outer view without its contiguous axis
     LL finishLen;        // n handed to finish() (tadLen)
+    LL *zIndex;          // index reductions only: when set, the winning position of TAD r is written here as an
+                         // exact 64-bit integer instead of into z in the element type (half cannot hold
+                         // positions above 2048 exactly, float none above 2^24)
 };
 
 constexpr int kBlock = 256;
@@ -83,6 +86,18 @@ ND_D void fold_pack(typename P::State &s, const Pack<T> &xv, const Pack<T> &yv, 
         ya[k] = P::kInputs == 2 ? Elem<T>::to_c(yv.v[k]) : C(0);
     }
     P::template accum_many<N>(s, xa, ya, j0, 1, p);
+}
+
+// One result per TAD. Policies whose state carries a position (`State::i`, marked by kIndexResult) can deliver
+// it exactly through ReduceArgs::zIndex.
+template <class P, class = void> struct HasIndexResult { static constexpr bool value = false; };
+template <class P> struct HasIndexResult<P, decltype((void) P::kIndexResult)> { static constexpr bool value = true; };
+template <class T, class P>
+ND_D void write_result(const ReduceArgs &a, LL r, const typename P::State &s, const typename Elem<T>::C *p) {
+    if constexpr (HasIndexResult<P>::value) {
+        if (a.zIndex) { a.zIndex[r] = s.i; return; }
+    }
+    static_cast<T *>(a.z)[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
 }
 
 // Policies that can fold a whole tile of packs at once declare kTile (see pol::IndexExtreme).
@@ -118,7 +133,6 @@ __global__ void __launch_bounds__(kBlock, RowBudget<T, P>::v) k_reduce_tads(cons
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     const T *ax = static_cast<const T *>(a.x);
     const T *ay = static_cast<const T *>(a.y);
-    T *az = static_cast<T *>(a.z);
 
     const int g = a.group;
     const int groupsPerBlock = kBlock / g;
@@ -224,7 +238,7 @@ __global__ void __launch_bounds__(kBlock, RowBudget<T, P>::v) k_reduce_tads(cons
             __syncthreads();
         }
         if (a.splits == 1) {
-            if (active && lane == 0) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+            if (active && lane == 0) write_result<T, P>(a, r, s, p);
             continue;
         }
         State *parts = reinterpret_cast<State *>(a.partials);
@@ -264,7 +278,7 @@ __global__ void __launch_bounds__(kBlock, RowBudget<T, P>::v) k_reduce_tads(cons
             }
             __syncthreads();
         }
-        if (last && lane == 0) az[r] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        if (last && lane == 0) write_result<T, P>(a, r, m, p);
     }
 }
 
@@ -296,7 +310,6 @@ ND_D void cols_finish(const ReduceArgs &a, const typename P::State (&s)[W], type
     typedef typename P::State State;
     constexpr int kTile = 32 * W;
     State (*rows)[kTile] = reinterpret_cast<State (*)[kTile]>(rowsFlat);
-    T *az = static_cast<T *>(a.z);
     State *parts = reinterpret_cast<State *>(a.partials);
 #pragma unroll
     for (int w = 0; w < W; w++) rows[threadIdx.y][threadIdx.x * W + w] = s[w];
@@ -333,7 +346,7 @@ ND_D void cols_finish(const ReduceArgs &a, const typename P::State (&s)[W], type
         if (rank != 0) return;
     }
     if (owner) {
-        if (a.splits == 1) az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        if (a.splits == 1) write_result<T, P>(a, tr, m, p);
         else parts[(LL) (blockIdx.y / a.cluster) * a.partSplitStride + tr] = m;
     }
     if (a.splits == 1 || a.counters == nullptr) return;
@@ -373,7 +386,7 @@ ND_D void cols_finish(const ReduceArgs &a, const typename P::State (&s)[W], type
         State m = rows[0][t];
 #pragma unroll
         for (int k = 1; k < kColRows; k++) P::merge(m, rows[k][t]);
-        az[tr] = Elem<T>::from_c(P::finish(m, a.finishLen, p));
+        write_result<T, P>(a, tr, m, p);
     }
 }
 
@@ -387,7 +400,6 @@ __global__ void __launch_bounds__(32 * kColRows, 4) k_reduce_cols(const ReduceAr
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
     const T *ax = static_cast<const T *>(a.x);
     const T *ay = static_cast<const T *>(a.y);
-    T *az = static_cast<T *>(a.z);
 
     const LL tilesPerHi = (a.colLo + 32 * W - 1) / (32 * W);
     const LL hi = blockIdx.x / tilesPerHi;
@@ -460,7 +472,6 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
     typedef typename P::State State;
     C p[P::kParams ? P::kParams : 1];
     load_params<T, P::kParams>(static_cast<const T *>(a.extra), p);
-    T *az = static_cast<T *>(a.z);
     const State *parts = reinterpret_cast<const State *>(a.partials);
     if (a.partSplitStride != 1) {
         for (LL r = (LL) blockIdx.x * kBlock + threadIdx.x; r < a.numTads; r += (LL) gridDim.x * kBlock) {
@@ -474,7 +485,7 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
                 P::merge(s, q0); P::merge(s, q1); P::merge(s, q2); P::merge(s, q3);
             }
             for (; k < a.splits; k++) P::merge(s, src[(LL) k * a.partSplitStride]);
-            az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+            write_result<T, P>(a, r, s, p);
         }
         return;
     }
@@ -485,7 +496,7 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
         P::init(s);
         for (int k = lane; k < a.splits; k += 32) P::merge(s, parts[r * a.partTadStride + k]);
         group_merge<P>(s, 32);
-        if (lane == 0) az[r] = Elem<T>::from_c(P::finish(s, a.finishLen, p));
+        if (lane == 0) write_result<T, P>(a, r, s, p);
     }
 }
 

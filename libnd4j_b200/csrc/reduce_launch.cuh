@@ -15,6 +15,7 @@ struct ReduceCall {
     TadPlan yPlan;               // only when y != nullptr
     bool yBroadcast = false;     // y (or x) is a single TAD reused for every TAD of the other operand
     LL finishLen = 0;            // n handed to the policy's finish()
+    LL *zIndex = nullptr;        // index reductions: exact 64-bit positions go here instead of into z
 };
 
 // Workspace layout: [256-byte result slot][kCounterSlots arrival counters][partial states]. The
@@ -58,6 +59,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     a.yOuter = two ? c.yPlan.outer : c.xPlan.outer;
     a.yInner = two ? c.yPlan.inner : c.xPlan.inner;
     a.finishLen = c.finishLen;
+    a.zIndex = c.zIndex;
     a.splits = 1; a.cluster = 1; a.group = 32; a.mode = 2;
     a.partTadStride = 1; a.partSplitStride = 1;
     a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;

@@ -3,6 +3,7 @@
 #include <map>
 #include <mutex>
 #include <sstream>
+#include <vector>
 
 namespace nd4jb200 {
 
@@ -28,6 +29,10 @@ namespace {
 struct Block { void *dev = nullptr; size_t cap = 0; void *host = nullptr; };
 std::mutex g_mu;
 std::map<std::pair<int, cudaStream_t>, Block> g_blocks;
+// Blocks that were outgrown. They stay allocated until release_workspaces(): a caller may have handed out
+// pointers into one (result slots, position lists) that launches still queued on the stream will use, and a
+// block grows by half each time, so everything retired together is smaller than twice the live block.
+std::vector<void *> g_retired;
 }  // namespace
 
 Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot) {
@@ -38,14 +43,14 @@ Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot)
     if (bytes > b.cap) {
         size_t want = bytes < (size_t(4) << 20) ? (size_t(4) << 20) : bytes + bytes / 2;
         if (b.dev) {
-            // work queued on the stream may still read the old block
-            ND_CUDA(cudaStreamSynchronize(stream));
-            ND_CUDA(cudaFree(b.dev));
+            g_retired.push_back(b.dev);
             b.dev = nullptr; b.cap = 0;
         }
         ND_CUDA(cudaMalloc(&b.dev, want));
-        // arrival counters live in this block and must start at zero
-        ND_CUDA(cudaMemset(b.dev, 0, want));
+        // arrival counters live in this block and must start at zero. The fill is ordered on the stream the
+        // block belongs to, i.e. in front of the launch that asked for it: a fill on the legacy default stream
+        // would not be ordered against a non-blocking stream.
+        ND_CUDA(cudaMemsetAsync(b.dev, 0, want, stream));
         b.cap = want;
     }
     if (hostSlot && !b.host) ND_CUDA(cudaMallocHost(&b.host, 64));
@@ -61,6 +66,8 @@ void release_workspaces() {
         if (kv.second.host) cudaFreeHost(kv.second.host);
     }
     g_blocks.clear();
+    for (void *p : g_retired) cudaFree(p);
+    g_retired.clear();
 }
 
 }  // namespace nd4jb200

@@ -23,7 +23,8 @@ Status cuda_fail(cudaError_t e, const char *where);
     } while (0)
 
 // Scratch memory owned by the library, one block per (device, stream) so that calls on
-// different streams never share it. The block only ever grows; growing synchronises the device.
+// different streams never share it. The block only ever grows; an outgrown block is kept until
+// release_workspaces(), so pointers into it stay valid for work already queued.
 // `hostSlot`, when requested, is a 64-byte pinned buffer used to bring scalar results back.
 Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot);
 // Layout of a workspace block: [256-byte result slot][kCounterSlots arrival counters, always left zero]

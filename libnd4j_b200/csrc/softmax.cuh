@@ -311,7 +311,7 @@ Status run_softmax(const SoftmaxArgs &a, cudaStream_t stream) {
 // strict "currMax < x" scan keeps), 0 elsewhere. The positions come from the IndexMax reduction of the
 // indexreduce family; this kernel only writes the marks: element j of TAD r gets (j == index[r]).
 struct IsMaxArgs {
-    const void *index;   // one position per TAD, stored in the element type
+    const LL *index;     // one exact position per TAD
     void *z;
     LL numTads, tadLen;
     View zOuter, zInner;
@@ -321,13 +321,12 @@ template <class T>
 __global__ void __launch_bounds__(kSmBlock) k_ismax_mark(const IsMaxArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
-    const T *idx = static_cast<const T *>(a.index);
     T *az = static_cast<T *>(a.z);
     const LL total = a.numTads * a.tadLen;
     const LL nthreads = (LL) gridDim.x * kSmBlock;
     for (LL i = (LL) blockIdx.x * kSmBlock + threadIdx.x; i < total; i += nthreads) {
         const LL r = i / a.tadLen, j = i - r * a.tadLen;
-        const LL hit = (LL) Elem<T>::load(idx + r);
+        const LL hit = __ldg(a.index + r);
         Elem<T>::store(az + view_offset(a.zOuter, r) + view_offset(a.zInner, j), j == hit ? C(1) : C(0));
     }
 }

@@ -509,8 +509,15 @@ int nd4jb200_pull_rows(void *stream, int dtype, const void *x, void *z, Nd4jLong
     PullArgs a;
     a.x = x; a.z = z; a.targets = nullptr; a.n = n; a.tadLen = xt.length;
     a.indexes = indexes; a.xOffsets = tadOffsets; a.zOffsets = zTadOffsets;
-    ND_TRY(linear_view(xt, &a.xInner));
-    ND_TRY(linear_view(zt, &a.zInner));
+    // both sides walk by elementWiseStride only when both have one; otherwise element i is the i-th c-order
+    // coordinate of each TAD's own shape (blas/cpu/NativeOps.cpp:2072-2101)
+    if (xt.ews >= 1 && zt.ews >= 1) {
+        ND_TRY(linear_view(xt, &a.xInner));
+        ND_TRY(linear_view(zt, &a.zInner));
+    } else {
+        ND_TRY(coord_view(xt, &a.xInner));
+        ND_TRY(coord_view(zt, &a.zInner));
+    }
     const int bytes = dtype_bytes(dtype);
     a.dense = unit_run(a.xInner) && unit_run(a.zInner) && (xt.length * bytes) % 16 == 0;
     return launch_pull(bytes, a, as_stream(stream));

@@ -63,6 +63,75 @@ class Reference:
         self.lib.ref_convertTypes(int(src_type), _p(x), ctypes.c_longlong(x.size), int(dst_type), _p(z))
         return z
 
+    # ---- memory-movement utilities: the CPU NativeOps members themselves (oracle/ref_nativeops.cpp) ----
+    @staticmethod
+    def _ptrs(arrays):
+        return (ctypes.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+
+    def flatten(self, offset, order, z, z_info, x, x_info):
+        """NativeOps::flatten* (blas/cpu/NativeOps.cpp:1530-1660, 1797-1860); float and double."""
+        zi, xi = _li(z_info), _li(x_info)
+        self._f("ref_flatten", x)(int(offset), ctypes.c_char(order.encode()), _p(z), _p(zi), _p(x), _p(xi))
+        return z
+
+    def concat(self, dimension, arrays, infos, z, z_info):
+        """NativeOps::concat* -> SpecialMethods<T>::concatCpuGeneric (include/ops/impl/specials.cpp:17-120)."""
+        keep = [_li(i) for i in infos]
+        zi = _li(z_info)
+        self._f("ref_concat", z)(int(dimension), len(arrays), self._ptrs(arrays), self._ptrs(keep), _p(z), _p(zi))
+        return z
+
+    def pull_rows(self, x, x_info, z, z_info, indexes, tad_info, tad_offsets, ztad_info, ztad_offsets):
+        """NativeOps::pullRows* (blas/cpu/NativeOps.cpp:2045-2116); float and double."""
+        a = [_li(v) for v in (x_info, z_info, indexes, tad_info, tad_offsets, ztad_info, ztad_offsets)]
+        self._f("ref_pullRows", x)(_p(x), _p(a[0]), _p(z), _p(a[1]), ctypes.c_longlong(len(a[2])), _p(a[2]), _p(a[3]),
+                                   _p(a[4]), _p(a[5]), _p(a[6]))
+        return z
+
+    def tear(self, x, x_info, targets, z_info, tad_info, tad_offsets):
+        """NativeOps::tear* (blas/cpu/NativeOps.cpp:2119-2174)."""
+        xi, zi, ti, to = _li(x_info), _li(z_info), _li(tad_info), _li(tad_offsets)
+        self._f("ref_tear", x)(_p(x), _p(xi), self._ptrs(targets), _p(zi), _p(ti), _p(to))
+        return targets
+
+    def shuffle(self, arrays, infos, shuffle_map, tad_infos, tad_offsets):
+        """NativeOps::shuffle* in place (blas/cpu/NativeOps.cpp:2266-2380); float and double."""
+        ki, kt, ko = [_li(i) for i in infos], [_li(i) for i in tad_infos], [_li(i) for i in tad_offsets]
+        m = _ii(shuffle_map)
+        self._f("ref_shuffle", arrays[0])(self._ptrs(arrays), self._ptrs(ki), self._ptrs(arrays), self._ptrs(ki),
+                                          len(arrays), _p(m), self._ptrs(kt), self._ptrs(ko))
+        return arrays
+
+    def average(self, arrays, z, propagate):
+        """NativeOps::average* -> SpecialMethods<T>::averageGeneric (specials.cpp:374-433); float and double."""
+        self._f("ref_average", arrays[0])(self._ptrs(arrays), _p(z), len(arrays), ctypes.c_longlong(arrays[0].size),
+                                          1 if propagate else 0)
+        return z
+
+    def accumulate(self, arrays, z):
+        """NativeOps::accumulate* -> SpecialMethods<T>::accumulateGeneric (specials.cpp:344-371)."""
+        self._f("ref_accumulate", z)(self._ptrs(arrays), _p(z), len(arrays), ctypes.c_longlong(z.size))
+        return z
+
+    def sort(self, x, x_info, descending):
+        """NativeOps::sort* -> SpecialMethods<T>::sortGeneric (specials.cpp:547-549), in place; float and double."""
+        xi = _li(x_info)
+        self._f("ref_sort", x)(_p(x), _p(xi), 1 if descending else 0)
+        return x
+
+    def sort_tad(self, x, x_info, dims, descending):
+        """NativeOps::sortTad* -> SpecialMethods<T>::sortTadGeneric (specials.cpp:552-564), in place."""
+        xi, d = _li(x_info), _ii(dims)
+        tad_info, tad_off = self.tad(x_info, dims)
+        self._f("ref_sortTad", x)(_p(x), _p(xi), _p(d), len(d), _p(tad_info), _p(tad_off), 1 if descending else 0)
+        return x
+
+    def sort_coo_indices(self, indices, values, rank):
+        """NativeOps::sortCooIndices* (include/ops/impl/specials_sparse.cpp), in place: `indices` holds
+        length x rank coordinates, `values` the matching values."""
+        self._f("ref_sortCooIndices", values)(_p(indices), _p(values), ctypes.c_longlong(values.size), int(rank))
+        return indices, values
+
     def threads(self):
         return self.lib.ref_omp_max_threads()
 

@@ -45,3 +45,11 @@ def real_ref():
     if not reference.available():
         pytest.skip("oracle/_ref/libnd4jref.so not built (needs the reference checkout)")
     return reference.Reference()
+
+
+@pytest.fixture(scope="session")
+def maybe_ref():
+    """The reference build when oracle/_ref is present, else None: GPU tests of the memory-movement utilities
+    compare with it directly in addition to the restatements it pins (tests/test_oracle_utilities.py)."""
+    from oracle import reference
+    return reference.Reference() if reference.available() else None

@@ -463,3 +463,33 @@ def test_ismax_first_maximum_wins(ops, real_ref, shape, extra):
     np.testing.assert_array_equal(host(dz), want)
     if extra is None:
         assert host(dz).sum() == 1 and host(dz)[int(x.argmax())] == 1
+
+
+def test_ismax_positions_beyond_what_the_element_type_can_hold(ops, real_ref):
+    """The winning position is carried as a 64-bit integer: half cannot represent positions above 2048 and
+    float none above 2^24 exactly, and the reference scans with an integer index (special_ops.h:2199-2260)."""
+    # half rows of 5001 elements with the maximum at odd positions far beyond 2048
+    rows, cols = 6, 5001
+    x = np.zeros((rows, cols), np.float16)
+    where = [2049, 3001, 4097, 4999, 5000, 2051]
+    for r, j in enumerate(where):
+        x[r, j] = 3.0
+        x[r, (j + 7) % cols if (j + 7) % cols > j else j] = 3.0          # a later duplicate where it fits
+    info = S.shape_info([rows, cols])
+    ex = np.array([1, 1], np.float16)
+    dz = dev(np.full(x.size, 7, np.float16))
+    ops.execTransformHalf(None, 41, dev(x), info, dz, info, dev(ex))
+    got = host(dz).reshape(rows, cols)
+    assert (got.sum(1) == 1).all()
+    assert [int(g.argmax()) for g in got] == where
+    # float, whole array of 2^24 + 1025 elements with the maximum at an odd position above 2^24
+    n = (1 << 24) + 1025
+    xf = np.zeros(n, np.float32)
+    xf[(1 << 24) + 1001] = 2.0
+    xf[(1 << 24) + 1003] = 2.0
+    finfo = S.shape_info([1, n])
+    dz = torch.full((n,), 7.0, device="cuda")
+    ops.execTransformFloat(None, 41, dev(xf), finfo, dz, finfo, None)
+    assert int(dz.sum().item()) == 1 and int(dz.argmax().item()) == (1 << 24) + 1001
+    want = real_ref.transform(41, xf.copy(), finfo, np.full(n, 7, np.float32), finfo, None)
+    np.testing.assert_array_equal(host(dz), want)

@@ -1,12 +1,15 @@
 """sort / sortTad on the GPU (NativeOps.h:2940-2952; include/ops/impl/specials.cpp:457-564). A sorted
 sequence does not depend on the sorting algorithm, so the expectation is numpy's sort of the same values laid
-out over the same positions; inputs have no NaN, and equal values are interchangeable."""
+out over the same positions (tests/test_oracle_utilities.py holds that expectation against the reference's own
+quicksort), and where oracle/_ref is present the reference's CPU sort is run on the same buffer as well;
+inputs have no NaN, and equal values are interchangeable."""
 import numpy as np
 import pytest
 import torch
 
 from libnd4j_b200 import shape as S
 from tests.cases import Layout
+from tests import utility_truth as U
 
 pytestmark = pytest.mark.gpu
 
@@ -21,23 +24,21 @@ def host(t):
     return t.cpu().numpy()
 
 
-def _values(rng, n, dt):
-    x = (rng.standard_normal(n) * 100).astype(dt)
-    if n > 8:
-        x[:4] = [np.inf, -np.inf, 0.0, x[5]]          # infinities (the padding value) and a duplicate
-    return x
+_values = U.sort_values
 
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("n", [1, 2, 3, 31, 256, 257, 2048, 2049, 8192, 8193, 20000, 65536, 100003])
 @pytest.mark.parametrize("descending", [False, True])
-def test_sort_whole_array(ops, dt, name, n, descending):
+def test_sort_whole_array(ops, maybe_ref, dt, name, n, descending):
     rng = np.random.default_rng(n)
     x = _values(rng, n, dt)
     dx = dev(x)
     getattr(ops, "sort" + name)(None, dx, S.shape_info([1, n]), descending)
     want = np.sort(x)[::-1] if descending else np.sort(x)
     np.testing.assert_array_equal(host(dx), want)
+    if maybe_ref is not None and dt != np.float16:          # sortHalf is empty in the reference's CPU build
+        np.testing.assert_array_equal(host(dx), maybe_ref.sort(x.copy(), S.shape_info([1, n]), descending))
 
 
 def test_sort_small_known_answer(ops):
@@ -50,7 +51,7 @@ def test_sort_small_known_answer(ops):
 
 
 @pytest.mark.parametrize("kind", ["c", "f", "cview2"])
-def test_sort_walks_linear_positions(ops, kind):
+def test_sort_walks_linear_positions(ops, maybe_ref, kind):
     # positions are i * ews, or c-order coordinates where there is no element-wise stride
     rng = np.random.default_rng(4)
     x = rng.standard_normal((37, 53)).astype(np.float32)
@@ -60,6 +61,8 @@ def test_sort_walks_linear_positions(ops, kind):
     got = lay.read(host(dx))
     flat = got.ravel(order="F" if kind == "f" else "C")
     np.testing.assert_array_equal(flat, np.sort(x.ravel()))
+    if maybe_ref is not None:
+        np.testing.assert_array_equal(got, lay.read(maybe_ref.sort(lay.buffer.copy(), lay.info, False)))
 
 
 @pytest.mark.parametrize("dt,name", NAMES)
@@ -67,7 +70,7 @@ def test_sort_walks_linear_positions(ops, kind):
                                        ((2, 20001), 1), ((3, 20000), 1), ((5, 6, 7), 2), ((5, 6, 7), 0)])
 @pytest.mark.parametrize("kind", ["c", "f"])
 @pytest.mark.parametrize("descending", [False, True])
-def test_sort_tad(ops, dt, name, shape, dim, kind, descending):
+def test_sort_tad(ops, maybe_ref, dt, name, shape, dim, kind, descending):
     rng = np.random.default_rng(sum(shape) + dim)
     x = (rng.standard_normal(shape) * 50).astype(dt)
     lay = Layout(x, kind)
@@ -77,6 +80,8 @@ def test_sort_tad(ops, dt, name, shape, dim, kind, descending):
     if descending:
         want = np.flip(want, axis=dim)
     np.testing.assert_array_equal(lay.read(host(dx)), want)
+    if maybe_ref is not None and dt != np.float16:          # sortTadHalf is empty in the reference's CPU build
+        np.testing.assert_array_equal(lay.read(host(dx)), lay.read(maybe_ref.sort_tad(lay.buffer.copy(), lay.info, [dim], descending)))
 
 
 def test_sort_large_is_sorted_and_a_permutation(ops):

@@ -1,13 +1,14 @@
-"""flatten / concat / pullRows / average / accumulate on the GPU. They move or add elements without
-any transcendental arithmetic, so the expected values are computed with numpy following the reference's
-loops (blas/cpu/NativeOps.cpp:1530-1700, 2045-2104; include/ops/impl/specials.cpp:250-433), and every
-result must be bit-exact."""
+"""flatten / concat / pullRows / tear / shuffle / average / accumulate / convertTypes on the GPU. They move or
+add elements without any transcendental arithmetic, so every result must be bit-exact. Expected values come
+from the reference's own CPU NativeOps members (oracle/_ref, when it was built) and from numpy restatements of
+the same loops (tests/utility_truth.py), which tests/test_oracle_utilities.py holds against the reference."""
 import numpy as np
 import pytest
 import torch
 
 from libnd4j_b200 import shape as S
 from tests.cases import Layout
+from tests import utility_truth as U
 
 pytestmark = pytest.mark.gpu
 
@@ -25,7 +26,7 @@ def host(t):
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("order", ["c", "f"])
 @pytest.mark.parametrize("kind", ["c", "f", "cview2"])
-def test_flatten_orders_and_offset(ops, dt, name, order, kind):
+def test_flatten_orders_and_offset(ops, maybe_ref, dt, name, order, kind):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((6, 5, 4)).astype(dt)
     lay = Layout(x, kind)
@@ -33,14 +34,15 @@ def test_flatten_orders_and_offset(ops, dt, name, order, kind):
     z = np.full(total, -1, dt)
     dz = dev(z)
     getattr(ops, "flatten" + name)(None, 9, order, dz, S.shape_info([1, total]), dev(lay.buffer), lay.info)
-    want = z.copy()
-    want[9:9 + x.size] = x.ravel(order="C" if order == "c" else "F")
-    np.testing.assert_array_equal(host(dz), want)
+    np.testing.assert_array_equal(host(dz), U.flatten_truth(z, 9, order, x))
+    if maybe_ref is not None and dt != np.float16:          # flattenHalf is empty in the reference's CPU build
+        want = maybe_ref.flatten(9, order, z.copy(), S.shape_info([1, total]), lay.buffer.copy(), lay.info)
+        np.testing.assert_array_equal(host(dz), want)
 
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("dim", [0, 1, 2])
-def test_concat_along_each_axis(ops, dt, name, dim):
+def test_concat_along_each_axis(ops, maybe_ref, dt, name, dim):
     rng = np.random.default_rng(dim)
     base = [3, 4, 5]
     parts = []
@@ -55,6 +57,10 @@ def test_concat_along_each_axis(ops, dt, name, dim):
     getattr(ops, "concat" + name)(None, dim, 3, [dev(l.buffer) for l in lays], [l.info for l in lays], dz,
                                   S.shape_info(list(want.shape)))
     np.testing.assert_array_equal(host(dz).reshape(want.shape), want)
+    if maybe_ref is not None:
+        zr = maybe_ref.concat(dim, [l.buffer for l in lays], [l.info for l in lays], np.zeros(want.size, dt),
+                              S.shape_info(list(want.shape)))
+        np.testing.assert_array_equal(host(dz), zr)
 
 
 def test_concat_large_rows_takes_the_dense_path(ops):
@@ -70,7 +76,7 @@ def test_concat_large_rows_takes_the_dense_path(ops):
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("kind,dim", [("c", 1), ("f", 1), ("c", 0)])
-def test_pull_rows(ops, dt, name, kind, dim):
+def test_pull_rows(ops, maybe_ref, dt, name, kind, dim):
     rng = np.random.default_rng(5)
     x = rng.standard_normal((50, 24)).astype(dt)
     lay = Layout(x, kind)
@@ -85,29 +91,53 @@ def test_pull_rows(ops, dt, name, kind, dim):
                                     tad_info, dev(tad_offsets.astype(np.int64)), ztad_info,
                                     dev(ztad_offsets.astype(np.int64)))
     np.testing.assert_array_equal(host(dz).reshape(zshape), rows)
+    if maybe_ref is not None and dt != np.float16:          # pullRowsHalf is empty in the reference's CPU build
+        zr = maybe_ref.pull_rows(lay.buffer.copy(), lay.info, np.zeros(rows.size, dt), zinfo, picks, tad_info,
+                                 tad_offsets, ztad_info, ztad_offsets)
+        np.testing.assert_array_equal(host(dz), zr)
+
+
+def test_pull_rows_pairs_by_coordinates_unless_both_sides_have_a_stride(ops, maybe_ref):
+    """Source TADs with an elementWiseStride (matrices of an f-order array, walked first axis fastest) against
+    target TADs without one (rows padded by one element): the reference then pairs the i-th c-order coordinate
+    of both (blas/cpu/NativeOps.cpp:2072-2101), so z[k, p, q] = x[p, q, pick[k]]."""
+    rng = np.random.default_rng(6)
+    a, b, n, k = 5, 7, 9, 4
+    x = rng.standard_normal((a, b, n)).astype(np.float32)
+    lay = Layout(x, "f")
+    _, tad_offsets = ops.tadOnlyShapeInfo(lay.info, [0, 1], 2)
+    tad_info = S.shape_info([a, b], "f", [1, a], ews=1)               # the source TAD has a stride
+    picks = rng.integers(0, n, k)
+    zinfo = S.shape_info([k, a, b], "c", [a * (b + 1), b + 1, 1])     # parent [k, a, b + 1]
+    ztad_info, ztad_offsets = ops.tadOnlyShapeInfo(zinfo, [1, 2], 2)
+    assert ztad_info[2 * 2 + 2] < 1                                   # the target TAD has none
+    zbuf = np.zeros(k * a * (b + 1), np.float32)
+    dz = dev(zbuf)
+    ops.pullRowsFloat(None, dev(lay.buffer), lay.info, dz, zinfo, k, dev(picks.astype(np.int64)), tad_info,
+                      dev(np.asarray(tad_offsets, dtype=np.int64)), ztad_info, dev(np.asarray(ztad_offsets, dtype=np.int64)))
+    got = host(dz).reshape(k, a, b + 1)[:, :, :b]
+    np.testing.assert_array_equal(got, np.moveaxis(x[:, :, picks], 2, 0))
+    if maybe_ref is not None:
+        zr = maybe_ref.pull_rows(lay.buffer.copy(), lay.info, zbuf.copy(), zinfo, picks, tad_info, tad_offsets, ztad_info,
+                                 ztad_offsets)
+        np.testing.assert_array_equal(host(dz), zr)
 
 
 @pytest.mark.parametrize("dt,name", NAMES)
-def test_average_and_accumulate(ops, dt, name):
+def test_average_and_accumulate(ops, maybe_ref, dt, name):
     rng = np.random.default_rng(11)
     n, length = 5, 10007
     xs = [rng.standard_normal(length).astype(dt) for _ in range(n)]
-
-    def seq(terms, start, divide):
-        acc = start.copy()
-        for t in terms:
-            v = (t / dt(n)).astype(dt) if divide else t
-            acc = (acc + v).astype(dt)
-        return acc
-
-    want_avg = seq(xs, np.zeros(length, dt), True)
+    want_avg = U.average_truth(xs, dt)
     dxs = [dev(x) for x in xs]
     dz = dev(np.full(length, 3, dt))
     getattr(ops, "average" + name)(None, dxs, dz, n, length, False)
     got = host(dz)
     # the reference's build may replace x / n by x * (1 / n): one ulp per term at most
-    tol = 0 if dt == np.float64 else None
     assert np.abs(got.astype(np.float64) - want_avg.astype(np.float64)).max() <= n * np.spacing(np.abs(want_avg).max())
+    if maybe_ref is not None and dt != np.float16:          # averageHalf is empty in the reference's CPU build
+        zr = maybe_ref.average([x.copy() for x in xs], np.zeros(length, dt), False)
+        assert np.abs(got.astype(np.float64) - zr.astype(np.float64)).max() <= n * np.spacing(np.abs(zr).max())
     for x, d in zip(xs, dxs):
         np.testing.assert_array_equal(host(d), x)             # sources untouched without propagate
     getattr(ops, "average" + name)(None, dxs, dz, n, length, True)
@@ -118,7 +148,9 @@ def test_average_and_accumulate(ops, dt, name):
     start = rng.standard_normal(length).astype(dt)
     dz = dev(start)
     getattr(ops, "accumulate" + name)(None, dxs, dz, n, length)
-    np.testing.assert_array_equal(host(dz), seq(xs, start, False))
+    np.testing.assert_array_equal(host(dz), U.accumulate_truth(xs, start, dt))
+    if maybe_ref is not None:
+        np.testing.assert_array_equal(host(dz), maybe_ref.accumulate([x.copy() for x in xs], start.copy()))
 
 
 def test_average_into_first_source_and_limits(ops):
@@ -179,7 +211,7 @@ def _tad_view(x, lay, ops, dims):
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("kind,dim,zorder", [("c", 1, "c"), ("f", 1, "c"), ("c", 0, "c"), ("cview2", 1, "c"), ("c", 1, "f")])
-def test_tear_rows_and_columns(ops, dt, name, kind, dim, zorder):
+def test_tear_rows_and_columns(ops, maybe_ref, dt, name, kind, dim, zorder):
     # TAD k of x lands in its own array (blas/cpu/NativeOps.cpp:2119-2162)
     rng = np.random.default_rng(21)
     x = rng.standard_normal((12, 40)).astype(dt)
@@ -192,9 +224,13 @@ def test_tear_rows_and_columns(ops, dt, name, kind, dim, zorder):
     getattr(ops, "tear" + name)(None, dev(lay.buffer), lay.info, targets, zinfo, tad_info, dev(tad_offsets))
     for t, p in zip(targets, pieces):
         np.testing.assert_array_equal(host(t), p)
+    if maybe_ref is not None:
+        rt = maybe_ref.tear(lay.buffer.copy(), lay.info, [np.zeros(p.size, dt) for p in pieces], zinfo, tad_info, tad_offsets)
+        for t, r in zip(targets, rt):
+            np.testing.assert_array_equal(host(t), r)
 
 
-def test_tear_matrices_in_f_order_enumeration(ops):
+def test_tear_matrices_in_f_order_enumeration(ops, maybe_ref):
     # neither side addressable by one stride: element j of a TAD in f-order goes to element j of the target in f-order
     rng = np.random.default_rng(22)
     x = rng.standard_normal((5, 6, 7)).astype(np.float32)
@@ -205,6 +241,10 @@ def test_tear_matrices_in_f_order_enumeration(ops):
     ops.tearFloat(None, dev(lay.buffer), lay.info, targets, zlay.info, tad_info, dev(tad_offsets))
     for k, t in enumerate(targets):
         np.testing.assert_array_equal(zlay.read(host(t)), x[k])
+    if maybe_ref is not None:
+        rt = maybe_ref.tear(lay.buffer.copy(), lay.info, [zlay.buffer.copy() for _ in range(5)], zlay.info, tad_info, tad_offsets)
+        for t, r in zip(targets, rt):
+            np.testing.assert_array_equal(zlay.read(host(t)), zlay.read(r))
 
 
 def test_tear_few_long_tads_are_cut_into_chunks(ops):
@@ -220,38 +260,13 @@ def test_tear_few_long_tads_are_cut_into_chunks(ops):
             np.testing.assert_array_equal(host(t), a[k])
 
 
-def _shuffled(x, axis, shuffle_map):
-    """The reference's loop: swaps applied one after another (blas/cpu/NativeOps.cpp:2289-2324)."""
-    out = np.moveaxis(x.copy(), axis, 0)
-    for r in range(out.shape[0]):
-        m = shuffle_map[r]
-        if m < 0:
-            continue
-        tmp = out[r].copy()
-        out[r] = out[m]
-        out[m] = tmp
-    return np.moveaxis(out, 0, axis)
-
-
-def _half_map(n, rng):
-    # the usual map: every TAD of the first half meets one of the second half, nothing else moves
-    m = np.full(n, -1, np.int32)
-    m[:n // 2] = n // 2 + rng.permutation(n // 2)
-    return m
-
-
-MAPS = {
-    "pairs": lambda n, rng: _half_map(n, rng),
-    "chain": lambda n, rng: np.array([r + 1 if r + 1 < n else -1 for r in range(n)], np.int32),
-    "random": lambda n, rng: rng.integers(-1, n, n).astype(np.int32),
-    "identity": lambda n, rng: np.arange(n, dtype=np.int32),
-}
+_shuffled, _half_map, MAPS = U.shuffled, U.half_map, U.MAPS
 
 
 @pytest.mark.parametrize("dt,name", NAMES)
 @pytest.mark.parametrize("which", sorted(MAPS))
 @pytest.mark.parametrize("kind,dim", [("c", 1), ("f", 1), ("c", 0)])
-def test_shuffle_features_and_labels_together(ops, dt, name, which, kind, dim):
+def test_shuffle_features_and_labels_together(ops, maybe_ref, dt, name, which, kind, dim):
     rng = np.random.default_rng(31)
     n = 21
     feats = rng.standard_normal((n, 36) if dim == 1 else (36, n)).astype(dt)
@@ -265,6 +280,11 @@ def test_shuffle_features_and_labels_together(ops, dt, name, which, kind, dim):
     axis = 0 if dim == 1 else 1
     for lay, buf, a in zip(lays, bufs, (feats, labels)):
         np.testing.assert_array_equal(lay.read(host(buf)), _shuffled(a, axis, shuffle_map))
+    if maybe_ref is not None and dt != np.float16:          # shuffleHalf is empty in the reference's CPU build
+        rb = maybe_ref.shuffle([l.buffer.copy() for l in lays], [l.info for l in lays], shuffle_map, [t[0] for t in tads],
+                               [t[1] for t in tads])
+        for lay, buf, r in zip(lays, bufs, rb):
+            np.testing.assert_array_equal(lay.read(host(buf)), lay.read(r))
 
 
 def test_shuffle_long_rows_and_bad_map(ops):
