@@ -129,16 +129,26 @@ public:
                         Nd4jLong resultStride, float scalar, float16 *extraParams, Nd4jLong n);
     void execScalarHalf(Nd4jPointer *extraPointers, int opNum, float16 *x, Nd4jLong *xShapeInfo, float16 *result,
                         Nd4jLong *resultShapeInfo, float scalar, float16 *extraParams);
-    /* nd4jb200_exec_scalar_indexed (NativeOps.h:1132-1141 and the Double / Half twins) */
+    /* nd4jb200_exec_scalar_indexed (NativeOps.h:420-430, 1132-1141): the Double member carries an element count,
+     * the Float member does not, and the reference declares none for Half */
     void execScalarDouble(Nd4jPointer *extraPointers, int opNum, double *x, Nd4jLong *xShapeInfo, double *result,
-                          Nd4jLong *resultShapeInfo, double scalar, double *extraParams, Nd4jLong *xIndexes,
-                          Nd4jLong *resultIndexes);
+                          Nd4jLong *resultShapeInfo, double scalar, double *extraParams, Nd4jLong n,
+                          Nd4jLong *xIndexes, Nd4jLong *resultIndexes);
     void execScalarFloat(Nd4jPointer *extraPointers, int opNum, float *x, Nd4jLong *xShapeInfo, float *result,
                          Nd4jLong *resultShapeInfo, float scalar, float *extraParams, Nd4jLong *xIndexes,
                          Nd4jLong *resultIndexes);
-    void execScalarHalf(Nd4jPointer *extraPointers, int opNum, float16 *x, Nd4jLong *xShapeInfo, float16 *result,
-                        Nd4jLong *resultShapeInfo, float scalar, float16 *extraParams, Nd4jLong *xIndexes,
-                        Nd4jLong *resultIndexes);
+    /* the indexed transform members (NativeOps.h:327-360, 1400-1443) do nothing in the reference, in its CUDA build
+     * (blas/cuda/NativeOps.cu:3598-3624) as in its CPU build (the call is commented out,
+     * blas/cpu/NativeOpExcutioner.cpp:345-346); they are exported with the same empty behaviour */
+    void execTransformDouble(Nd4jPointer *extraPointers, int opNum, double *dx, Nd4jLong *xShapeInfo, double *result,
+                             Nd4jLong *resultShapeInfo, double *extraParams, Nd4jLong *xIndexes,
+                             Nd4jLong *resultIndexes);
+    void execTransformFloat(Nd4jPointer *extraPointers, int opNum, float *dx, Nd4jLong *xShapeInfo, float *result,
+                            Nd4jLong *resultShapeInfo, float *extraParams, Nd4jLong *xIndexes,
+                            Nd4jLong *resultIndexes);
+    void execTransformHalf(Nd4jPointer *extraPointers, int opNum, float16 *dx, Nd4jLong *xShapeInfo, float16 *result,
+                           Nd4jLong *resultShapeInfo, float16 *extraParams, Nd4jLong *xIndexes,
+                           Nd4jLong *resultIndexes);
 
     /* nd4jb200_init_random and friends (NativeOps.h:2510-2539). extraPointers[0] = host table,
      * [1] = stream, ptrToBuffer = device table (blas/cuda/NativeOps.cu:5384-5391). */
@@ -179,6 +189,13 @@ public:
     int memsetAsync(Nd4jPointer dst, int value, Nd4jLong size, int flags, Nd4jPointer reserved);
     /* nd4jb200_convert_types (NativeOps.h:2144) */
     void convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z);
+    /* nd4jb200_memcpy_constant_async / nd4jb200_get_constant_space (NativeOps.h:1836-1846) */
+    int memcpyConstantAsync(Nd4jLong dst, Nd4jPointer src, Nd4jLong size, int flags, Nd4jPointer reserved);
+    Nd4jPointer getConstantSpace();
+    /* nd4jb200_enable_p2p / nd4jb200_check_p2p / nd4jb200_is_p2p_available (NativeOps.h:2047-2058) */
+    void enableP2P(bool enable);
+    void checkP2P();
+    bool isP2PAvailable();
     int getAvailableDevices();
     void enableDebugMode(bool reallyEnable);
     void enableVerboseMode(bool reallyEnable);

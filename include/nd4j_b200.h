@@ -190,6 +190,15 @@ void *nd4jb200_rng_device_table(Nd4jPointer state);
 int nd4jb200_tad_only_shape_info(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength,
                                  Nd4jLong *target, Nd4jLong *offsets);
 Nd4jLong nd4jb200_tad_count(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength);
+/* The dimension list that yields the given TADs of x, recovered on the host from the two descriptors (both host
+ * pointers): the reference's CUDA callers keep a host copy of the TAD shapeInfo in extraPointers[9]
+ * (blas/cuda/NativeOps.cu:2111) while `dimension` itself lives on the device. Returns the number of axes written
+ * to `dimension` (room for 32), 0 when the TAD is the whole array, -1 when the descriptors do not determine it. */
+/* Diagnostics: how many blocking device-to-host reads of shapeInfo / dimension arrays the NativeOps members
+ * (include/NativeOps.h) have made since load because a call came without the host copies the reference's CUDA
+ * callers provide in extraPointers[0], [7], [8] and [9]. A caller that fills those slots keeps this at zero. */
+unsigned long long nd4jb200_metadata_reads(void);
+int nd4jb200_dims_from_tad(const Nd4jLong *xShapeInfo, const Nd4jLong *tadShapeInfo, int *dimension);
 
 /* ---- memory-movement utilities on the same boundary (blas/NativeOps.h:1457-1601, 1904-2037). Pointer
  *      arrays (`sources`, `data`, `inputShapeInfo`) are HOST arrays; what they point to follows the usual
@@ -267,6 +276,20 @@ Nd4jLong nd4jb200_device_total_memory(int device);
 int nd4jb200_device_major(int device);
 int nd4jb200_device_minor(int device);
 const char *nd4jb200_device_name(int device);
+
+/* ---- peer access and the constant-memory staging area (blas/NativeOps.h:1836-1846, 2047-2058;
+ *      blas/cuda/NativeOps.cu:87, 3854-3938, 4793-4834) -------------------------------------------------------
+ * check_p2p probes every ordered device pair and records whether all of them can reach each other (one device
+ * counts as supported); enable_p2p turns peer access on or off for every pair that supports it. The exec*
+ * kernels never read another GPU's memory; these exist for callers that copy between devices themselves.
+ * The constant space is a 49152-byte __constant__ array, as in the reference: memcpy_constant_async copies
+ * `bytes` to byte offset `offset` of it (flags 1 host->device, 3 device->device) and get_constant_space returns
+ * its device address, so that descriptors staged there can be passed as device pointers. */
+int nd4jb200_check_p2p(void);
+int nd4jb200_is_p2p_available(void);
+int nd4jb200_enable_p2p(int enable);
+int nd4jb200_memcpy_constant_async(Nd4jLong offset, const void *src, Nd4jLong bytes, int flags, void *stream);
+void *nd4jb200_get_constant_space(void);
 
 #ifdef __cplusplus
 }

@@ -806,6 +806,12 @@ int nd4jb200_tad_only_shape_info(const Nd4jLong *xShapeInfo, const int *dimensio
     return tad_only_shape_info(xShapeInfo, dimension, dimensionLength, target, offsets, nullptr);
 }
 
+int nd4jb200_dims_from_tad(const Nd4jLong *xShapeInfo, const Nd4jLong *tadShapeInfo, int *dimension) {
+    ShapeDesc x, t;
+    if (parse_shape(xShapeInfo, "xShapeInfo", &x) != kOk || parse_shape(tadShapeInfo, "tadShapeInfo", &t) != kOk) return -1;
+    return dims_from_tad_info(x, t, dimension);
+}
+
 Nd4jLong nd4jb200_tad_count(const Nd4jLong *xShapeInfo, const int *dimension, int dimensionLength) {
     LL n = -1;
     if (tad_only_shape_info(xShapeInfo, dimension, dimensionLength, nullptr, nullptr, &n) != kOk) return -1;

@@ -10,8 +10,13 @@
 #include <string>
 #include <vector>
 
+#include <atomic>
+
 namespace {
 
+// Blocking device-to-host reads of call metadata (shapeInfo, dimension lists) made because a caller left the
+// host copies out of extraPointers; read through nd4jb200_metadata_reads().
+std::atomic<unsigned long long> g_metadataReads{0};
 
 [[noreturn]] void fail(const char *where) {
     throw std::runtime_error(std::string(where) + ": " + nd4jb200_last_error());
@@ -21,6 +26,15 @@ inline void check(int status, const char *where) { if (status != 0) fail(where);
 inline void *stream_of(Nd4jPointer *extra) { return extra ? extra[1] : nullptr; }
 
 bool is_device_pointer(const void *p) {
+    // descriptors staged in the constant space (memcpyConstantAsync) are device memory whatever the driver
+    // reports for addresses of __constant__ symbols
+    thread_local const char *constBase[16] = {nullptr};
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 16) {
+        if (!constBase[device]) constBase[device] = static_cast<const char *>(nd4jb200_get_constant_space());
+        const char *c = static_cast<const char *>(p);
+        if (constBase[device] && c >= constBase[device] && c < constBase[device] + 49152) return true;
+    }
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return false; }
     return attr.type == cudaMemoryTypeDevice;
@@ -39,6 +53,7 @@ const Nd4jLong *host_info(Nd4jPointer *extra, int slot, const Nd4jLong *arg) {
     thread_local int next = 0;
     std::vector<Nd4jLong> &v = ring[next];
     next = (next + 1) % kKeep;
+    g_metadataReads.fetch_add(1, std::memory_order_relaxed);
     Nd4jLong rank = 0;
     if (cudaMemcpy(&rank, arg, sizeof(Nd4jLong), cudaMemcpyDeviceToHost) != cudaSuccess || rank < 0 || rank > 32)
         throw std::runtime_error("could not read shapeInfo from the device");
@@ -48,16 +63,36 @@ const Nd4jLong *host_info(Nd4jPointer *extra, int slot, const Nd4jLong *arg) {
     return v.data();
 }
 
-// The dimension list lives on the device in the reference's CUDA build; TAD geometry is decoded on the host, so
-// it is read back on every call (dimension buffers are routinely reused with other contents).
-const int *host_dims(const int *dimension, int n) {
-    if (dimension == nullptr || n <= 0) return nullptr;
-    if (!is_device_pointer(dimension)) return dimension;
+// The dimension list lives on the device in the reference's CUDA build, while TAD geometry is decoded on the
+// host here. Callers of that build keep host copies of x's shapeInfo and of its TAD shapeInfo in
+// extraPointers[0] and [9] (blas/cuda/NativeOps.cu:2107-2118); the list is recovered from those two without
+// touching the device. Only when a slot is missing, or the descriptors do not determine the list, is the
+// device array read back (a blocking copy; dimension buffers are routinely reused with other contents, so the
+// download is never cached).
+struct HostDims {
+    const int *p;
+    int n;
+};
+HostDims host_dims(Nd4jPointer *extra, const int *dimension, int n) {
+    if (dimension == nullptr || n <= 0) return HostDims{nullptr, 0};
+    thread_local int recovered[32];
+    if (extra && extra[0] && extra[9]) {
+        const Nd4jLong *xInfo = static_cast<const Nd4jLong *>(extra[0]);
+        const int got = nd4jb200_dims_from_tad(xInfo, static_cast<const Nd4jLong *>(extra[9]), recovered);
+        if (got > 0) return HostDims{recovered, got};
+        if (got == 0) {                       // the TAD is the whole array: every axis is listed
+            const int rank = (int) xInfo[0];
+            for (int i = 0; i < rank; i++) recovered[i] = i;
+            return HostDims{recovered, rank};
+        }
+    }
+    if (!is_device_pointer(dimension)) return HostDims{dimension, n};
+    g_metadataReads.fetch_add(1, std::memory_order_relaxed);
     thread_local std::vector<int> v;
     v.resize(n);
     if (cudaMemcpy(v.data(), dimension, sizeof(int) * n, cudaMemcpyDeviceToHost) != cudaSuccess)
         throw std::runtime_error("could not read the dimension array from the device");
-    return v.data();
+    return HostDims{v.data(), n};
 }
 
 // A host copy the caller owns: calls that take many descriptors (concat, shuffle) would outrun the ring.
@@ -75,10 +110,15 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
 
 }  // namespace
 
+extern "C" __attribute__((visibility("default"))) unsigned long long nd4jb200_metadata_reads(void) {
+    return g_metadataReads.load(std::memory_order_relaxed);
+}
+
 #define X_INFO host_info(extraPointers, 0, xShapeInfo)
 #define Y_INFO host_info(extraPointers, 7, yShapeInfo)
 #define Z_INFO(arg) host_info(extraPointers, 8, arg)
 #define STREAM stream_of(extraPointers)
+#define DIMS host_dims(extraPointers, dimension, dimensionLength)
 
 #define ND4JB200_DEFINE_FAMILIES(T, S, R)                                                                              \
     R NativeOps::execIndexReduceScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,          \
@@ -91,16 +131,18 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     void NativeOps::execIndexReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,             \
                                        T *extraParams, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,    \
                                        int dimensionLength) {                                                         \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_index_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,               \
-                                         Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),        \
-                                         dimensionLength), "execIndexReduce" #S);                                      \
+                                         Z_INFO(resultShapeInfoBuffer), dims.p,        \
+                                         dims.n), "execIndexReduce" #S);                                      \
     }                                                                                                                  \
     void NativeOps::execBroadcast##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *y,         \
                                      Nd4jLong *yShapeInfo, T *result, Nd4jLong *resultShapeInfo, int *dimension,      \
                                      int dimensionLength) {                                                           \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_broadcast(STREAM, TypeCode<T>::v, opNum, x, X_INFO, y, Y_INFO, result,                    \
-                                      Z_INFO(resultShapeInfo), host_dims(dimension, dimensionLength),                 \
-                                      dimensionLength), "execBroadcast" #S);                                           \
+                                      Z_INFO(resultShapeInfo), dims.p,                 \
+                                      dims.n), "execBroadcast" #S);                                           \
     }                                                                                                                  \
     void NativeOps::execPairwiseTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong xStride, T *y,    \
                                              Nd4jLong yStride, T *result, Nd4jLong resultStride, T *extraParams,      \
@@ -127,8 +169,9 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     }                                                                                                                  \
     void NativeOps::execReduce##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *extraParams,  \
                                   T *result, Nd4jLong *resultShapeInfo, int *dimension, int dimensionLength) {        \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_reduce(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,                     \
-                                   Z_INFO(resultShapeInfo), host_dims(dimension, dimensionLength), dimensionLength),  \
+                                   Z_INFO(resultShapeInfo), dims.p, dims.n),  \
               "execReduce" #S);                                                                                        \
     }                                                                                                                  \
     R NativeOps::execReduceScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,               \
@@ -154,17 +197,19 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     void NativeOps::execReduce3##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,                 \
                                    T *extraParamsVals, T *y, Nd4jLong *yShapeInfo, T *result,                         \
                                    Nd4jLong *resultShapeInfoBuffer, int *dimension, int dimensionLength) {            \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_reduce3(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO, result,     \
-                                    Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),             \
-                                    dimensionLength), "execReduce3" #S);                                               \
+                                    Z_INFO(resultShapeInfoBuffer), dims.p,             \
+                                    dims.n), "execReduce3" #S);                                               \
     }                                                                                                                  \
     void NativeOps::execReduce3All##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,              \
                                       T *extraParamsVals, T *y, Nd4jLong *yShapeInfo, T *result,                      \
                                       Nd4jLong *resultShapeInfoBuffer, int *dimension, int dimensionLength,           \
                                       Nd4jLong *, Nd4jLong *, Nd4jLong *, Nd4jLong *) {                               \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_reduce3_all(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParamsVals, y, Y_INFO,         \
-                                        result, Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength), \
-                                        dimensionLength), "execReduce3All" #S);                                        \
+                                        result, Z_INFO(resultShapeInfoBuffer), dims.p, \
+                                        dims.n), "execReduce3All" #S);                                        \
     }                                                                                                                  \
     void NativeOps::flatten##S(Nd4jPointer *extraPointers, int offset, char order, T *result,                         \
                                Nd4jLong *resultShapeInfo, T *input, Nd4jLong *inputShapeInfo) {                       \
@@ -216,8 +261,9 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     }                                                                                                                  \
     void NativeOps::sortTad##S(Nd4jPointer *extraPointers, T *x, Nd4jLong *xShapeInfo, int *dimension,                \
                                int dimensionLength, Nd4jLong *, Nd4jLong *, bool descending) {                        \
-        check(nd4jb200_sort_tad(STREAM, TypeCode<T>::v, x, X_INFO, host_dims(dimension, dimensionLength),             \
-                                dimensionLength, descending ? 1 : 0), "sortTad" #S);                                   \
+        const HostDims dims = DIMS;                                                                                    \
+        check(nd4jb200_sort_tad(STREAM, TypeCode<T>::v, x, X_INFO, dims.p,             \
+                                dims.n, descending ? 1 : 0), "sortTad" #S);                                   \
     }                                                                                                                  \
     void NativeOps::average##S(Nd4jPointer *extras, Nd4jPointer *dx, T *dz, int n, Nd4jLong length,                   \
                                bool propagate) {                                                                      \
@@ -230,9 +276,10 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *z,            \
                                   Nd4jLong *zShapeInfo, T *scalars, T *extraParams, int *dimension,                   \
                                   int dimensionLength) {                                                              \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_scalar_along_dimension(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, z,          \
                                                    Z_INFO(zShapeInfo), scalars,                                       \
-                                                   host_dims(dimension, dimensionLength), dimensionLength),           \
+                                                   dims.p, dims.n),           \
               "execScalar" #S);                                                                                        \
     }                                                                                                                  \
     R NativeOps::execSummaryStatsScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,         \
@@ -251,9 +298,10 @@ template <> struct TypeCode<float16> { static constexpr int v = ND4JB200_HALF; }
     void NativeOps::execSummaryStats##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo,            \
                                         T *extraParams, T *result, Nd4jLong *resultShapeInfoBuffer, int *dimension,   \
                                         int dimensionLength, bool biasCorrected) {                                    \
+        const HostDims dims = DIMS;                                                                                    \
         check(nd4jb200_exec_summary_stats(STREAM, TypeCode<T>::v, opNum, x, X_INFO, extraParams, result,              \
-                                          Z_INFO(resultShapeInfoBuffer), host_dims(dimension, dimensionLength),       \
-                                          dimensionLength, biasCorrected ? 1 : 0), "execSummaryStats" #S);             \
+                                          Z_INFO(resultShapeInfoBuffer), dims.p,       \
+                                          dims.n, biasCorrected ? 1 : 0), "execSummaryStats" #S);             \
     }                                                                                                                  \
     void NativeOps::execTransform##S(Nd4jPointer *extraPointers, int opNum, T *dx, Nd4jLong xStride, T *result,       \
                                      Nd4jLong resultStride, T *extraParams, Nd4jLong n) {                             \
@@ -297,16 +345,29 @@ ND4JB200_DEFINE_FAMILIES(float16, Half, float)
                                   Nd4jLong *resultShapeInfo, ST scalar, T *extraParams) {                             \
         check(nd4jb200_exec_scalar(STREAM, TypeCode<T>::v, opNum, x, X_INFO, result, Z_INFO(resultShapeInfo),         \
                                    (double) scalar, extraParams), "execScalar" #S);                                    \
-    }                                                                                                                  \
-    void NativeOps::execScalar##S(Nd4jPointer *extraPointers, int opNum, T *x, Nd4jLong *xShapeInfo, T *result,       \
-                                  Nd4jLong *, ST scalar, T *extraParams, Nd4jLong *xIndexes,                          \
-                                  Nd4jLong *resultIndexes) {                                                          \
-        check(nd4jb200_exec_scalar_indexed(STREAM, TypeCode<T>::v, opNum, x, X_INFO, result, (double) scalar,         \
-                                           extraParams, xIndexes, resultIndexes), "execScalar" #S);                    \
     }
 ND4JB200_DEFINE_SCALAR(double, Double, double)
 ND4JB200_DEFINE_SCALAR(float, Float, float)
 ND4JB200_DEFINE_SCALAR(float16, Half, float)
+
+void NativeOps::execScalarFloat(Nd4jPointer *extraPointers, int opNum, float *x, Nd4jLong *xShapeInfo, float *result,
+                                Nd4jLong *, float scalar, float *extraParams, Nd4jLong *xIndexes, Nd4jLong *resultIndexes) {
+    check(nd4jb200_exec_scalar_indexed(STREAM, ND4JB200_FLOAT, opNum, x, X_INFO, result, (double) scalar, extraParams,
+                                       xIndexes, resultIndexes), "execScalarFloat");
+}
+void NativeOps::execScalarDouble(Nd4jPointer *extraPointers, int opNum, double *x, Nd4jLong *xShapeInfo, double *result,
+                                 Nd4jLong *, double scalar, double *extraParams, Nd4jLong, Nd4jLong *xIndexes,
+                                 Nd4jLong *resultIndexes) {
+    // the element count is that of xShapeInfo, as for the Float member
+    check(nd4jb200_exec_scalar_indexed(STREAM, ND4JB200_DOUBLE, opNum, x, X_INFO, result, scalar, extraParams, xIndexes,
+                                       resultIndexes), "execScalarDouble");
+}
+void NativeOps::execTransformDouble(Nd4jPointer *, int, double *, Nd4jLong *, double *, Nd4jLong *, double *, Nd4jLong *,
+                                    Nd4jLong *) {}
+void NativeOps::execTransformFloat(Nd4jPointer *, int, float *, Nd4jLong *, float *, Nd4jLong *, float *, Nd4jLong *,
+                                   Nd4jLong *) {}
+void NativeOps::execTransformHalf(Nd4jPointer *, int, float16 *, Nd4jLong *, float16 *, Nd4jLong *, float16 *, Nd4jLong *,
+                                  Nd4jLong *) {}
 
 void NativeOps::convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z) {
     check(nd4jb200_convert_types(stream_of(extras), srcType, x, N, dstType, z), "convertTypes");
@@ -375,6 +436,17 @@ int NativeOps::memset(Nd4jPointer dst, int value, Nd4jLong size, int, Nd4jPointe
 int NativeOps::memsetAsync(Nd4jPointer dst, int value, Nd4jLong size, int, Nd4jPointer reserved) {
     check(nd4jb200_memset_async(dst, value, size, reserved), "memsetAsync"); return 1;
 }
+int NativeOps::memcpyConstantAsync(Nd4jLong dst, Nd4jPointer src, Nd4jLong size, int flags, Nd4jPointer reserved) {
+    check(nd4jb200_memcpy_constant_async(dst, src, size, flags, reserved), "memcpyConstantAsync"); return 1;
+}
+Nd4jPointer NativeOps::getConstantSpace() {
+    Nd4jPointer p = nd4jb200_get_constant_space();
+    if (!p) fail("getConstantSpace");
+    return p;
+}
+void NativeOps::enableP2P(bool enable) { check(nd4jb200_enable_p2p(enable ? 1 : 0), "enableP2P"); }
+void NativeOps::checkP2P() { check(nd4jb200_check_p2p(), "checkP2P"); }
+bool NativeOps::isP2PAvailable() { return nd4jb200_is_p2p_available() != 0; }
 int NativeOps::getAvailableDevices() { return nd4jb200_get_available_devices(); }
 // The reference's tuning knobs for its own launch heuristics and OpenMP loops have no effect on
 // these kernels; they are accepted so that callers need no change.

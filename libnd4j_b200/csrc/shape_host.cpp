@@ -149,6 +149,32 @@ Status make_tad_plan(const ShapeDesc &x, const int *dimension, int dimensionLeng
     return collapse_view(no, os_, ot, &out->outer);
 }
 
+int dims_from_tad_info(const ShapeDesc &x, const ShapeDesc &tad, int *dims) {
+    if (tad.length == x.length) return 0;                 // one TAD: the whole array
+    if (tad.length <= 0 || x.length % tad.length != 0) return -1;
+    bool used[kMaxRank] = {false};
+    int n = 0;
+    if (tad.length == 1) {
+        for (int i = 0; i < x.rank; i++) if (x.shape[i] == 1) dims[n++] = i;
+        return n > 0 ? n : -1;
+    }
+    int from = 0;
+    for (int t = 0; t < tad.rank; t++) {
+        if (tad.shape[t] == 1) continue;
+        int hit = -1;
+        // TAD axes keep the array's axis order, so look behind the previous match first
+        for (int pass = 0; pass < 2 && hit < 0; pass++)
+            for (int i = pass == 0 ? from : 0; i < (pass == 0 ? x.rank : from); i++)
+                if (!used[i] && x.shape[i] == tad.shape[t] && x.stride[i] == tad.stride[t]) { hit = i; break; }
+        if (hit < 0) return -1;
+        used[hit] = true;
+        from = hit + 1;
+    }
+    LL len = 1;
+    for (int i = 0; i < x.rank; i++) if (used[i]) { dims[n++] = i; len *= x.shape[i]; }
+    return len == tad.length ? n : -1;
+}
+
 static void write_info(LL *target, int rank, const LL *shape, const LL *stride, LL offset, LL ews, char order) {
     target[0] = rank;
     for (int i = 0; i < rank; i++) { target[1 + i] = shape[i]; target[1 + rank + i] = stride[i]; }

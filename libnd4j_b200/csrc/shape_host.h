@@ -57,6 +57,14 @@ Status make_tad_plan(const ShapeDesc &x, const int *dimension, int dimensionLeng
 Status tad_only_shape_info(const LL *xShapeInfo, const int *dimension, int dimensionLength,
                            LL *target, LL *offsets, LL *numTadsOut);
 
+// Recovers a dimension list from the array's shapeInfo and the shapeInfo of its TADs (what callers of the
+// reference's CUDA build keep on the host next to the device copies): every non-unit TAD axis is matched to
+// the array axis with the same extent and stride, in ascending order. Unit axes do not change any offset and
+// are left out, except when the TAD is a single element (then the array's unit axes are the list). Returns the
+// number of dimensions written to `dims` (room for kMaxRank), 0 when the TAD is the whole array, and -1 when
+// the descriptors do not determine the list (the caller then has to obtain it another way).
+int dims_from_tad_info(const ShapeDesc &x, const ShapeDesc &tad, int *dims);
+
 // 'c'/'f'/'a' classification of a (shape, stride) pair, as written into permuted and sliced
 // shapeInfos by the reference (include/helpers/shape.h:2195-2236).
 char stride_order(int rank, const LL *shape, const LL *stride);

@@ -117,6 +117,13 @@ def load_library(path=None):
         "nd4jb200_rng_device_table": (vp, [vp]),
         "nd4jb200_tad_only_shape_info": (i, [llp, ip, i, llp, llp]),
         "nd4jb200_tad_count": (ll, [llp, ip, i]),
+        "nd4jb200_dims_from_tad": (i, [llp, llp, ip]),
+        "nd4jb200_metadata_reads": (ctypes.c_ulonglong, []),
+        "nd4jb200_check_p2p": (i, []),
+        "nd4jb200_is_p2p_available": (i, []),
+        "nd4jb200_enable_p2p": (i, [i]),
+        "nd4jb200_memcpy_constant_async": (i, [ll, vp, ll, i, vp]),
+        "nd4jb200_get_constant_space": (vp, []),
         "nd4jb200_get_available_devices": (i, []),
         "nd4jb200_set_device": (i, [i]),
         "nd4jb200_get_device": (i, []),
@@ -407,6 +414,15 @@ class NativeOps:
         r = int(tgt[0])
         return tgt[:2 * r + 4].copy(), off[:int(n)].copy()
 
+    def dimsFromTad(self, xShapeInfo, tadShapeInfo):
+        """The dimension list that yields the given TADs of x, recovered from the two host descriptors, or None
+        when they do not determine it (nd4jb200_dims_from_tad). An empty list means the whole array."""
+        xs, xsp = _longs(xShapeInfo)
+        ts, tsp = _longs(tadShapeInfo)
+        out = np.zeros(32, dtype=np.int32)
+        n = self.lib.nd4jb200_dims_from_tad(xsp, tsp, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+        return None if n < 0 else [int(v) for v in out[:n]]
+
     # ---- device / memory / stream utilities (blas/NativeOps.h:1607-1870) ---------------------
     def getAvailableDevices(self):
         return self.lib.nd4jb200_get_available_devices()
@@ -543,6 +559,25 @@ class NativeOps:
 
     def memsetAsync(self, dst, value, size, flags=0, reserved=None):
         self._check(self.lib.nd4jb200_memset_async(_ptr(dst), value, size, _ptr(reserved)))
+
+    def memcpyConstantAsync(self, dst, src, size, flags, reserved=None):
+        self._check(self.lib.nd4jb200_memcpy_constant_async(int(dst), _ptr(src), int(size), int(flags), _ptr(reserved)))
+        return 1
+
+    def getConstantSpace(self):
+        p = self.lib.nd4jb200_get_constant_space()
+        if not p:
+            raise Nd4jError(4, self.lastError())
+        return p
+
+    def enableP2P(self, enable):
+        self._check(self.lib.nd4jb200_enable_p2p(1 if enable else 0))
+
+    def checkP2P(self):
+        self._check(self.lib.nd4jb200_check_p2p())
+
+    def isP2PAvailable(self):
+        return bool(self.lib.nd4jb200_is_p2p_available())
 
     def getDeviceFreeMemory(self, device=0):
         return self.lib.nd4jb200_device_free_memory(int(device))

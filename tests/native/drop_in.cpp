@@ -47,9 +47,14 @@ int main() {
     float *dsum = static_cast<float *>(ops.mallocDevice(rows * 4, nullptr, 0));
     float *dimax = static_cast<float *>(ops.mallocDevice(rows * 4, nullptr, 0));
 
-    // extraPointers as the CUDA build expects them: [0] host xShapeInfo, [1] stream, [7]/[8] host y / z shapeInfo
+    // extraPointers as the CUDA build expects them: [0] host xShapeInfo, [1] stream, [7]/[8] host y / z shapeInfo,
+    // [9] host TAD shapeInfo (with [10]/[11] its device copy and the device TAD offsets, which this backend does
+    // not need). With these slots filled no call below may read metadata back from the device.
+    std::vector<Nd4jLong> tadInfo(8), tadOffsets(rows);
+    ops.tadOnlyShapeInfo(xi.data(), dim.data(), 1, tadInfo.data(), tadOffsets.data());
     Nd4jPointer extras[16] = {nullptr};
-    extras[0] = xi.data(); extras[1] = stream; extras[7] = bi.data(); extras[8] = xi.data();
+    extras[0] = xi.data(); extras[1] = stream; extras[7] = bi.data(); extras[8] = xi.data(); extras[9] = tadInfo.data();
+    const unsigned long long readsBefore = nd4jb200_metadata_reads();
     ops.execBroadcastFloat(extras, 0, dx, dxi, db, dbi, t1, dxi, ddim, 1);                    // x + b along dimension 1
     extras[7] = nullptr;
     ops.execTransformFloat(extras, 15, t1, dxi, t2, dxi, nullptr);                             // tanh
@@ -59,6 +64,7 @@ int main() {
     ops.execReduceFloat(extras, 1, t3, dxi, nullptr, dsum, dzi, ddim, 1);                       // row sums
     ops.execIndexReduceFloat(extras, 0, t3, dxi, nullptr, dimax, dzi, ddim, 1);                 // row argmax
     const float total = ops.execReduceScalarFloat(extras, 1, t3, dxi, nullptr);                 // whole-array sum
+    expect(nd4jb200_metadata_reads() == readsBefore, "no device reads of metadata when the host slots are filled");
 
     std::vector<float> g3 = to_host(t3, rows * cols), gsum = to_host(dsum, rows), gimax = to_host(dimax, rows);
     double all = 0;
@@ -89,6 +95,7 @@ int main() {
         Nd4jPointer bare[16] = {nullptr};
         bare[1] = stream;
         ops.execReduceFloat(bare, 1, t3, dxi, nullptr, dcol, dzi, ddim, 1);
+        expect(nd4jb200_metadata_reads() > readsBefore, "without host slots the descriptors are read from the device");
         std::vector<float> gcol = to_host(dcol, cols);
         for (Nd4jLong c = 0; c < cols; c++) {
             double s = 0, mag = 0;
@@ -100,6 +107,22 @@ int main() {
         ops.memcpyAsync(ddim, dim.data(), 4, 1, stream);
         ops.memcpyAsync(dzi, zi.data(), (Nd4jLong) (zi.size() * sizeof(Nd4jLong)), 1, stream);
         ops.streamSynchronize(stream);
+    }
+
+    // the constant-memory staging area: a descriptor placed there is a valid device shapeInfo argument
+    {
+        char *space = static_cast<char *>(ops.getConstantSpace());
+        expect(space != nullptr, "constant space address");
+        ops.memcpyConstantAsync(256, xi.data(), (Nd4jLong) (xi.size() * sizeof(Nd4jLong)), 1, stream);
+        Nd4jPointer bare[16] = {nullptr};
+        bare[1] = stream;
+        ops.execTransformFloat(bare, 0, t3, reinterpret_cast<Nd4jLong *>(space + 256), t2, reinterpret_cast<Nd4jLong *>(space + 256), nullptr);   // abs
+        std::vector<float> ga = to_host(t2, rows * cols);
+        for (Nd4jLong i = 0; i < rows * cols; i++) expect(ga[i] == std::fabs(g3[i]), "transform with shapeInfo in constant space");
+        ops.checkP2P();
+        expect(ops.getAvailableDevices() > 1 || ops.isP2PAvailable(), "one device counts as peer-capable");
+        ops.enableP2P(true);
+        ops.enableP2P(false);
     }
 
     // random: two identical states give identical draws, and the state advances

@@ -79,6 +79,74 @@ def test_mangled_nativeops_members_are_exported(lib):
     assert len(members) >= 100
 
 
+REFERENCE = os.environ.get("ND4J_REFERENCE", "/root/reference")
+REF_INCLUDES = ["blas", "include", "include/helpers", "include/loops", "include/graph", "include/ops", "include/types",
+                "include/array", "include/cnpy", "include/memory", "include/indexing"]
+
+
+def reference_member_declarations(ref_root):
+    """(return type, name, [parameter types]) of every member function the reference's class declares
+    (blas/NativeOps.h), read from the header text."""
+    text = open(os.path.join(ref_root, "blas", "NativeOps.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"//[^\n]*", "", text)
+    body = text[text.index("class ND4J_EXPORT NativeOps"):]
+    body = body[body.index("{") + 1:]
+    decls = []
+    for stmt in body.split(";"):
+        m = re.match(r"^\s*(?:public:\s*)?([\w\s\*:]+?)\s*\b(\w+)\s*\((.*)\)\s*$", stmt, flags=re.S)
+        if not m:
+            continue
+        types = []
+        for prm in [q.strip() for q in m.group(3).split(",") if q.strip()]:
+            prm = prm.split("=")[0].strip()
+            named = re.match(r"^(.*?[\s\*&])(\w+)$", prm, flags=re.S)
+            types.append(named.group(1).strip() if named else prm)
+        decls.append((m.group(1).strip(), m.group(2), types))
+    return decls
+
+
+def test_exports_equal_the_reference_headers_manglings(lib, tmp_path):
+    """With the reference checkout present: a translation unit that takes the address of every member the
+    reference's own blas/NativeOps.h declares is compiled against that header; its undefined symbols are the
+    manglings nd4j's JNI layer binds. Every overload of every member name this library serves must be exported
+    under exactly that mangling, and the library must export no NativeOps member the reference does not have."""
+    if not os.path.isfile(os.path.join(REFERENCE, "blas", "NativeOps.h")):
+        pytest.skip("reference checkout not present")
+    decls = reference_member_declarations(REFERENCE)
+    assert len(decls) >= 200
+    lines = ["#include <NativeOps.h>", "void *sink[%d];" % len(decls), "void take() {"]
+    for i, (ret, name, types) in enumerate(decls):
+        lines.append("  { %s (NativeOps::*p)(%s) = &NativeOps::%s; sink[%d] = *reinterpret_cast<void **>(&p); }"
+                     % (ret, ", ".join(types), name, i))
+    lines.append("}")
+    src = tmp_path / "members.cpp"
+    src.write_text("\n".join(lines))
+    obj = str(tmp_path / "members.o")
+    cmd = ["g++", "-std=c++11", "-w", "-include", "limits", "-include", "cstdint", "-D__CPUBLAS__=true"]
+    for d in REF_INCLUDES:
+        cmd += ["-I", os.path.join(REFERENCE, d)]
+    env = dict(os.environ, PATH="/usr/bin:" + os.environ.get("PATH", ""))
+    subprocess.run(cmd + ["-c", str(src), "-o", obj], check=True, env=env)
+    out = subprocess.run(["nm", "-u", obj], capture_output=True, text=True, check=True).stdout
+    wanted = {l.split()[-1] for l in out.splitlines() if "_ZN9NativeOps" in l}
+    assert len(wanted) == len(decls)
+    ours = {sym for sym in exported_symbols() if sym.startswith("_ZN9NativeOps")}
+    strays = ours - wanted
+    assert not strays, "exported but not declared by the reference: %s" % sorted(strays)
+    # member names served here = the names our class header declares
+    mine = open(CLASS_HEADER).read()
+    served = {name for _, name, _ in decls if re.search(r"\b%s\b|\b%s##S" % (name, re.sub(r"(Float|Double|Half)$", "", name)), mine)}
+
+    def member_name(sym):
+        m = re.match(r"_ZN9NativeOps(\d+)", sym)
+        n = int(m.group(1))
+        return sym[len(m.group(0)):len(m.group(0)) + n]
+    missing = sorted(sym for sym in wanted if member_name(sym) in served and sym not in ours)
+    assert not missing, "overloads of served members that are not exported: %s" % missing
+    assert len(ours) >= 140
+
+
 def test_class_header_and_c_header_compile_as_c_and_cpp(tmp_path):
     c = tmp_path / "t.c"
     c.write_text('#include "nd4j_b200.h"\nint main(void) { return nd4jb200_get_device == 0; }\n')

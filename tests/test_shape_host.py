@@ -65,6 +65,47 @@ def test_random_sweep_against_live_reference(host_ops, real_ref):
         np.testing.assert_array_equal(got_info, want_info, err_msg=str((shape, order, dims)))
 
 
+def test_dimension_list_recovered_from_the_tad_descriptor(host_ops, real_ref):
+    """nd4jb200_dims_from_tad: given the array's shapeInfo and the REFERENCE's TAD shapeInfo for some dimension
+    list (what a caller of the CUDA build keeps on the host), the recovered list must produce the same TADs:
+    same count, same length, same base offsets and the same element offsets inside a TAD."""
+    rng = np.random.default_rng(1)
+    for trial in range(400):
+        rank = int(rng.integers(1, 6))
+        shape = [int(v) for v in rng.integers(1, 5, rank)]
+        if trial % 3 == 0:
+            shape = [int(v) for v in rng.integers(2, 5, rank)]     # no unit axes
+        order = "c" if rng.random() < 0.5 else "f"
+        nd = int(rng.integers(1, rank + 1))
+        dims = sorted(int(d) for d in rng.choice(rank, nd, replace=False))
+        info = S.shape_info(shape, order)
+        ref_tad, ref_off = real_ref.tad(info, dims)
+        got = host_ops.dimsFromTad(info, ref_tad)
+        assert got is not None, (shape, order, dims, ref_tad)
+        what = str((shape, order, dims, got))
+        if not got:                                                 # whole array
+            assert int(np.prod(shape)) == int(np.prod(S.shape_of(ref_tad))), what
+            continue
+        _, off = host_ops.tadOnlyShapeInfo(info, got, len(got))
+        np.testing.assert_array_equal(off, ref_off, err_msg=what)
+        strides = S.strides_of(info)
+        inner = lambda dd: sorted(int(np.dot(c, [strides[d] for d in dd]))
+                                  for c in np.ndindex(*[shape[d] for d in dd]))
+        assert inner(got) == inner(dims), what
+
+
+def test_dimension_list_recovery_on_views_and_failures(host_ops):
+    # f-order parent [32768, 1024], every second column: the benchmark's reduce3 view, TAD along dimension 1
+    view = S.shape_info([32768, 512], "f", [1, 65536], ews=-1)
+    tad, _ = host_ops.tadOnlyShapeInfo(view, [1], 1)
+    assert host_ops.dimsFromTad(view, tad) == [1]
+    tad, _ = host_ops.tadOnlyShapeInfo(view, [0], 1)
+    assert host_ops.dimsFromTad(view, tad) == [0]
+    # a descriptor that belongs to another array is refused instead of guessed
+    other, _ = host_ops.tadOnlyShapeInfo(S.shape_info([7, 9]), [1], 1)
+    assert host_ops.dimsFromTad(view, other) is None
+
+
 def test_offsets_with_unit_axes_match_reference(host_ops, real_ref):
     for shape, dims in (((3, 1, 4), [2]), ((3, 1, 4), [0, 1]), ((1, 5), [0]), ((5, 1), [1]), ((2, 1, 1, 3), [3])):
         info = S.shape_info(shape)
