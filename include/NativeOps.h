@@ -150,6 +150,27 @@ public:
                            Nd4jLong *resultShapeInfo, float16 *extraParams, Nd4jLong *xIndexes,
                            Nd4jLong *resultIndexes);
 
+    /* nd4jb200_exec_meta_predicate_strided / _shape (NativeOps.h:2564-2759): pairwise opNumA (opTypeA 2) followed by
+     * scalar opNumB (opTypeB 0) in one launch; shapeInfo arguments are device pointers with host copies in
+     * extraPointers[0], [7], [8] like everywhere else */
+#define ND4JB200_DECLARE_META(T, S, ST)                                                                             \
+    void execMetaPredicateStrided##S(Nd4jPointer *extras, const int opTypeA, const int opNumA, const int opTypeB,    \
+                                     const int opNumB, Nd4jLong N, T *dx, Nd4jLong xStride, T *dy, Nd4jLong yStride, \
+                                     T *dz, Nd4jLong zStride, T *extraA, T *extraB, ST scalarA, ST scalarB);         \
+    void execMetaPredicateShape##S(Nd4jPointer *extras, const int opTypeA, const int opNumA, const int opTypeB,      \
+                                   const int opNumB, Nd4jLong N, T *dx, Nd4jLong *xShapeInfo, T *dy,                 \
+                                   Nd4jLong *yShapeInfo, T *dz, Nd4jLong *zShapeInfo, T *extraA, T *extraB,          \
+                                   ST scalarA, ST scalarB);
+    ND4JB200_DECLARE_META(float, Float, float)
+    ND4JB200_DECLARE_META(double, Double, double)
+    ND4JB200_DECLARE_META(float16, Half, float)
+    /* does nothing in the reference either (blas/cuda/NativeOps.cu:5065-5078, blas/cpu/NativeOps.cpp:2393-2417) */
+    void execMetaPredicateReduceFloat(Nd4jPointer *extras, const int opTypeA, const int opNumA, const int opTypeB,
+                                      const int opNumB, float *dx, Nd4jLong *xShapeInfo, float *dy, Nd4jLong *yShapeInfo,
+                                      float *dz, Nd4jLong *zShapeInfo, int *dimension, int dimensionLength,
+                                      Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets, float *extraA, float *extraB,
+                                      float scalarA, float scalarB, bool scalarReturned);
+
     /* nd4jb200_init_random and friends (NativeOps.h:2510-2539). extraPointers[0] = host table,
      * [1] = stream, ptrToBuffer = device table (blas/cuda/NativeOps.cu:5384-5391). */
     Nd4jPointer initRandom(Nd4jPointer *extraPointers, long seed, long bufferSize, Nd4jPointer ptrToBuffer);

@@ -277,6 +277,31 @@ int nd4jb200_device_major(int device);
 int nd4jb200_device_minor(int device);
 const char *nd4jb200_device_name(int device);
 
+/* ---- fused elementwise chains --------------------------------------------------------------------------------
+ * exec_chain has no counterpart among the reference's members: it runs what a caller would otherwise issue as
+ *   execBroadcast(broadcastOp, x, b, dimension) -> execTransform(transformOp) -> execPairwiseTransform(pairwiseOp, ., y)
+ * (blas/NativeOps.h:615-649, 1337-1443, 665-798) as ONE pass that reads x and y once and writes z once, with results
+ * bit-identical to the three calls. x, y and z must have one shape; z may alias x or y. Fused for the arithmetic /
+ * comparison / min / max broadcast and pairwise ops and every elementwise transform; any other op combination is
+ * executed as the three separate launches (through z, which must then not alias y).
+ * exec_meta_predicate_* serve the reference's own fusion hook, NativeOps::execMetaPredicateShape* / Strided*
+ * (blas/NativeOps.h:2564-2785): opTypeA 2 (pairwise opNumA on x, y with extraA) followed by opTypeB 0 (scalar
+ * opNumB with scalarB), the only pair the reference implements (include/loops/cuda/grid_shaped.cu:159-211).
+ * Unlike the reference's kernel, out-of-place calls write every element of z (grid_shaped.cu:283 writes
+ * result[0] only). */
+int nd4jb200_exec_chain(void *stream, int dtype, int broadcastOp, const void *x, const Nd4jLong *xShapeInfo,
+                        const void *b, const Nd4jLong *bShapeInfo, const int *dimension, int dimensionLength,
+                        int transformOp, const void *transformExtra, int pairwiseOp, const void *y,
+                        const Nd4jLong *yShapeInfo, const void *pairwiseExtra, void *z, const Nd4jLong *zShapeInfo);
+int nd4jb200_exec_meta_predicate_shape(void *stream, int dtype, int opTypeA, int opNumA, int opTypeB, int opNumB,
+                                       const void *x, const Nd4jLong *xShapeInfo, const void *y,
+                                       const Nd4jLong *yShapeInfo, void *z, const Nd4jLong *zShapeInfo,
+                                       const void *extraA, const void *extraB, double scalarA, double scalarB);
+int nd4jb200_exec_meta_predicate_strided(void *stream, int dtype, int opTypeA, int opNumA, int opTypeB, int opNumB,
+                                         Nd4jLong n, const void *x, Nd4jLong xStride, const void *y, Nd4jLong yStride,
+                                         void *z, Nd4jLong zStride, const void *extraA, const void *extraB,
+                                         double scalarA, double scalarB);
+
 /* ---- peer access and the constant-memory staging area (blas/NativeOps.h:1836-1846, 2047-2058;
  *      blas/cuda/NativeOps.cu:87, 3854-3938, 4793-4834) -------------------------------------------------------
  * check_p2p probes every ordered device pair and records whether all of them can reach each other (one device

@@ -27,7 +27,7 @@ NVCC_FLAGS = [
 
 def _sources():
     units = []
-    for fam in range(6):
+    for fam in range(7):
         for dt in range(3):
             units.append(("family_%d_%d" % (fam, dt), "family_tu.cu", ["-DND_FAMILY=%d" % fam, "-DND_DTYPE=%d" % dt]))
     units.append(("api", "api.cu", []))

@@ -659,6 +659,113 @@ int nd4jb200_exec_scalar_along_dimension(void *stream, int dtype, int opNum, con
 }
 
 // ---------------------------------------------------------------------------------------------
+// Fused chains. exec_chain: z = pairwise(transform(broadcast(x, b)), y) in one pass (fused_engine.cuh) when the
+// broadcast and pairwise ops are light ops; otherwise the three steps run as separate launches through z.
+int nd4jb200_exec_chain(void *stream, int dtype, int broadcastOp, const void *x, const Nd4jLong *xShapeInfo,
+                        const void *b, const Nd4jLong *bShapeInfo, const int *dimension, int dimensionLength,
+                        int transformOp, const void *transformExtra, int pairwiseOp, const void *y,
+                        const Nd4jLong *yShapeInfo, const void *pairwiseExtra, void *z, const Nd4jLong *zShapeInfo) {
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(b, "b")); ND_TRY(need(y, "y")); ND_TRY(need(z, "z"));
+    ND_TRY(need(dimension, "dimension"));
+    const int bc = light_of_broadcast(broadcastOp), pw = light_of_pairwise(pairwiseOp);
+    const bool composite = transformOp == 36 || transformOp == 37 || transformOp == 38 || transformOp == 39 ||
+                           transformOp == 40 || transformOp == 41 || transformOp == 48 || transformOp == 70 ||
+                           transformOp == 71;
+    if (bc == kLightNone || pw == kLightNone || composite) {
+        if (z == y) return unsupported("exec_chain: with these ops the steps run as separate launches through z, which "
+                                       "must then not alias y");
+        ND_TRY((Status) nd4jb200_exec_broadcast(stream, dtype, broadcastOp, x, xShapeInfo, b, bShapeInfo, z, zShapeInfo,
+                                                dimension, dimensionLength));
+        ND_TRY((Status) nd4jb200_exec_transform(stream, dtype, transformOp, z, zShapeInfo, z, zShapeInfo, transformExtra));
+        return nd4jb200_exec_pairwise(stream, dtype, pairwiseOp, z, zShapeInfo, y, yShapeInfo, z, zShapeInfo, pairwiseExtra);
+    }
+    ShapeDesc xd, yd, zd, bd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &yd));
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    ND_TRY(parse_shape(bShapeInfo, "bShapeInfo", &bd));
+    // the pairwise step pairs by coordinates, which is what the separate launches do for arrays of one shape
+    if (!same_shape(xd, yd) || !same_shape(xd, zd)) return bad_arg("exec_chain: x, y and z must have the same shape");
+    TadPlan xp, yp, zp;
+    ND_TRY(make_tad_plan(xd, dimension, dimensionLength, &xp));
+    ND_TRY(make_tad_plan(yd, dimension, dimensionLength, &yp));
+    ND_TRY(make_tad_plan(zd, dimension, dimensionLength, &zp));
+    if (xp.whole) { ND_TRY(coord_view(xd, &xp.inner)); ND_TRY(coord_view(yd, &yp.inner)); ND_TRY(coord_view(zd, &zp.inner)); }
+    if (bd.length != xp.tadLen) {
+        std::ostringstream os;
+        os << "exec_chain: b holds " << bd.length << " elements but a TAD along the given dimension holds " << xp.tadLen;
+        return bad_arg(os.str());
+    }
+    if (xd.length == 0) return kOk;
+    ChainArgs a;
+    a.x = x; a.b = b; a.y = y; a.z = z; a.trExtra = transformExtra;
+    a.numTads = xp.numTads; a.tadLen = xp.tadLen;
+    a.xOuter = xp.outer; a.xInner = xp.inner; a.yOuter = yp.outer; a.yInner = yp.inner;
+    a.zOuter = zp.outer; a.zInner = zp.inner;
+    ND_TRY(coord_view(bd, &a.bView));
+    a.bcCode = bc; a.pwCode = pw; a.rowsPerBlock = 1;
+    const LL V = 16 / (LL) dtype_size(dtype);
+    auto unit = [](const View &v) { return v.rank == 0 || (v.rank == 1 && v.stride[0] == 1); };
+    auto rowsOf = [&](const View &inner, const View &outer, const void *ptr) {
+        return unit(inner) && outer.rank <= 1 && aligned16(ptr) && view_strides_multiple_of(outer, V);
+    };
+    const bool rows = rowsOf(a.xInner, a.xOuter, x) && rowsOf(a.yInner, a.yOuter, y) && rowsOf(a.zInner, a.zOuter, z) &&
+                      a.tadLen % V == 0 && unit(a.bView) && aligned16(b);
+    a.mode = rows ? 0 : 1;
+    return BY_DTYPE(dtype, chain, transformOp, a, as_stream(stream));
+}
+
+// The reference's meta-op hook (blas/NativeOps.h:2564-2785): opTypeA 2 = a pairwise op on (x, y) with extraA,
+// followed by opTypeB 0 = a scalar op with scalarB (include/loops/cuda/grid_shaped.cu:159-211; no other type
+// pair has an implementation there). One launch when the scalar op is a light op, two otherwise.
+static Status meta_pair(void *stream, int dtype, int opTypeA, int opNumA, int opTypeB, int opNumB, EwArgs &a,
+                        const Nd4jLong *zShapeInfo, Nd4jLong zStride, double scalarB, const void *extraB) {
+    if (opTypeA != 2 || opTypeB != 0)
+        return unsupported("execMetaPredicate: only a pairwise op (type 2) followed by a scalar op (type 0) is defined");
+    const int post = light_of_scalar(opNumB);
+    if (post != kLightNone) {
+        a.postCode = post; a.postScalar = scalarB;
+        return BY_DTYPE(dtype, pairwise_post, opNumA, a, as_stream(stream));
+    }
+    ND_TRY(BY_DTYPE(dtype, pairwise, opNumA, a, as_stream(stream)));
+    if (zShapeInfo) return (Status) nd4jb200_exec_scalar(stream, dtype, opNumB, a.z, zShapeInfo, a.z, zShapeInfo, scalarB, extraB);
+    return (Status) nd4jb200_exec_scalar_strided(stream, dtype, opNumB, a.z, zStride, a.z, zStride, scalarB, extraB, a.n);
+}
+
+int nd4jb200_exec_meta_predicate_shape(void *stream, int dtype, int opTypeA, int opNumA, int opTypeB, int opNumB,
+                                       const void *x, const Nd4jLong *xShapeInfo, const void *y,
+                                       const Nd4jLong *yShapeInfo, void *z, const Nd4jLong *zShapeInfo,
+                                       const void *extraA, const void *extraB, double scalarA, double scalarB) {
+    (void) scalarA;
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(y, "y")); ND_TRY(need(z, "z"));
+    ShapeDesc xd, yd, zd;
+    ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
+    ND_TRY(parse_shape(yShapeInfo, "yShapeInfo", &yd));
+    ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    if (xd.length != yd.length || xd.length != zd.length) return bad_arg("execMetaPredicateShape: x, y and z hold different numbers of elements");
+    EwArgs a;
+    a.x = x; a.y = y; a.z = z; a.extra = extraA; a.n = xd.length; a.scalar = 0;
+    ND_TRY(setup_linear(&xd, &yd, &zd, x, y, z, &a));
+    return meta_pair(stream, dtype, opTypeA, opNumA, opTypeB, opNumB, a, zShapeInfo, 0, scalarB, extraB);
+}
+
+int nd4jb200_exec_meta_predicate_strided(void *stream, int dtype, int opTypeA, int opNumA, int opTypeB, int opNumB,
+                                         Nd4jLong n, const void *x, Nd4jLong xStride, const void *y, Nd4jLong yStride,
+                                         void *z, Nd4jLong zStride, const void *extraA, const void *extraB,
+                                         double scalarA, double scalarB) {
+    (void) scalarA;
+    ND_TRY(check_dtype(dtype));
+    ND_TRY(need(x, "x")); ND_TRY(need(y, "y")); ND_TRY(need(z, "z"));
+    EwArgs a;
+    a.x = x; a.y = y; a.z = z; a.extra = extraA; a.n = n; a.scalar = 0;
+    a.sx = xStride; a.sy = yStride; a.sz = zStride;
+    a.mode = (xStride == 1 && yStride == 1 && zStride == 1 && aligned16(x) && aligned16(y) && aligned16(z)) ? 0 : 1;
+    return meta_pair(stream, dtype, opTypeA, opNumA, opTypeB, opNumB, a, nullptr, zStride, scalarB, extraB);
+}
+
+// ---------------------------------------------------------------------------------------------
 Nd4jPointer nd4jb200_init_random(void *stream, Nd4jLong seed, Nd4jLong bufferSize, void *hostTable, void *deviceTable) {
     if (bufferSize <= 0) { bad_arg("initRandom: bufferSize must be positive"); return nullptr; }
     RandomState *s = new RandomState();

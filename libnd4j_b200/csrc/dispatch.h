@@ -6,12 +6,15 @@
 #include "rng_engine.cuh"
 #include "reduce3_all.cuh"
 #include "softmax.cuh"
+#include "fused_engine.cuh"
 
 namespace nd4jb200 {
 
 #define ND_DECLARE_DISPATCH(S)                                                         \
     Status transform_##S(int opNum, const EwArgs &a, cudaStream_t st);                 \
     Status pairwise_##S(int opNum, const EwArgs &a, cudaStream_t st);                  \
+    Status pairwise_post_##S(int opNum, const EwArgs &a, cudaStream_t st);             \
+    Status chain_##S(int transformOp, const ChainArgs &a, cudaStream_t st);            \
     Status scalar_##S(int opNum, const EwArgs &a, cudaStream_t st);                    \
     Status broadcast_##S(int opNum, const BcArgs &a, cudaStream_t st);                 \
     Status scalar_tad_##S(int opNum, const BcArgs &a, cudaStream_t st);                \

@@ -13,6 +13,7 @@
 // thread and inputs are fetched with ordinary (coherent) loads.
 #pragma once
 #include "device_utils.cuh"
+#include "light_ops.cuh"
 #include "runtime.h"
 
 namespace nd4jb200 {
@@ -28,6 +29,10 @@ struct EwArgs {
     LL sx, sy, sz;
     View vx, vy, vz;
     const LL *ix = nullptr, *iy = nullptr, *iz = nullptr;   // indexed: device arrays of n offsets per operand
+    // POST kernels only: z = light_apply(postCode, f(x, y), postScalar), the pairwise-then-scalar pair of the
+    // reference's meta-op hook (include/ops/meta_ops.h:13-52)
+    int postCode = kLightNone;
+    double postScalar = 0;
 };
 
 constexpr int kEwBlock = 256;
@@ -39,11 +44,17 @@ template <class Op, int ARITY, class C> ND_D C ew_apply(C x, C y, C sc, const C 
     else if constexpr (ARITY == 2) return Op::template f<C>(x, y, p);
     else return Op::template f<C>(x, sc, p);
 }
+// The optional second step of a POST kernel; the first step's result goes through the element type as if it
+// had been stored by one launch and loaded by the next.
+template <class T, bool POST, class C> ND_D C ew_post(const EwArgs &a, C r) {
+    if constexpr (POST) return light_apply<C>(a.postCode, through_memory<T>(r), C(a.postScalar));
+    else return r;
+}
 // Functors that keep a table in shared memory declare kPrepare and a prepare() every thread of the CTA calls.
 template <class Op, class = void> struct HasPrepare { static constexpr bool value = false; };
 template <class Op> struct HasPrepare<Op, decltype((void) Op::kPrepare)> { static constexpr bool value = true; };
 
-template <class T, class Op, int ARITY>
+template <class T, class Op, int ARITY, bool POST = false>
 __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
     grid_dependency_sync();
     if constexpr (HasPrepare<Op>::value) Op::prepare();
@@ -78,7 +89,7 @@ __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
 #pragma unroll
                     for (int k = 0; k < V; k++) {
                         C yc = ARITY == 2 ? Elem<T>::to_c(yv[u].v[k]) : C(0);
-                        r.v[k] = Elem<T>::from_c(ew_apply<Op, ARITY, C>(Elem<T>::to_c(xv[u].v[k]), yc, sc, p));
+                        r.v[k] = Elem<T>::from_c(ew_post<T, POST, C>(a, ew_apply<Op, ARITY, C>(Elem<T>::to_c(xv[u].v[k]), yc, sc, p)));
                     }
                     store_pack(az + i * V, r);
                 }
@@ -88,7 +99,7 @@ __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
         const LL i = npacks * V + tid;
         if (i < a.n) {
             C yc = ARITY == 2 ? Elem<T>::load(ay + i) : C(0);
-            Elem<T>::store(az + i, ew_apply<Op, ARITY, C>(Elem<T>::load(ax + i), yc, sc, p));
+            Elem<T>::store(az + i, ew_post<T, POST, C>(a, ew_apply<Op, ARITY, C>(Elem<T>::load(ax + i), yc, sc, p)));
         }
     } else {
         for (LL i = tid; i < a.n; i += nthreads) {
@@ -100,12 +111,12 @@ __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
                 if (ARITY == 2) oy = view_offset(a.vy, i);
             }
             C yc = ARITY == 2 ? Elem<T>::load(ay + oy) : C(0);
-            Elem<T>::store(az + oz, ew_apply<Op, ARITY, C>(Elem<T>::load(ax + ox), yc, sc, p));
+            Elem<T>::store(az + oz, ew_post<T, POST, C>(a, ew_apply<Op, ARITY, C>(Elem<T>::load(ax + ox), yc, sc, p)));
         }
     }
 }
 
-template <class T, class Op, int ARITY>
+template <class T, class Op, int ARITY, bool POST = false>
 Status run_elementwise(EwArgs a, cudaStream_t stream) {
     constexpr int V = Elem<T>::kVec;
     if (a.n <= 0) return kOk;
@@ -114,7 +125,7 @@ Status run_elementwise(EwArgs a, cudaStream_t stream) {
     const LL cap = (LL) kNumSMs * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    launch_kernel(k_elementwise<T, Op, ARITY>, dim3((unsigned) blocks), dim3(kEwBlock), stream, a);
+    launch_kernel(k_elementwise<T, Op, ARITY, POST>, dim3((unsigned) blocks), dim3(kEwBlock), stream, a);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }

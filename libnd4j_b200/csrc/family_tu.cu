@@ -2,7 +2,8 @@
 // opNum of the reference's table and exposes a switch-based dispatcher.
 //   ND_DTYPE:  0 float, 1 double, 2 half
 //   ND_FAMILY: 0 transform, 1 binary (pairwise, scalar, broadcast, scalar-along-dimension),
-//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random, 5 composites (reduce3 over all TAD pairs, row softmax family)
+//              2 reduce, 3 reduce3 + indexreduce + summarystats, 4 random, 5 composites (reduce3 over all TAD pairs, row softmax family),
+//              6 fused elementwise (broadcast -> transform -> pairwise chain, pairwise -> scalar pair)
 #include "dispatch.h"
 #include "functors.cuh"
 #include "policies.cuh"
@@ -133,6 +134,23 @@ Status ND_S(softmax)(int kind, const SoftmaxArgs &a, cudaStream_t st) {
     return run_softmax<ND_T, 2>(a, st);
 }
 Status ND_S(ismax_mark)(const IsMaxArgs &a, cudaStream_t st) { return run_ismax_mark<ND_T>(a, st); }
+#elif ND_FAMILY == 6
+Status ND_S(chain)(int transformOp, const ChainArgs &a, cudaStream_t st) {
+    switch (transformOp) {
+#define X(num, Name) case num: return run_chain<ND_T, fn::Name>(a, st);
+        ND_TRANSFORM_TABLE(X)
+#undef X
+        default: return unknown_op("transform", transformOp);
+    }
+}
+Status ND_S(pairwise_post)(int opNum, const EwArgs &a, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_elementwise<ND_T, fn::Name, 2, true>(a, st);
+        ND_PAIRWISE_TABLE(X)
+#undef X
+        default: return unknown_op("pairwise transform", opNum);
+    }
+}
 #elif ND_FAMILY == 4
 // Dense launches give every CTA one contiguous chunk of indices (a multiple of `quantum`), enough
 // CTAs to fill the machine a few times over, so that the per-thread cursor set-up is amortised.

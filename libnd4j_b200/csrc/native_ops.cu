@@ -369,6 +369,30 @@ void NativeOps::execTransformFloat(Nd4jPointer *, int, float *, Nd4jLong *, floa
 void NativeOps::execTransformHalf(Nd4jPointer *, int, float16 *, Nd4jLong *, float16 *, Nd4jLong *, float16 *, Nd4jLong *,
                                   Nd4jLong *) {}
 
+#define ND4JB200_DEFINE_META(T, S, ST)                                                                                 \
+    void NativeOps::execMetaPredicateStrided##S(Nd4jPointer *extraPointers, const int opTypeA, const int opNumA,      \
+                                                const int opTypeB, const int opNumB, Nd4jLong N, T *dx,               \
+                                                Nd4jLong xStride, T *dy, Nd4jLong yStride, T *dz, Nd4jLong zStride,   \
+                                                T *extraA, T *extraB, ST scalarA, ST scalarB) {                       \
+        check(nd4jb200_exec_meta_predicate_strided(STREAM, TypeCode<T>::v, opTypeA, opNumA, opTypeB, opNumB, N, dx,   \
+                                                   xStride, dy, yStride, dz, zStride, extraA, extraB,                 \
+                                                   (double) scalarA, (double) scalarB), "execMetaPredicateStrided" #S); \
+    }                                                                                                                  \
+    void NativeOps::execMetaPredicateShape##S(Nd4jPointer *extraPointers, const int opTypeA, const int opNumA,        \
+                                              const int opTypeB, const int opNumB, Nd4jLong, T *dx,                   \
+                                              Nd4jLong *xShapeInfo, T *dy, Nd4jLong *yShapeInfo, T *dz,               \
+                                              Nd4jLong *zShapeInfo, T *extraA, T *extraB, ST scalarA, ST scalarB) {   \
+        check(nd4jb200_exec_meta_predicate_shape(STREAM, TypeCode<T>::v, opTypeA, opNumA, opTypeB, opNumB, dx,        \
+                                                 X_INFO, dy, Y_INFO, dz, Z_INFO(zShapeInfo), extraA, extraB,          \
+                                                 (double) scalarA, (double) scalarB), "execMetaPredicateShape" #S);    \
+    }
+ND4JB200_DEFINE_META(float, Float, float)
+ND4JB200_DEFINE_META(double, Double, double)
+ND4JB200_DEFINE_META(float16, Half, float)
+void NativeOps::execMetaPredicateReduceFloat(Nd4jPointer *, const int, const int, const int, const int, float *, Nd4jLong *,
+                                             float *, Nd4jLong *, float *, Nd4jLong *, int *, int, Nd4jLong *, Nd4jLong *,
+                                             float *, float *, float, float, bool) {}
+
 void NativeOps::convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z) {
     check(nd4jb200_convert_types(stream_of(extras), srcType, x, N, dstType, z), "convertTypes");
 }

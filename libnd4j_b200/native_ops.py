@@ -99,6 +99,9 @@ def load_library(path=None):
         "nd4jb200_exec_pairwise_strided": (i, [vp, i, i, vp, ll, vp, ll, vp, ll, vp, ll]),
         "nd4jb200_exec_pairwise_indexed": (i, [vp, i, i, vp, llp, vp, vp, vp, vp, vp, vp]),
         "nd4jb200_exec_scalar_indexed": (i, [vp, i, i, vp, llp, vp, d, vp, vp, vp]),
+        "nd4jb200_exec_chain": (i, [vp, i, i, vp, llp, vp, llp, ip, i, i, vp, i, vp, llp, vp, vp, llp]),
+        "nd4jb200_exec_meta_predicate_shape": (i, [vp, i, i, i, i, i, vp, llp, vp, llp, vp, llp, vp, vp, d, d]),
+        "nd4jb200_exec_meta_predicate_strided": (i, [vp, i, i, i, i, i, ll, vp, ll, vp, ll, vp, ll, vp, vp, d, d]),
         "nd4jb200_exec_broadcast": (i, [vp, i, i, vp, llp, vp, llp, vp, llp, ip, i]),
         "nd4jb200_exec_scalar": (i, [vp, i, i, vp, llp, vp, llp, d, vp]),
         "nd4jb200_exec_scalar_strided": (i, [vp, i, i, vp, ll, vp, ll, d, vp, ll]),
@@ -305,6 +308,35 @@ class NativeOps:
         dm, dmp = _ints(dimension)
         self._check(self.lib.nd4jb200_exec_broadcast(self._stream(extraPointers), dt, opNum, _ptr(x), xsp, _ptr(y), ysp,
                                                      _ptr(result), zsp, dmp, dimensionLength))
+
+    def execChain(self, dt, extraPointers, broadcastOp, x, xShapeInfo, b, bShapeInfo, dimension, dimensionLength,
+                  transformOp, transformExtra, pairwiseOp, y, yShapeInfo, pairwiseExtra, z, zShapeInfo):
+        """z = pairwise(transform(broadcast(x, b)), y) in one pass (nd4jb200_exec_chain): what execBroadcast ->
+        execTransform -> execPairwiseTransform would compute, bit for bit."""
+        xs, xsp = _longs(xShapeInfo)
+        bs, bsp = _longs(bShapeInfo)
+        ys, ysp = _longs(yShapeInfo)
+        zs, zsp = _longs(zShapeInfo)
+        dm, dmp = _ints(dimension)
+        self._check(self.lib.nd4jb200_exec_chain(self._stream(extraPointers), dt, broadcastOp, _ptr(x), xsp, _ptr(b), bsp,
+                                                 dmp, dimensionLength, transformOp, _ptr(transformExtra), pairwiseOp,
+                                                 _ptr(y), ysp, _ptr(pairwiseExtra), _ptr(z), zsp))
+
+    def _execMetaPredicateShape(self, dt, extras, opTypeA, opNumA, opTypeB, opNumB, N, dx, xShapeInfo, dy, yShapeInfo,
+                                dz, zShapeInfo, extraA, extraB, scalarA, scalarB):
+        xs, xsp = _longs(xShapeInfo)
+        ys, ysp = _longs(yShapeInfo)
+        zs, zsp = _longs(zShapeInfo)
+        self._check(self.lib.nd4jb200_exec_meta_predicate_shape(self._stream(extras), dt, opTypeA, opNumA, opTypeB, opNumB,
+                                                                _ptr(dx), xsp, _ptr(dy), ysp, _ptr(dz), zsp, _ptr(extraA),
+                                                                _ptr(extraB), float(scalarA), float(scalarB)))
+
+    def _execMetaPredicateStrided(self, dt, extras, opTypeA, opNumA, opTypeB, opNumB, N, dx, xStride, dy, yStride, dz,
+                                  zStride, extraA, extraB, scalarA, scalarB):
+        self._check(self.lib.nd4jb200_exec_meta_predicate_strided(self._stream(extras), dt, opTypeA, opNumA, opTypeB,
+                                                                  opNumB, N, _ptr(dx), xStride, _ptr(dy), yStride, _ptr(dz),
+                                                                  zStride, _ptr(extraA), _ptr(extraB), float(scalarA),
+                                                                  float(scalarB)))
 
     def _execScalar(self, dt, extraPointers, opNum, x, xShapeInfo, result, resultShapeInfo, scalar, extraParams,
                     n=None, resultIndexes=None):
@@ -604,7 +636,8 @@ def _bind(generic, dt):
 for _fam in ("execReduce", "execReduceScalar", "execIndexReduce", "execIndexReduceScalar", "execSummaryStats",
              "execSummaryStatsScalar", "execReduce3", "execReduce3All", "execReduce3Scalar", "execTransform", "execPairwiseTransform",
              "execBroadcast", "execScalar", "execScalarAlongDimension", "execRandom", "flatten", "concat", "pullRows",
-             "tear", "shuffle", "sort", "sortTad", "average", "accumulate"):
+             "tear", "shuffle", "sort", "sortTad", "average", "accumulate", "execMetaPredicateShape",
+             "execMetaPredicateStrided"):
     for _sfx, _dt in _SUFFIX.items():
         _m = _bind("_" + _fam, _dt)
         _m.__name__ = _fam + _sfx
