@@ -583,6 +583,16 @@ def run_ours(args):
         calls.check(lib.nd4jb200_set_tuning(int(key), ctypes.c_longlong(int(value))))
     peak, peak_src = measured_peaks()
 
+    if world > 1 and hasattr(os, "sched_setaffinity"):
+        # every rank keeps to its own slice of the host cores, so that its copy threads and the pages of its
+        # pinned buffers (first touched below) stay together
+        cores = sorted(os.sched_getaffinity(0))
+        share = max(1, len(cores) // world)
+        mine = cores[local * share:(local + 1) * share] or cores
+        try:
+            os.sched_setaffinity(0, mine)
+        except OSError:
+            pass
     x, b, y = make_inputs(ROWS)
     hx, hb, hy = (torch.from_numpy(a).pin_memory() for a in (x, b, y))
     hz = torch.empty(ELEMS, dtype=torch.float32).pin_memory()
@@ -712,7 +722,9 @@ def run_ours(args):
         e2e_ms = float(t.item())
     e2e = {"value": round(world * ELEMS / e2e_ms / 1e6, 3), "unit": "Gelem/s", "ms_per_step": round(e2e_ms, 3),
            "h2d_bytes_per_step": 2 * ELEMS * 4 + COLS * 4, "d2h_bytes_per_step": ELEMS * 4,
-           "pipeline": "%d row blocks; H2D, chain and D2H on three streams" % NBLK}
+           "pipeline": "%d row blocks; H2D, chain and D2H on three streams" % NBLK,
+           "per_rank_h2d_GBps": round((2 * ELEMS * 4 + COLS * 4) / e2e_ms / 1e6, 1),
+           "per_rank_d2h_GBps": round(ELEMS * 4 / e2e_ms / 1e6, 1)}
 
     families = None
     if world == 1 and not args.no_families:
@@ -754,33 +766,51 @@ def run_ours(args):
 
 
 def sharded_families(torch, dist, ops, calls, stream, world, rank, quick):
-    """N > 1: the two sharded workloads. Random generation is offset-sharded with global indices
-    and needs no exchange; the whole-array Sum reduces each shard locally and combines the
-    per-GPU partials with one NCCL all-reduce (the only collective on this path)."""
+    """N > 1: every family of the configurations, sharded the way it shards naturally. Random generation is
+    offset-sharded with global indices; reductions along a dimension are row- or column-sharded (disjoint result
+    slices); neither needs an exchange. The whole-array Sum reduces each shard locally and combines accumulator
+    states through the library's own communicator (one ncclAllGather on the launch stream, then the same
+    fixed-order fold on every rank): the only collective on this path. Times are CUDA-event times on the launch
+    stream, max over ranks; Gelem/s counts the elements of all ranks."""
     from libnd4j_b200 import shape as S
     lib, st, P = calls.lib, calls.stream, calls.p
     dev = torch.device("cuda")
     out = {}
+    uid = [ops.commUniqueId() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    ops.commInit(uid[0], rank, world)
+
+    def over_ranks(ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, iters, graph=False):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = time_graph(torch, stream, fn, iters) if graph else time_loop(torch, stream, fn, iters)
+        return over_ranks(ms)
+
+    # ---- C5a: 2^30 draws, rank g produces global indices [g * n / G, (g + 1) * n / G) ----
     n = 1 << (26 if quick else 30)
     per = n // world
     state = ops.initRandom([None, stream.cuda_stream], 119, 100000, None)
     sp = ctypes.c_void_p(state)
     z = torch.empty(per, device=dev)
-    e01 = torch.tensor([0.0, 1.0], device=dev)
-
-    def timed(fn, iters):
-        for _ in range(2):
-            fn()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms = time_loop(torch, stream, fn, iters)
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    ms = timed(lambda: calls.check(lib.nd4jb200_exec_random_range(st, 0, 0, 0, sp, None, None, P(z), P(e01),
-                                                                  rank * per, per, n)), 3)
-    out["random_uniform_sharded"] = {"ms": round(ms, 4), "Gelem_s": round(n / ms / 1e6, 2), "elements": n}
+    ones = torch.ones(per, device=dev)
+    for name, op, arity, extra, bytes_per in (("uniform", 0, 0, [0.0, 1.0], 4), ("gaussian", 6, 2, [0.0, 1.0], 4),
+                                              ("bernoulli", 7, 0, [0.3], 4), ("dropout_inverted", 2, 1, [0.5], 8)):
+        ex = torch.tensor(extra, device=dev)
+        xa = ones if arity == 1 else (z if arity == 2 else None)
+        ya = z if arity == 2 else None
+        ms = timed(lambda: calls.check(lib.nd4jb200_exec_random_range(st, 0, op, arity, sp, P(xa), P(ya), P(z), P(ex),
+                                                                      rank * per, per, n)), 3)
+        out["random_%s_sharded" % name] = {"ms": round(ms, 4), "Gelem_s": round(n / ms / 1e6, 2),
+                                           "GBps": round(bytes_per * n / ms / 1e6, 1), "elements": n}
+    del ones
+    # ---- C5b: whole-array Sum of 2^31 floats over a fixed grid of 8 shards ----
     n2 = 1 << (27 if quick else 31)
     per2 = n2 // world
     big = torch.empty(per2, device=dev)
@@ -789,21 +819,81 @@ def sharded_families(torch, dist, ops, calls, stream, world, rank, quick):
     for off in range(0, per2, chunk):
         calls.check(lib.nd4jb200_exec_random_range(st, 0, 0, 0, sp, None, None, P(big[off:off + chunk]), P(em1),
                                                    rank * per2 + off, chunk, n2))
-    bi2 = calls.longs(S.shape_info([1, per2]))
-    res = ctypes.c_double()
-    total = torch.zeros(1, device=dev, dtype=torch.float64)
-
-    def reduce_step():
-        calls.check(lib.nd4jb200_exec_reduce_scalar(st, 0, 1, P(big), bi2, None, ctypes.byref(res)))
-        total[0] = res.value
-        with torch.cuda.stream(stream):
-            dist.all_reduce(total)
-
-    ms = timed(reduce_step, 5)
-    out["reduce_scalar_sum_sharded_allreduce"] = {"ms": round(ms, 4), "Gelem_s": round(n2 / ms / 1e6, 2),
+    grid_shards = max(8, world)
+    zdev = torch.zeros(1, device=dev)
+    ms = timed(lambda: calls.check(lib.nd4jb200_exec_reduce_scalar_sharded(st, 0, 1, P(big), per2, None, grid_shards // world,
+                                                                           n2, P(zdev), None)), 10)
+    stream.synchronize()
+    out["reduce_scalar_sum_sharded_allgather"] = {"ms": round(ms, 4), "Gelem_s": round(n2 / ms / 1e6, 2),
                                                   "GBps": round(4 * n2 / ms / 1e6, 1), "elements": n2,
-                                                  "sum": float(total.item())}
+                                                  "shard_grid": grid_shards, "sum": float(zdev.item()),
+                                                  "note": "same shard grid at every N: the sum's bits must not change with N"}
     ops.destroyRandom(state)
+    del big
+    # ---- C1 / C3 / C4: the along-dimension reductions with their TADs split over the ranks ----
+    g = torch.Generator(device=dev)
+    g.manual_seed(100 + rank)
+    d1, d0 = calls.ints([1]), calls.ints([0])
+    k = [0]
+
+    def rotating(make, count):
+        return [make() for _ in range(count)]
+    r1 = 8192 // world
+    xs = rotating(lambda: torch.empty(r1, 4096, device=dev).uniform_(-1, 1, generator=g), 3)
+    zz = torch.zeros(r1, device=dev)
+    xi, zi = calls.longs(S.shape_info([r1, 4096])), calls.longs(S.shape_info([r1, 1]))
+
+    def f():
+        k[0] = (k[0] + 1) % 3
+        calls.check(lib.nd4jb200_exec_reduce(st, 0, 1, P(xs[k[0]]), xi, None, P(zz), zi, d1, 1))
+    ms = timed(f, 20, graph=True)
+    out["reduce_sum_dim1_8192x4096_row_sharded"] = {"ms": round(ms, 5), "Gelem_s": round(8192 * 4096 / ms / 1e6, 1),
+                                                    "GBps": round(134250496 / ms / 1e6, 1)}
+    del xs
+    r3 = 65536 // world
+    lv = rotating(lambda: torch.randint(0, 16, (r3, 1024), device=dev, generator=g).float() / 8 - 1, 2)
+    zr = torch.zeros(r3, device=dev)
+    xi3, zi3 = calls.longs(S.shape_info([r3, 1024])), calls.longs(S.shape_info([r3, 1]))
+
+    def f():
+        k[0] = (k[0] + 1) % 2
+        calls.check(lib.nd4jb200_exec_index_reduce(st, 0, 0, P(lv[k[0]]), xi3, None, P(zr), zi3, d1, 1))
+    ms = timed(f, 20, graph=True)
+    out["indexreduce_imax_dim1_65536x1024_row_sharded"] = {"ms": round(ms, 5), "Gelem_s": round(65536 * 1024 / ms / 1e6, 1),
+                                                           "GBps": round(268697600 / ms / 1e6, 1)}
+    del lv
+    # variance along dimension 0: every rank owns 1024 / G columns of all 65536 rows (a strided view of the array)
+    c3 = 1024 // world
+    full = rotating(lambda: torch.randint(0, 16, (65536, 1024), device=dev, generator=g).float() / 8 - 1, 2)
+    zc = torch.zeros(c3, device=dev)
+    vi3 = calls.longs(S.shape_info([65536, c3], "c", [1024, 1]))
+    zic = calls.longs(S.shape_info([1, c3]))
+
+    def f():
+        k[0] = (k[0] + 1) % 2
+        calls.check(lib.nd4jb200_exec_summary_stats(st, 0, 0, ctypes.c_void_p(full[k[0]].data_ptr() + 4 * rank * c3), vi3, None,
+                                                    P(zc), zic, d0, 1, 1))
+    ms = timed(f, 20, graph=True)
+    out["summarystats_variance_dim0_65536x1024_column_sharded"] = {"ms": round(ms, 5), "Gelem_s": round(65536 * 1024 / ms / 1e6, 1),
+                                                                   "GBps": round(268439552 / ms / 1e6, 1)}
+    del full
+    r4 = 32768 // world
+    for dt, code, name in ((torch.float32, 0, "f32"), (torch.float16, 2, "f16")):
+        es = 4 if code == 0 else 2
+        xa = rotating(lambda: torch.randn(r4, 512, device=dev, generator=g).to(dt), 4)
+        ya = rotating(lambda: torch.randn(r4, 512, device=dev, generator=g).to(dt), 4)
+        z4 = torch.zeros(r4, device=dev, dtype=dt)
+        ci, zi4 = calls.longs(S.shape_info([r4, 512])), calls.longs(S.shape_info([r4, 1]))
+        for op, opname in ((2, "cosine"), (1, "euclidean")):
+            def f(op=op):
+                k[0] = (k[0] + 1) % 4
+                calls.check(lib.nd4jb200_exec_reduce3(st, code, op, P(xa[k[0]]), ci, None, P(ya[k[0]]), ci, P(z4), zi4, d1, 1))
+            ms = timed(f, 20, graph=True)
+            out["reduce3_%s_%s_32768x512_row_sharded" % (opname, name)] = {
+                "ms": round(ms, 5), "Gelem_s": round(32768 * 512 / ms / 1e6, 1),
+                "GBps": round((2 * 32768 * 512 * es + 32768 * es) / ms / 1e6, 1)}
+        del xa, ya
+    ops.commDestroy()
     return out
 
 

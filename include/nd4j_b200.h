@@ -302,6 +302,37 @@ int nd4jb200_exec_meta_predicate_strided(void *stream, int dtype, int opTypeA, i
                                          void *z, Nd4jLong zStride, const void *extraA, const void *extraB,
                                          double scalarA, double scalarB);
 
+/* ---- several GPUs: one process per GPU, one communicator per process -------------------------------------------
+ * The exec* families shard without any exchange (TADs, elements and random indices are independent; see
+ * nd4jb200_exec_random_range). The one exchange step of this path is the combine of per-GPU partials of a
+ * whole-array reduction, and the across-GPU forms of average / accumulate; the reference does these by letting a
+ * kernel read its peers' memory (blas/cuda/NativeOps.cu:4884-4968, include/loops/special_kernels.h:711-821;
+ * peer access control blas/NativeOps.h:2047-2058). Here partial states travel through NCCL on the caller's stream
+ * and no kernel reads another GPU's memory.
+ *   comm_unique_id: rank 0 obtains 128 bytes and hands them to the other ranks by any means (it is ncclGetUniqueId);
+ *   comm_init:      every rank, with its device current; collective. world == 1 needs neither an id nor NCCL;
+ *   exec_reduce_scalar_sharded: the whole-array reduce (opNum of execReduceScalar*, blas/NativeOps.h:886-906) of
+ *       an array cut into world * shardsPerRank equal contiguous shards, of which this rank holds shardsPerRank
+ *       consecutive ones at x (localLength elements, dense). Every shard is reduced to an accumulator state, the
+ *       states are all-gathered and every rank folds them in global shard order, so the value depends on the
+ *       shard grid only: 8 shards give the same bits on 1, 2, 4 or 8 GPUs. totalLength is the n of Mean-like ops.
+ *       The value goes to z (device, one element; may be null) and, if `result` is not null, to the host after a
+ *       stream synchronisation; with result == null the call is asynchronous.
+ *   accumulate_across: z = sum over ranks of x (ncclAllReduce; NativeOps::accumulate* across devices).
+ *   average_across: z (or x when z is null) = sum over ranks of x / world, each term divided first as the
+ *       reference's loop does (include/ops/impl/specials.cpp:392-400); propagate != 0 also writes it back to x.
+ *       The order of the additions is NCCL's: results agree with the sequential loop to rounding, not bit for bit. */
+int nd4jb200_comm_unique_id(void *id128);
+int nd4jb200_comm_init(const void *id128, int rank, int world);
+int nd4jb200_comm_destroy(void);
+int nd4jb200_comm_rank(void);
+int nd4jb200_comm_world(void);
+int nd4jb200_exec_reduce_scalar_sharded(void *stream, int dtype, int opNum, const void *x, Nd4jLong localLength,
+                                        const void *extraParams, int shardsPerRank, Nd4jLong totalLength, void *z,
+                                        double *result);
+int nd4jb200_accumulate_across(void *stream, int dtype, const void *x, void *z, Nd4jLong length);
+int nd4jb200_average_across(void *stream, int dtype, void *x, void *z, Nd4jLong length, int propagate);
+
 /* ---- peer access and the constant-memory staging area (blas/NativeOps.h:1836-1846, 2047-2058;
  *      blas/cuda/NativeOps.cu:87, 3854-3938, 4793-4834) -------------------------------------------------------
  * check_p2p probes every ordered device pair and records whether all of them can reach each other (one device

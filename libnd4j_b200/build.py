@@ -36,6 +36,7 @@ def _sources():
     units.append(("utility_ops", "utility_ops.cu", []))
     units.append(("sort_ops", "sort_ops.cu", []))
     units.append(("device_env", "device_env.cu", []))
+    units.append(("comm", "comm.cu", []))
     units.append(("runtime", "runtime.cu", []))
     units.append(("shape_host", "shape_host.cpp", []))
     return [u for u in units if os.path.exists(os.path.join(CSRC, u[1]))]
@@ -76,7 +77,7 @@ def build(force=False, ptxas_verbose=False, jobs=None):
         for obj, log in ex.map(lambda u: _compile(u, extra), units):
             objs.append(obj)
             logs.append(log)
-    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs
+    cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + ["-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))

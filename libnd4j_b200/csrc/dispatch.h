@@ -19,6 +19,8 @@ namespace nd4jb200 {
     Status broadcast_##S(int opNum, const BcArgs &a, cudaStream_t st);                 \
     Status scalar_tad_##S(int opNum, const BcArgs &a, cudaStream_t st);                \
     Status reduce_##S(int opNum, const ReduceCall &c, cudaStream_t st);                \
+    Status reduce_merge_##S(int opNum, const MergeCall &m, cudaStream_t st);           \
+    int reduce_state_bytes_##S(int opNum);                                             \
     Status reduce3_##S(int opNum, const ReduceCall &c, cudaStream_t st);               \
     Status reduce3_all_##S(int opNum, const ReduceCall &c, cudaStream_t st);           \
     Status softmax_##S(int kind, const SoftmaxArgs &a, cudaStream_t st);               \

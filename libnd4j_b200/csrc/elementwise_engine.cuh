@@ -81,17 +81,43 @@ __global__ void __launch_bounds__(kEwBlock) k_elementwise(const EwArgs a) {
                     if (ARITY == 2) yv[u] = load_pack_rw(ay + i * V);
                 }
             }
+            if constexpr (POST) {
+                // both steps tile-wide, so that the second op is selected once per tile and not per element
+                C t[kEwIlp * V], sv[kEwIlp * V];
 #pragma unroll
-            for (int u = 0; u < kEwIlp; u++) {
-                LL i = base + u * nthreads;
-                if (i < npacks) {
-                    Pack<T> r;
+                for (int u = 0; u < kEwIlp; u++)
 #pragma unroll
                     for (int k = 0; k < V; k++) {
-                        C yc = ARITY == 2 ? Elem<T>::to_c(yv[u].v[k]) : C(0);
-                        r.v[k] = Elem<T>::from_c(ew_post<T, POST, C>(a, ew_apply<Op, ARITY, C>(Elem<T>::to_c(xv[u].v[k]), yc, sc, p)));
+                        const bool live = base + u * nthreads < npacks;
+                        C xc = live ? Elem<T>::to_c(xv[u].v[k]) : C(1);
+                        C yc = (ARITY == 2 && live) ? Elem<T>::to_c(yv[u].v[k]) : C(1);
+                        t[u * V + k] = through_memory<T>(ew_apply<Op, ARITY, C>(xc, yc, sc, p));
+                        sv[u * V + k] = C(a.postScalar);
                     }
-                    store_pack(az + i * V, r);
+                light_apply_tile<C, kEwIlp * V>(a.postCode, t, sv);
+#pragma unroll
+                for (int u = 0; u < kEwIlp; u++) {
+                    LL i = base + u * nthreads;
+                    if (i < npacks) {
+                        Pack<T> r;
+#pragma unroll
+                        for (int k = 0; k < V; k++) r.v[k] = Elem<T>::from_c(t[u * V + k]);
+                        store_pack(az + i * V, r);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < kEwIlp; u++) {
+                    LL i = base + u * nthreads;
+                    if (i < npacks) {
+                        Pack<T> r;
+#pragma unroll
+                        for (int k = 0; k < V; k++) {
+                            C yc = ARITY == 2 ? Elem<T>::to_c(yv[u].v[k]) : C(0);
+                            r.v[k] = Elem<T>::from_c(ew_apply<Op, ARITY, C>(Elem<T>::to_c(xv[u].v[k]), yc, sc, p));
+                        }
+                        store_pack(az + i * V, r);
+                    }
                 }
             }
         }

@@ -81,6 +81,24 @@ Status ND_S(reduce)(int opNum, const ReduceCall &c, cudaStream_t st) {
         default: return unknown_op("reduce", opNum);
     }
 }
+Status ND_S(reduce_merge)(int opNum, const MergeCall &m, cudaStream_t st) {
+    switch (opNum) {
+#define X(num, Name) case num: return run_merge_states<ND_T, pol::Reduce<fn::Name, CT> >(m, st);
+        ND_REDUCE_TABLE(X)
+#undef X
+        case 19: return run_merge_states<ND_T, pol::LogSumExp<CT> >(m, st);
+        default: return unknown_op("reduce", opNum);
+    }
+}
+int ND_S(reduce_state_bytes)(int opNum) {
+    switch (opNum) {
+#define X(num, Name) case num: return (int) sizeof(pol::Reduce<fn::Name, CT>::State);
+        ND_REDUCE_TABLE(X)
+#undef X
+        case 19: return (int) sizeof(pol::LogSumExp<CT>::State);
+        default: return 0;
+    }
+}
 #elif ND_FAMILY == 3
 Status ND_S(reduce3)(int opNum, const ReduceCall &c, cudaStream_t st) {
     switch (opNum) {

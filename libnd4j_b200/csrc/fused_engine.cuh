@@ -59,18 +59,31 @@ __global__ void __launch_bounds__(kEwBlock) k_chain(const ChainArgs a) {
                 if (r + u < rEnd) {
                     xv[u] = load_pack_rw(ax + (r + u) * xs + col);
                     yv[u] = load_pack_rw(ay + (r + u) * ys + col);
+                } else {
+                    xv[u] = Pack<T>(); yv[u] = Pack<T>();
                 }
+            // the three steps run tile-wide (rows past the end compute on zeros and are not stored), each
+            // intermediate going through the element type as a store and a load between launches would make it
+            C t[kEwIlp * V], o[kEwIlp * V];
+#pragma unroll
+            for (int u = 0; u < kEwIlp; u++)
+#pragma unroll
+                for (int k = 0; k < V; k++) { t[u * V + k] = Elem<T>::to_c(xv[u].v[k]); o[u * V + k] = Elem<T>::to_c(bv.v[k]); }
+            light_apply_tile<C, kEwIlp * V>(bc, t, o);
+#pragma unroll
+            for (int i = 0; i < kEwIlp * V; i++) t[i] = through_memory<T>(Tr::template f<C>(through_memory<T>(t[i]), p));
+#pragma unroll
+            for (int u = 0; u < kEwIlp; u++)
+#pragma unroll
+                for (int k = 0; k < V; k++) o[u * V + k] = Elem<T>::to_c(yv[u].v[k]);
+            light_apply_tile<C, kEwIlp * V>(pw, t, o);
 #pragma unroll
             for (int u = 0; u < kEwIlp; u++) {
                 if (r + u < rEnd) {
-                    Pack<T> o;
+                    Pack<T> w;
 #pragma unroll
-                    for (int k = 0; k < V; k++) {
-                        C t = through_memory<T>(light_apply<C>(bc, Elem<T>::to_c(xv[u].v[k]), Elem<T>::to_c(bv.v[k])));
-                        t = through_memory<T>(Tr::template f<C>(t, p));
-                        o.v[k] = Elem<T>::from_c(light_apply<C>(pw, t, Elem<T>::to_c(yv[u].v[k])));
-                    }
-                    store_pack(az + (r + u) * zs + col, o);
+                    for (int k = 0; k < V; k++) w.v[k] = Elem<T>::from_c(t[u * V + k]);
+                    store_pack(az + (r + u) * zs + col, w);
                 }
             }
         }

@@ -35,6 +35,39 @@ template <class C> ND_D C light_apply(int code, C x, C y) {
     }
 }
 
+// t[i] = op(t[i], y[i]) for a register tile: the op is selected once per tile, outside the element loop, so the
+// selection costs a few instructions per N elements instead of per element.
+template <class C, int N> ND_D void light_apply_tile(int code, C (&t)[N], const C (&y)[N]) {
+#define ND_LIGHT_CASE(CODE, EXPR)                                         \
+    case CODE: {                                                          \
+        _Pragma("unroll") for (int i = 0; i < N; i++) {                   \
+            const C a = t[i], b = y[i];                                   \
+            t[i] = (EXPR);                                                \
+        }                                                                 \
+    } break;
+    switch (code) {
+        ND_LIGHT_CASE(kLightAdd, a + b)
+        ND_LIGHT_CASE(kLightSubtract, a - b)
+        ND_LIGHT_CASE(kLightMultiply, a * b)
+        ND_LIGHT_CASE(kLightDivide, a / b)
+        ND_LIGHT_CASE(kLightReverseDivide, b / a)
+        ND_LIGHT_CASE(kLightReverseSubtract, b - a)
+        ND_LIGHT_CASE(kLightCopy, b)
+        ND_LIGHT_CASE(kLightMax, a > b ? a : b)
+        ND_LIGHT_CASE(kLightMin, a < b ? a : b)
+        ND_LIGHT_CASE(kLightSquaredSubtract, (a - b) * (a - b))
+        ND_LIGHT_CASE(kLightEqualTo, C(a == b))
+        ND_LIGHT_CASE(kLightNotEqualTo, C(a != b))
+        ND_LIGHT_CASE(kLightGreaterThan, C(a > b))
+        ND_LIGHT_CASE(kLightGreaterThanOrEqual, C(a >= b))
+        ND_LIGHT_CASE(kLightLessThan, C(a < b))
+        default: {
+            _Pragma("unroll") for (int i = 0; i < N; i++) t[i] = C(t[i] <= y[i]);
+        } break;
+    }
+#undef ND_LIGHT_CASE
+}
+
 // BROADCAST_OPS / PAIRWISE_TRANSFORM_OPS / SCALAR_OPS number -> light code, or kLightNone.
 inline int light_of_broadcast(int opNum) {
     static const int map[] = {kLightAdd, kLightSubtract, kLightMultiply, kLightDivide, kLightReverseDivide,

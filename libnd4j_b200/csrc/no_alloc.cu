@@ -124,6 +124,7 @@ extern "C" int nd4jb200_exec_reduce_scalar_noalloc(void *stream, int dtype, int 
     a.xOuterHi = plan.outer; a.yOuterHi = plan.outer;
     a.finishLen = xd.length;
     a.zIndex = nullptr;
+    a.zState = nullptr;
     const size_t es = dtype == kF64 ? 8 : (dtype == kF16 ? 2 : 4);
     const LL V = 16 / (LL) es;
     const bool unit = plan.inner.rank == 0 || (plan.inner.rank == 1 && plan.inner.stride[0] == 1);

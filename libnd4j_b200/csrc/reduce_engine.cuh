@@ -61,6 +61,9 @@ struct ReduceArgs {
     LL *zIndex;          // index reductions only: when set, the winning position of TAD r is written here as an
                          // exact 64-bit integer instead of into z in the element type (half cannot hold
                          // positions above 2048 exactly, float none above 2^24)
+    void *zState;        // when set, the raw accumulator state of TAD r is stored at zState[r] (sizeof(State) bytes
+                         // each) instead of a finished result: partial results that a later step merges with the
+                         // states of other shards (k_merge_states)
 };
 
 constexpr int kBlock = 256;
@@ -94,6 +97,7 @@ template <class P, class = void> struct HasIndexResult { static constexpr bool v
 template <class P> struct HasIndexResult<P, decltype((void) P::kIndexResult)> { static constexpr bool value = true; };
 template <class T, class P>
 ND_D void write_result(const ReduceArgs &a, LL r, const typename P::State &s, const typename Elem<T>::C *p) {
+    if (a.zState) { static_cast<typename P::State *>(a.zState)[r] = s; return; }
     if constexpr (HasIndexResult<P>::value) {
         if (a.zIndex) { a.zIndex[r] = s.i; return; }
     }
@@ -498,6 +502,24 @@ __global__ void __launch_bounds__(kBlock) k_reduce_finalize(const ReduceArgs a) 
         group_merge<P>(s, 32);
         if (lane == 0) write_result<T, P>(a, r, s, p);
     }
+}
+
+// Folds `count` accumulator states in index order and writes the finished result: the combine step of a
+// reduction whose shards were reduced separately (by other launches, or on other GPUs and gathered here).
+// The order is fixed by position in `states`, so the result depends on how the array was cut into shards
+// but not on which process reduced which shard.
+template <class T, class P>
+__global__ void k_merge_states(const void *states, int count, LL finishLen, const void *extra, void *z) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    typedef typename P::State State;
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    C p[P::kParams ? P::kParams : 1];
+    load_params<T, P::kParams>(static_cast<const T *>(extra), p);
+    const State *st = static_cast<const State *>(states);
+    State m = st[0];
+    for (int i = 1; i < count; i++) { State o = st[i]; P::merge(m, o); }
+    static_cast<T *>(z)[0] = Elem<T>::from_c(P::finish(m, finishLen, p));
 }
 
 }  // namespace nd4jb200

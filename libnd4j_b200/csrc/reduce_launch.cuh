@@ -16,6 +16,18 @@ struct ReduceCall {
     bool yBroadcast = false;     // y (or x) is a single TAD reused for every TAD of the other operand
     LL finishLen = 0;            // n handed to the policy's finish()
     LL *zIndex = nullptr;        // index reductions: exact 64-bit positions go here instead of into z
+    void *zState = nullptr;      // raw accumulator states (one per TAD) go here instead of finished results into z
+    LL fixedSegment = 0;         // > 0: dense TADs are cut into segments of this many elements, each reduced by one
+                                 // CTA, and merged by the finalize launch, whatever the number of TADs in the call,
+                                 // so that the bits of a TAD's result depend on that TAD alone
+};
+
+struct MergeCall {
+    const void *states;          // device: `count` accumulator states of the op's policy, in combine order
+    int count;
+    LL finishLen;
+    const void *extra;
+    void *z;                     // device: one element of the call's type
 };
 
 // Workspace layout: [256-byte result slot][kCounterSlots arrival counters][partial states]. The
@@ -60,6 +72,7 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
     a.yInner = two ? c.yPlan.inner : c.xPlan.inner;
     a.finishLen = c.finishLen;
     a.zIndex = c.zIndex;
+    a.zState = c.zState;
     a.splits = 1; a.cluster = 1; a.group = 32; a.mode = 2;
     a.partTadStride = 1; a.partSplitStride = 1;
     a.colLo = 0; a.colStrideX = 0; a.colStrideY = 0;
@@ -144,9 +157,15 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
             if (splits > maxSplits) splits = maxSplits;
             if (splits < 1) splits = 1;
         }
+        if (c.fixedSegment > 0) {
+            a.group = kBlock;
+            splits = ceil_div(a.tadLen, c.fixedSegment);
+            if (splits < 1) splits = 1;
+        }
         a.splits = (int) splits;
         a.partTadStride = a.splits; a.partSplitStride = 1;
         if (a.splits > 1) ND_TRY(split_scratch<State>(stream, a, (size_t) a.numTads));
+        if (c.fixedSegment > 0) a.counters = nullptr;
         const LL totalSegs = a.numTads * a.splits;
         LL blocks = ceil_div(totalSegs, kBlock / a.group);
         // the grid is capped so that CTAs loop over several TADs instead of being launched once per handful of
@@ -161,6 +180,14 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
         launch_kernel(k_reduce_finalize<T, P>, dim3((unsigned) blocks), dim3(kBlock), stream, a);
     }
+    ND_CUDA(cudaGetLastError());
+    return kOk;
+}
+
+template <class T, class P>
+Status run_merge_states(const MergeCall &m, cudaStream_t stream) {
+    if (m.count <= 0) return bad_arg("no states to merge");
+    launch_kernel(k_merge_states<T, P>, dim3(1), dim3(32), stream, m.states, m.count, m.finishLen, m.extra, m.z);
     ND_CUDA(cudaGetLastError());
     return kOk;
 }

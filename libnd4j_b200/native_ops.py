@@ -102,6 +102,14 @@ def load_library(path=None):
         "nd4jb200_exec_chain": (i, [vp, i, i, vp, llp, vp, llp, ip, i, i, vp, i, vp, llp, vp, vp, llp]),
         "nd4jb200_exec_meta_predicate_shape": (i, [vp, i, i, i, i, i, vp, llp, vp, llp, vp, llp, vp, vp, d, d]),
         "nd4jb200_exec_meta_predicate_strided": (i, [vp, i, i, i, i, i, ll, vp, ll, vp, ll, vp, ll, vp, vp, d, d]),
+        "nd4jb200_comm_unique_id": (i, [vp]),
+        "nd4jb200_comm_init": (i, [vp, i, i]),
+        "nd4jb200_comm_destroy": (i, []),
+        "nd4jb200_comm_rank": (i, []),
+        "nd4jb200_comm_world": (i, []),
+        "nd4jb200_exec_reduce_scalar_sharded": (i, [vp, i, i, vp, ll, vp, i, ll, vp, dp]),
+        "nd4jb200_accumulate_across": (i, [vp, i, vp, vp, ll]),
+        "nd4jb200_average_across": (i, [vp, i, vp, vp, ll, i]),
         "nd4jb200_exec_broadcast": (i, [vp, i, i, vp, llp, vp, llp, vp, llp, ip, i]),
         "nd4jb200_exec_scalar": (i, [vp, i, i, vp, llp, vp, llp, d, vp]),
         "nd4jb200_exec_scalar_strided": (i, [vp, i, i, vp, ll, vp, ll, d, vp, ll]),
@@ -308,6 +316,34 @@ class NativeOps:
         dm, dmp = _ints(dimension)
         self._check(self.lib.nd4jb200_exec_broadcast(self._stream(extraPointers), dt, opNum, _ptr(x), xsp, _ptr(y), ysp,
                                                      _ptr(result), zsp, dmp, dimensionLength))
+
+    # ---- several GPUs (nd4jb200_comm_*) ---------------------------------------------------------
+    def commUniqueId(self):
+        buf = ctypes.create_string_buffer(128)
+        self._check(self.lib.nd4jb200_comm_unique_id(buf))
+        return buf.raw
+
+    def commInit(self, unique_id, rank, world):
+        self._check(self.lib.nd4jb200_comm_init(unique_id, rank, world))
+
+    def commDestroy(self):
+        self._check(self.lib.nd4jb200_comm_destroy())
+
+    def execReduceScalarSharded(self, dt, extraPointers, opNum, x, localLength, extraParams, shardsPerRank, totalLength,
+                                z=None, fetch=True):
+        """Whole-array reduce over world * shardsPerRank shards (nd4jb200_exec_reduce_scalar_sharded); returns the
+        value when `fetch`, else None (asynchronous, value in z)."""
+        out = ctypes.c_double()
+        self._check(self.lib.nd4jb200_exec_reduce_scalar_sharded(self._stream(extraPointers), dt, opNum, _ptr(x), localLength,
+                                                                 _ptr(extraParams), shardsPerRank, totalLength, _ptr(z),
+                                                                 ctypes.byref(out) if fetch else None))
+        return out.value if fetch else None
+
+    def accumulateAcross(self, dt, extraPointers, x, z, length):
+        self._check(self.lib.nd4jb200_accumulate_across(self._stream(extraPointers), dt, _ptr(x), _ptr(z), length))
+
+    def averageAcross(self, dt, extraPointers, x, z, length, propagate):
+        self._check(self.lib.nd4jb200_average_across(self._stream(extraPointers), dt, _ptr(x), _ptr(z), length, 1 if propagate else 0))
 
     def execChain(self, dt, extraPointers, broadcastOp, x, xShapeInfo, b, bShapeInfo, dimension, dimensionLength,
                   transformOp, transformExtra, pairwiseOp, y, yShapeInfo, pairwiseExtra, z, zShapeInfo):
