@@ -542,19 +542,34 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
     record("random_dropout_inverted_2p%d" % (26 if quick else 30), 8 * n, n,
            lambda: calls.check(lib.nd4jb200_exec_random_x(st, 0, 2, sp, P(xr), zin, P(zbuf), zin, P(e05))), iters=3)
     del xr
-    # whole-array Sum of 2^31 (2^27 when quick) floats drawn U(-1,1) on the device
+    # whole-array Sum of 2^31 (2^27 when quick) floats drawn U(-1,1) on the device: element e is draw e of a fresh
+    # seed-119 state, which is also what the ranks of a multi-GPU run generate for their shards
     n2 = 1 << (27 if quick else 31)
     big = torch.empty(n2, device=dev)
     chunk = 1 << 26
-    ci2 = calls.longs(S.shape_info([1, chunk]))
     em1 = torch.tensor([-1.0, 1.0], device=dev)
+    fresh = ops.initRandom([None, stream.cuda_stream], 119, 100000, None)
     for off in range(0, n2, chunk):
-        calls.check(lib.nd4jb200_exec_random(st, 0, 0, sp, P(big[off:off + chunk]), ci2, P(em1)))
+        calls.check(lib.nd4jb200_exec_random_range(st, 0, 0, 0, ctypes.c_void_p(fresh), None, None, P(big[off:off + chunk]),
+                                                   P(em1), off, chunk, n2))
+    ops.destroyRandom(fresh)
     bi2 = calls.longs(S.shape_info([1, n2]))
     res = ctypes.c_double()
     record("reduce_scalar_sum_2p%d" % (27 if quick else 31), 4 * n2, n2,
            lambda: calls.check(lib.nd4jb200_exec_reduce_scalar(st, 0, 1, P(big), bi2, None, ctypes.byref(res))), iters=5,
            graph=False)   # the scalar form synchronises the stream: timed as a plain loop
+    # the same sum through the sharded entry point (a communicator of one rank, grid of 8 shards, result left on
+    # the device): the value a 2-, 4- or 8-GPU run of this benchmark must reproduce bit for bit
+    if not only or "sharded" in only:
+        ops.commInit(None, 0, 1)
+        zdev = torch.zeros(1, device=dev)
+        record("reduce_scalar_sum_sharded_allgather", 4 * n2, n2,
+               lambda: calls.check(lib.nd4jb200_exec_reduce_scalar_sharded(st, 0, 1, P(big), n2, None, 8, n2, P(zdev), None)),
+               iters=10, graph=False)
+        stream.synchronize()
+        if "reduce_scalar_sum_sharded_allgather" in out:
+            out["reduce_scalar_sum_sharded_allgather"].update({"shard_grid": 8, "sum": float(zdev.item())})
+        ops.commDestroy()
     ops.destroyRandom(state)
     return out
 
@@ -778,7 +793,16 @@ def sharded_families(torch, dist, ops, calls, stream, world, rank, quick):
     out = {}
     uid = [ops.commUniqueId() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
-    ops.commInit(uid[0], rank, world)
+    # NCCL announces its version on stdout when a process creates its first communicator of its own; stdout
+    # carries the one JSON line, so the announcement is sent to stderr
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        ops.commInit(uid[0], rank, world)
+    finally:
+        os.dup2(saved, 1)
+        os.close(saved)
 
     def over_ranks(ms):
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)

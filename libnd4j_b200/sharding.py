@@ -89,6 +89,25 @@ def gather_partials(dist, value, device=None):
     return [float(t.item()) for t in out]
 
 
+def fold_states_in_shard_order(dist, local_states, merge, device=None):
+    """The combine step of nd4jb200_exec_reduce_scalar_sharded, stated on the host: every rank holds the
+    accumulator states of its consecutive shards (a float32 vector, one entry per shard); the states of all ranks
+    are gathered rank-major, which is global shard order, and folded from the left with `merge`. The value then
+    depends on the shard grid only: 8 shards give the same bits in a world of 1, 2, 4 or 8."""
+    import torch
+    mine = torch.tensor(np.asarray(local_states, dtype=np.float32), device=device)
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        states = [mine]
+    else:
+        states = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(states, mine)
+    flat = np.concatenate([t.cpu().numpy() for t in states]).astype(np.float32)
+    acc = flat[0]
+    for v in flat[1:]:
+        acc = merge(acc, v)
+    return acc
+
+
 def sharded_reduce_scalar(dist, op_num, local_reduce, total_length, device=None):
     """Whole-array reduction over shards. `local_reduce(local_op_num)` returns this rank's partial
     (on a GPU rank it calls execReduceScalar on the shard). Every rank returns the same value."""

@@ -49,7 +49,7 @@ def test_sum_depends_on_the_shard_grid_only(comm, real_ref, n):
 @pytest.mark.parametrize("op", [0, 1, 3, 4, 6, 19, 25])
 def test_other_ops_and_types_against_the_unsharded_call(comm, dt, code, op):
     ops = comm
-    n = 1 << 18
+    n = 1 << (14 if dt == np.float16 else 18)          # half: sums of squares must stay below 65504
     x = np.random.default_rng(op).uniform(-1, 1, n).astype(dt)
     dx = dev(x)
     name = {0: "Float", 1: "Double", 2: "Half"}[code]

@@ -51,6 +51,38 @@ def _worker(rank, world, port, n, results):
     dist.destroy_process_group()
 
 
+def _grid_worker(rank, world, port, n, grid, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x = np.random.default_rng(8).uniform(-1, 1, n).astype(np.float32)
+    per_shard = n // grid
+    k = grid // world
+    # what a rank's local kernels deliver: one float32 state per shard it holds, each a function of that shard alone
+    mine = [np.float32(x[(rank * k + j) * per_shard:(rank * k + j + 1) * per_shard].sum(dtype=np.float32)) for j in range(k)]
+    got = sharding.fold_states_in_shard_order(dist, mine, lambda a, b: np.float32(a + b))
+    results[rank] = float(got)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fixed_shard_grid_gives_the_same_bits_in_every_world(world):
+    """The combine order of the sharded whole-array reduction: states meet in global shard order whatever the
+    number of ranks, so a grid of 8 shards sums to the same float32 bits on 1, 2 or 4 ranks."""
+    n, grid = 8 * 12500, 8
+    x = np.random.default_rng(8).uniform(-1, 1, n).astype(np.float32)
+    shards = [np.float32(x[j * (n // grid):(j + 1) * (n // grid)].sum(dtype=np.float32)) for j in range(grid)]
+    want = sharding.fold_states_in_shard_order(None, shards, lambda a, b: np.float32(a + b))
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_grid_worker, args=(world, _free_port(), n, grid, results), nprocs=world, join=True)
+        results = dict(results)
+    assert len(results) == world
+    for rank, got in results.items():
+        assert np.float32(got) == np.float32(want), (rank, got, want)
+
+
 def _lonely(rank, port, flag):
     import datetime
     os.environ["MASTER_ADDR"] = "127.0.0.1"

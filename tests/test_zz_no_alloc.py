@@ -69,6 +69,42 @@ def test_other_types_and_strided_input(ops):
     assert float(z.item()) == 100000 ** 2
 
 
+@pytest.mark.parametrize("n", [65537, (1 << 22) + 3])
+def test_float_sum_against_the_reference_and_an_fp64_truth(ops, real_ref, n):
+    """Independent of the entry point it shares kernels with: the value is held against a float64 sum of the
+    same data and against the reference's own whole-array loop, with the bound the reduction tests use."""
+    fn = _bind(ops)
+    x = np.random.default_rng(n).uniform(-1, 1, n).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    keep, info = _info(S.shape_info([1, n]))
+    z = torch.zeros(1, device="cuda")
+    truth, mag = float(x.astype(np.float64).sum()), float(np.abs(x).astype(np.float64).sum())
+    want = float(real_ref.reduce_scalar(1, x, keep))
+    for _ in range(2):
+        assert fn(None, 0, 1, ctypes.c_void_p(dx.data_ptr()), info, None, ctypes.c_void_p(z.data_ptr())) == 0
+        torch.cuda.synchronize()
+        assert abs(float(z.item()) - truth) <= max(1e-5 * mag, abs(want - truth) * 1.0000001)
+
+
+def test_half_precision_sum_and_max(ops):
+    fn = _bind(ops)
+    n = 300001
+    x = (np.random.default_rng(3).uniform(-1, 1, n) / 64).astype(np.float16)     # the sum stays far below 65504
+    dx = torch.from_numpy(x).cuda()
+    keep, info = _info(S.shape_info([1, n]))
+    z = torch.zeros(1, device="cuda", dtype=torch.float16)
+    truth, mag = float(x.astype(np.float64).sum()), float(np.abs(x).astype(np.float64).sum())
+    for _ in range(2):
+        assert fn(None, 2, 1, ctypes.c_void_p(dx.data_ptr()), info, None, ctypes.c_void_p(z.data_ptr())) == 0
+        torch.cuda.synchronize()
+        got = float(z.item())
+        # accumulated in float, rounded to half once: half an ulp of the result plus the float sum's own error
+        assert abs(got - truth) <= 1e-2 * mag and abs(got - truth) <= 2 ** -10 * abs(truth) + 1e-5 * mag
+    assert fn(None, 2, 3, ctypes.c_void_p(dx.data_ptr()), info, None, ctypes.c_void_p(z.data_ptr())) == 0
+    torch.cuda.synchronize()
+    assert float(z.item()) == float(x.max())
+
+
 def test_inputs_beyond_the_built_in_scratch_are_refused(ops):
     fn = _bind(ops)
     x = torch.zeros(16, device="cuda")
