@@ -456,8 +456,25 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
         with torch.cuda.stream(stream):
             work_[:16384].copy_(unsorted_[:16384])
         calls.check(lib.nd4jb200_sort(st, 0, P(work_), flat_, 0))
+    def refill_rows():
+        with torch.cuda.stream(stream):
+            work_.copy_(unsorted_)
+
+    def refill_all():
+        with torch.cuda.stream(stream):
+            work_[:16384].copy_(unsorted_[:16384])
     record("sort_rows_f32_65536x1024_incl_refill", 4 * 65536 * 1024 * 4, 65536 * 1024, f_rows, iters=10, graph=False)
     record("sort_f32_2p24_incl_refill", 4 * (1 << 24) * 4, 1 << 24, f_all, iters=5, graph=False)
+    # the refill alone, so that the sort's own time can be read off: sort = incl_refill - refill
+    record("sort_refill_only_65536x1024", 2 * 65536 * 1024 * 4, 65536 * 1024, refill_rows, iters=10, graph=False)
+    record("sort_refill_only_2p24", 2 * (1 << 24) * 4, 1 << 24, refill_all, iters=5, graph=False)
+    for incl, refill, elems in (("sort_rows_f32_65536x1024_incl_refill", "sort_refill_only_65536x1024", 65536 * 1024),
+                                ("sort_f32_2p24_incl_refill", "sort_refill_only_2p24", 1 << 24)):
+        if incl in out and refill in out:
+            ms_ = out[incl]["ms"] - out[refill]["ms"]
+            out[incl]["sort_only_ms"] = round(ms_, 5)
+            out[incl]["sort_only_Gelem_s"] = round(elems / ms_ / 1e6, 2)
+            out[incl]["sort_only_frac_of_measured_peak"] = round(2 * elems * 4 / ms_ / 1e6 / peak, 3)
     del unsorted_, work_
     blocks_ = [torch.randn(4096, 4096, device=dev, generator=g) for _ in range(4)]
     cat_ = torch.empty(16384, 4096, device=dev)

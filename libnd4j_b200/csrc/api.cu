@@ -2,6 +2,7 @@
 // shape/TAD decoding and hand-off to the per-type dispatchers. No compute happens on the host.
 #include "../../include/nd4j_b200.h"
 #include "dispatch.h"
+#include <cmath>
 #include <cstring>
 #include <sstream>
 #include <vector>
@@ -219,12 +220,28 @@ Status random_common(void *stream, int dtype, int opNum, int arity, RandomState 
     }
     if (gaussian && (first & 1)) return bad_arg("the Gaussian family pairs elements (2k, 2k+1): `first` must be even");
     a.aux = nullptr; a.auxLen = 0;
-    if ((opNum == 5 || opNum == 8 || opNum == 9) && arity == 2) {
-        // Choice / Binomial / BinomialEx: whole calls on operands addressed by elementWiseStride
-        if (!zd || first != 0 || count != length) return unsupported("Choice and the binomial ops are served for whole calls only");
+    if ((opNum == 5 || opNum == 8 || opNum == 9 || opNum == 11) && arity == 2) {
+        // Choice / Binomial / BinomialEx / TruncatedNormal: whole calls on operands addressed by elementWiseStride
+        if (!zd || first != 0 || count != length)
+            return unsupported("Choice, the binomial ops and TruncatedNormal are served for whole calls only");
         if (zd->ews < 1 || xd->ews < 1 || yd->ews < 1)
-            return unsupported("Choice and the binomial ops address their operands by elementWiseStride (>= 1)");
+            return unsupported("Choice, the binomial ops and TruncatedNormal address their operands by elementWiseStride (>= 1)");
         a.mode = 1;
+        if (opNum == 11 && a.yIsZ) {
+            // with one mean for all elements the acceptance test |mean| + |result| <= 2 |stddev| can never hold once
+            // |mean| >= 2 |stddev|: the reference would not return (special_random_ops.h:779-798)
+            ND_TRY(need(extra, "extraArguments"));
+            unsigned char raw[16] = {0};
+            const size_t es = dtype == kF64 ? 8 : (dtype == kF32 ? 4 : 2);
+            ND_CUDA(cudaMemcpyAsync(raw, extra, 2 * es, cudaMemcpyDeviceToHost, as_stream(stream)));
+            ND_CUDA(cudaStreamSynchronize(as_stream(stream)));
+            double mean, sd;
+            if (dtype == kF64) { mean = reinterpret_cast<double *>(raw)[0]; sd = reinterpret_cast<double *>(raw)[1]; }
+            else if (dtype == kF32) { mean = reinterpret_cast<float *>(raw)[0]; sd = reinterpret_cast<float *>(raw)[1]; }
+            else { mean = __half2float(reinterpret_cast<__half *>(raw)[0]); sd = __half2float(reinterpret_cast<__half *>(raw)[1]); }
+            if (!(std::fabs(mean) < 2 * std::fabs(sd)))
+                return bad_arg("TruncatedNormal: |mean| must be below 2 |stddev|, otherwise no sample is ever accepted");
+        }
         if (opNum == 5) {
             const size_t es = dtype == kF64 ? 8 : (dtype == kF32 ? 4 : 2);
             void *ws = nullptr;

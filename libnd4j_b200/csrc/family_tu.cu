@@ -244,9 +244,12 @@ Status ND_S(random)(int opNum, int arity, const RngArgs &a, cudaStream_t st) {
             ND_CUDA(cudaGetLastError());
             return kOk;
         }
-        case 11:
-            return unsupported("random opNum 11 (TruncatedNormalDistribution) is not served: its rejection loop "
-                               "compares rounded transcendental results, which cannot be reproduced bit for bit");
+        case 11: {
+            if (a.count <= 0) return kOk;
+            launch_kernel(k_random_truncated_normal<ND_T>, dim3((unsigned) special_blocks(a.count - a.count / 2)), dim3(kRngBlock), st, a);
+            ND_CUDA(cudaGetLastError());
+            return kOk;
+        }
         default: return unknown_op("random", opNum);
     }
 }

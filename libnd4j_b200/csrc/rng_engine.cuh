@@ -347,6 +347,53 @@ __global__ void __launch_bounds__(kRngBlock) k_random_gaussian(const RngArgs a) 
     }
 }
 
+// TruncatedNormalDistribution (11): element e < middle = ceil(n / 2) and element e + middle share Box-Muller pairs
+// drawn at global indices (e + t * n, e + middle + t * n) for t = 0, 1, ... until both results satisfy
+// |mean| + |result| <= 2 |stddev| (special_random_ops.h:779-798). The uniforms are bit-exact; the normals go
+// through the device log / cos / sin, so a pair within rounding of the acceptance boundary can be accepted one
+// try earlier or later than on the host (counted in the tests: a few per million). The reference's loop has no
+// exit when |mean| >= 2 |stddev|; here it ends after kTruncatedMaxTries tries and keeps the last pair.
+constexpr int kTruncatedMaxTries = 4096;
+template <class T>
+__global__ void __launch_bounds__(kRngBlock) k_random_truncated_normal(const RngArgs a) {
+    grid_dependency_sync();
+    typedef typename Elem<T>::C C;
+    const T *ay = static_cast<const T *>(a.y);
+    T *az = static_cast<T *>(a.z);
+    C p[2];
+    load_params<T, 2>(static_cast<const T *>(a.extra), p);
+    const C mean = p[0], stddev = p[1];
+    const C twoPi = C(2.0 * 3.14159265358979323846);
+    const C eps = C(1e-6f);
+    const C ds = rn_mul(stddev < C(0) ? -stddev : stddev, C(2));
+    const LL n = a.length;
+    const LL middle = n - n / 2;
+    const LL nthreads = (LL) gridDim.x * kRngBlock;
+    for (LL e = (LL) blockIdx.x * kRngBlock + threadIdx.x; e < middle; e += nthreads) {
+        const bool second = e + middle < n;
+        const C m0 = a.yIsZ ? mean : Elem<T>::load(ay + e * a.sy);
+        // the reference reads y[(e + middle) * yEWS] even for the unpaired last element of an odd length; the
+        // value only enters the acceptance test there, and the mean stands in for it
+        const C m1 = (a.yIsZ || !second) ? (a.yIsZ ? mean : m0) : Elem<T>::load(ay + (e + middle) * a.sy);
+        const C am0 = m0 < C(0) ? -m0 : m0, am1 = m1 < C(0) ? -m1 : m1;
+        C r0 = C(0), r1 = C(0);
+        LL generation = 0;
+        for (int t = 0; t < kTruncatedMaxTries; t++) {
+            const C u0 = rng_uniform<T>(rng_element(a.g, e + generation), eps, C(1));
+            const C u1 = rng_uniform<T>(rng_element(a.g, e + middle + generation), eps, C(1));
+            const C radius = sqrt(rn_mul(C(-2), log(u0)));
+            const C angle = rn_mul(twoPi, u1);
+            r0 = rn_add(rn_mul(rn_mul(radius, cos(angle)), stddev), m0);
+            r1 = rn_add(rn_mul(rn_mul(radius, sin(angle)), stddev), m1);
+            generation += n;
+            const C a0 = r0 < C(0) ? -r0 : r0, a1 = r1 < C(0) ? -r1 : r1;
+            if (!(rn_add(am0, a0) > ds || rn_add(am1, a1) > ds)) break;
+        }
+        Elem<T>::store(az + e * a.sz, r0);
+        if (second) Elem<T>::store(az + (e + middle) * a.sz, r1);
+    }
+}
+
 // BinomialDistribution (8) and BinomialDistributionEx (9): z[e] = number of t in 1..trials whose
 // uniform draw at global index (e + 1) * t is below the success probability. extra = {trials,
 // probability}; when y does not alias z the probability is y[t - 1] (8: one per trial) or y[e]

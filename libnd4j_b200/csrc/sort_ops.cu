@@ -18,6 +18,7 @@
 #include "../../include/nd4j_b200.h"
 #include "device_utils.cuh"
 #include "runtime.h"
+#include "radix_sort.cuh"
 #include <math_constants.h>
 #include <vector>
 
@@ -378,9 +379,17 @@ void launch_chunks(const SortArgs &a, int fullSort, cudaStream_t st) {
     launch_kernel(k_sort_chunks<T, G, THREADS>, dim3((unsigned) blocks), dim3(THREADS), st, a, fullSort, dense);
 }
 
+// From this length on a single dense array goes to the radix sort: below it the network's few stages beyond a
+// chunk cost less than the radix sort's fixed dozen launches.
+constexpr LL kRadixMin = 1 << 16;
+
 template <class T>
 Status run_sort(SortArgs a, cudaStream_t st) {
     if (a.numTads <= 0 || a.n <= 1) return kOk;
+    // one long dense array: radix sort (3 sweeps per 8-bit digit instead of a sweep per network step)
+    static_assert(kRadixThreads == kRadixBins, "one thread per digit in the scans");
+    if (a.numTads == 1 && a.n >= kRadixMin && a.inner.rank == 1 && a.inner.stride[0] == 1)
+        return run_radix_sort<T>(static_cast<T *>(a.x), a.n, a.descending, st);
     // threads per full-size chunk: 8192 four-byte or 4096 eight-byte keys
     constexpr int kBig = sizeof(typename Elem<T>::C) == 8 ? 512 : 1024;
     constexpr int kChunk = kBig * kKeys;

@@ -257,9 +257,40 @@ def test_choice_bit_exact(ops, real_ref, pair, dt, name):
     np.testing.assert_array_equal(got, want)
 
 
-def test_truncated_normal_is_refused_with_a_reason(ops, pair):
-    st, _, _ = pair
-    zi = S.shape_info([1, 64])
-    dz = torch.zeros(64, device="cuda")
-    with pytest.raises(RuntimeError, match="TruncatedNormal"):
-        ops.execRandomFloat(None, 11, st, dz, zi, dz, zi, dz, zi, torch.tensor([0.0, 1.0], device="cuda"))
+@pytest.mark.parametrize("dt,name,n", [(np.float32, "Float", 200001), (np.float64, "Double", 100000), (np.float32, "Float", 2)])
+def test_truncated_normal_matches_up_to_boundary_flips(ops, real_ref, pair, dt, name, n):
+    """TruncatedNormalDistribution (special_random_ops.h:654-806): pairs (e, e + middle) are redrawn until both
+    samples lie within two standard deviations. The uniforms are bit-exact, so the GPU takes the same draws as
+    the reference except where a sample is within rounding of the boundary (device log / cos / sin against
+    glibc's): those elements are counted, everything else agrees to 1e-5 like the Gaussian op."""
+    st, rs, _ = pair
+    zi = S.shape_info([1, n])
+    ex = np.array([0.25, 1.5], dtype=dt)
+    z = np.zeros(n, dt)
+    dz = dev(z)
+    getattr(ops, "execRandom" + name)(None, 11, st, dz, zi, dz, zi, dz, zi, dev(ex))
+    real_ref.random_xy(11, rs, z, zi, z, zi, z, zi, ex)
+    got = host(dz)
+    assert (np.abs(got) + 0.25 <= 3.0 + 1e-5).all()                       # |mean| + |result| <= 2 stddev
+    flipped = int((np.abs(got - z) > 1e-5).sum())
+    assert flipped <= max(2, n // 20000), "%d of %d elements took another draw than the reference" % (flipped, n)
+    assert abs(float(got.mean()) - 0.25) < 0.02 and 0.5 < float(got.std()) < 1.5 or n < 100
+    # the state moved by n on both sides
+    a, b = run_both(ops, real_ref, st, rs, 0, 1000, [0.0, 1.0], dt=dt, name=name)
+    np.testing.assert_array_equal(a, b)
+
+
+def test_truncated_normal_per_element_means_and_refusals(ops, real_ref, pair):
+    st, rs, _ = pair
+    n = 50001                                                             # odd: the last pair has one member
+    zi = S.shape_info([1, n])
+    ex = np.array([0.0, 2.0], np.float32)
+    means = np.random.default_rng(3).uniform(-1, 1, n).astype(np.float32)
+    z = np.zeros(n, np.float32)
+    dz = dev(z)
+    ops.execRandomFloat(None, 11, st, dz, zi, dev(means), zi, dz, zi, dev(ex))
+    real_ref.random_xy(11, rs, z, zi, np.concatenate([means, means[-1:]]), zi, z, zi, ex)
+    got = host(dz)
+    assert int((np.abs(got - z) > 1e-5).sum()) <= 3
+    with pytest.raises(RuntimeError, match="never accepted"):              # the reference would loop forever
+        ops.execRandomFloat(None, 11, st, dz, zi, dz, zi, dz, zi, dev(np.array([5.0, 1.0], np.float32)))

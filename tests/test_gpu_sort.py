@@ -84,6 +84,25 @@ def test_sort_tad(ops, maybe_ref, dt, name, shape, dim, kind, descending):
         np.testing.assert_array_equal(lay.read(host(dx)), lay.read(maybe_ref.sort_tad(lay.buffer.copy(), lay.info, [dim], descending)))
 
 
+@pytest.mark.parametrize("dt,name", NAMES)
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_long_arrays_take_the_radix_path(ops, dt, name, descending):
+    """From 65536 elements on a dense array is radix-sorted (8-bit digits over an order-preserving integer key):
+    ragged last tile, many duplicates (every half value occurs dozens of times) and both directions."""
+    n = (1 << 21) + 4097 + 13
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal(n) * 300).astype(dt)
+    x[:6] = [np.inf, -np.inf, 0.0, -0.0, x[10], x[10]]
+    dx = dev(x)
+    getattr(ops, "sort" + name)(None, dx, S.shape_info([1, n]), descending)
+    want = np.sort(x)[::-1] if descending else np.sort(x)
+    got = host(dx)
+    np.testing.assert_array_equal(got, want)
+    zeros = np.flatnonzero(got == 0)
+    if len(zeros) >= 2:
+        assert np.signbit(got[zeros[0]]) != descending               # -0 sorts before +0
+
+
 def test_sort_large_is_sorted_and_a_permutation(ops):
     # 2^24 + 5 floats: 12 stages beyond the shared-memory chunks; sortedness plus an order-independent checksum
     n = (1 << 24) + 5
@@ -100,7 +119,7 @@ def test_sort_large_is_sorted_and_a_permutation(ops):
     assert torch.equal(x, want)
 
 
-@pytest.mark.parametrize("n", [40, 5000, 30000])
+@pytest.mark.parametrize("n", [40, 5000, 30000, 70001, (1 << 20) + 9])
 def test_sort_total_order_of_zeros_and_nans(ops, n):
     # on-chip keys are totally ordered: -0 before +0, NaNs (sign bit clear) after +inf; nothing is lost
     rng = np.random.default_rng(n)
