@@ -559,6 +559,18 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
     record("random_dropout_inverted_2p%d" % (26 if quick else 30), 8 * n, n,
            lambda: calls.check(lib.nd4jb200_exec_random_x(st, 0, 2, sp, P(xr), zin, P(zbuf), zin, P(e05))), iters=3)
     del xr
+    # The random family is bound by instruction issue on the integer pipes, not by HBM (the reference's hash is
+    # 64-bit integer work): its yardstick is the issue rate, 148 SMs x 4 schedulers x 32 lanes x the SM clock.
+    # Thread instructions per draw are the ncu counts of profiles/random_uniform_gaussian_2p26.md (the other two
+    # ops run the Uniform kernel's hash plus a compare / a multiply).
+    issue_peak = 148 * 4 * 32 * 1.965e9
+    for name_, per_draw in (("random_uniform", 139), ("random_gaussian", 189), ("random_bernoulli", 139), ("random_dropout_inverted", 142)):
+        key_ = "%s_2p%d" % (name_, 26 if quick else 30)
+        if key_ in out:
+            rate = out[key_]["Gelem_s"] * 1e9 * per_draw
+            out[key_].update({"bound": "int-alu", "thread_instr_per_draw": per_draw,
+                              "achieved_Tinstr_s": round(rate / 1e12, 2), "peak_Tinstr_s": round(issue_peak / 1e12, 2),
+                              "frac_of_issue_peak": round(rate / issue_peak, 3)})
     # whole-array Sum of 2^31 (2^27 when quick) floats drawn U(-1,1) on the device: element e is draw e of a fresh
     # seed-119 state, which is also what the ranks of a multi-GPU run generate for their shards
     n2 = 1 << (27 if quick else 31)

@@ -1,5 +1,5 @@
 // Least-significant-digit radix sort for one long dense array: 8-bit digits, so 4 passes for float, 8 for double
-// and 2 for half keys, each pass three launches (tile histograms, per-digit scan over the tiles, stable scatter).
+// and 2 for half keys, each pass four launches (tile histograms, two-level scan of them over the tiles, stable scatter).
 // The bitonic network of sort_ops.cu needs log2(n)^2 / 2 compare steps per key, 45 sweeps of the array for 2^24
 // keys; this needs 3 sweeps per pass whatever n is. The reference sorts with a quicksort on the host
 // (include/ops/impl/specials.cpp:457-564); the sorted sequence is the same.
@@ -11,7 +11,7 @@
 //
 // A tile of kRadixThreads * KPT consecutive keys is owned by one CTA, warp w holding a contiguous run and
 // lane l of round r the key at run offset r * 32 + l, so "earlier key" means "lower (warp, round, lane)".
-// Ranks among equal digits come from __match_any_sync plus a per-warp counter table in shared memory; keys are
+// Ranks among equal digits come from warp ballots plus a per-warp counter table in shared memory; keys are
 // first placed at their tile-local sorted position in shared memory and then written out in that order, which
 // turns the scatter into runs of (on average) tile / 256 consecutive keys per digit.
 #pragma once
@@ -68,10 +68,15 @@ template <> struct RadixKey<__half> {
 struct RadixArgs {
     const void *in;      // pass 0: the array's own values; later passes: keys
     void *out;           // last pass: values; earlier passes: keys
-    unsigned *hist;      // [kRadixBins][tiles]: keys of tile t with digit d; after the scan, their exclusive prefix over t
-    unsigned *totals;    // [kRadixBins]: keys with digit d in the whole array
+    unsigned *hist;      // [tiles][kRadixBins]: keys of tile t with digit d; after the chunk scan, their exclusive
+                         // prefix over the tiles of the same chunk
+    unsigned *chunks;    // [numChunks][kRadixBins]: keys with digit d in chunk c; after the top scan, their exclusive
+                         // prefix over the chunks
+    unsigned *digitBase; // [kRadixBins]: first output position of digit d (written by the top scan)
     LL n;
     LL tiles;
+    LL chunkTiles;       // tiles per chunk
+    LL numChunks;
     int shift;           // bit position of this pass's digit
     int descending;
 };
@@ -82,7 +87,26 @@ template <class T, bool RAW> ND_D typename RadixKey<T>::K radix_read(const void 
     return static_cast<const K *>(base)[i];
 }
 
-// Step 1: hist[d][tile] = number of keys of the tile whose digit is d.
+// Exclusive prefix sum over the CTA's 256 threads (one value each): shuffles inside a warp, one shared-memory round
+// across the 8 warps. `warpSums` is 8 words of shared memory that no other code uses around the call.
+ND_D unsigned radix_block_scan(unsigned v, unsigned *warpSums) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned inc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += t;
+    }
+    if (lane == 31) warpSums[warp] = inc;
+    __syncthreads();
+    unsigned before = 0;
+#pragma unroll
+    for (int w = 0; w < kRadixWarps; w++) before += w < warp ? warpSums[w] : 0u;
+    __syncthreads();
+    return before + inc - v;
+}
+
+// Step 1: hist[tile][d] = number of keys of the tile whose digit is d.
 template <class T, bool IN_RAW>
 __global__ void __launch_bounds__(kRadixThreads) k_radix_histogram(const RadixArgs a) {
     grid_dependency_sync();
@@ -93,133 +117,146 @@ __global__ void __launch_bounds__(kRadixThreads) k_radix_histogram(const RadixAr
         __syncthreads();
         const int warp = threadIdx.x >> 5;
         const LL base = tile * (LL) (kRadixThreads * KPT);
+        typename RadixKey<T>::K key[KPT];
 #pragma unroll
         for (int r = 0; r < KPT; r++) {
             const LL i = base + (LL) r * kRadixThreads + threadIdx.x;     // any order serves a histogram
-            if (i < a.n) atomicAdd(&bins[warp][(unsigned) (radix_read<T, IN_RAW>(a.in, i, a.descending) >> a.shift) & 0xffu], 1u);
+            key[r] = i < a.n ? radix_read<T, IN_RAW>(a.in, i, a.descending) : typename RadixKey<T>::K(0);
         }
-        __syncthreads();
-        for (int d = threadIdx.x; d < kRadixBins; d += kRadixThreads) {
-            unsigned s = 0;
 #pragma unroll
-            for (int w = 0; w < kRadixWarps; w++) s += bins[w][d];
-            a.hist[(LL) d * a.tiles + tile] = s;
+        for (int r = 0; r < KPT; r++) {
+            const LL i = base + (LL) r * kRadixThreads + threadIdx.x;
+            if (i < a.n) atomicAdd(&bins[warp][(unsigned) (key[r] >> a.shift) & 0xffu], 1u);
         }
         __syncthreads();
+        unsigned s = 0;
+#pragma unroll
+        for (int w = 0; w < kRadixWarps; w++) s += bins[w][threadIdx.x];
+        a.hist[tile * kRadixBins + threadIdx.x] = s;
+        __syncthreads();
     }
 }
 
-// Step 2: one CTA per digit turns hist[d][*] into its exclusive prefix over the tiles and records the total.
-__global__ void __launch_bounds__(kRadixThreads) k_radix_scan(const RadixArgs a) {
+// Step 2a: one CTA per chunk of tiles, thread d: exclusive prefix of hist[*][d] over the chunk's tiles (in place)
+// and the chunk's total.
+__global__ void __launch_bounds__(kRadixThreads) k_radix_scan_chunks(const RadixArgs a) {
     grid_dependency_sync();
-    __shared__ unsigned partial[kRadixThreads];
-    const int d = blockIdx.x;
-    unsigned *row = a.hist + (LL) d * a.tiles;
-    const LL per = (a.tiles + kRadixThreads - 1) / kRadixThreads;
-    const LL lo = (LL) threadIdx.x * per;
-    LL hi = lo + per;
-    if (hi > a.tiles) hi = a.tiles;
-    unsigned s = 0;
-    for (LL t = lo; t < hi; t++) s += row[t];
-    partial[threadIdx.x] = s;
-    __syncthreads();
-    // exclusive scan of the per-thread sums (Hillis-Steele over 256 entries)
-    unsigned mine = s;
-    for (int off = 1; off < kRadixThreads; off <<= 1) {
-        const unsigned add = threadIdx.x >= off ? partial[threadIdx.x - off] : 0u;
-        __syncthreads();
-        partial[threadIdx.x] += add;
-        __syncthreads();
+    const LL chunk = blockIdx.x;
+    const LL t0 = chunk * a.chunkTiles;
+    LL t1 = t0 + a.chunkTiles;
+    if (t1 > a.tiles) t1 = a.tiles;
+    unsigned *col = a.hist + threadIdx.x;
+    unsigned run = 0;
+    LL t = t0;
+    for (; t + 8 <= t1; t += 8) {
+        unsigned c[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) c[u] = col[(t + u) * kRadixBins];
+#pragma unroll
+        for (int u = 0; u < 8; u++) { col[(t + u) * kRadixBins] = run; run += c[u]; }
     }
-    unsigned run = partial[threadIdx.x] - mine;
-    if (threadIdx.x == kRadixThreads - 1) a.totals[d] = partial[threadIdx.x];
-    for (LL t = lo; t < hi; t++) { const unsigned c = row[t]; row[t] = run; run += c; }
+    for (; t < t1; t++) { const unsigned c = col[t * kRadixBins]; col[t * kRadixBins] = run; run += c; }
+    a.chunks[chunk * kRadixBins + threadIdx.x] = run;
 }
 
-// Step 3: stable scatter of every tile.
+// Step 2b: one CTA, thread d: exclusive prefix of chunks[*][d] over the chunks (in place), then the first output
+// position of every digit.
+__global__ void __launch_bounds__(kRadixThreads) k_radix_scan_top(const RadixArgs a) {
+    grid_dependency_sync();
+    __shared__ unsigned warpSums[kRadixWarps];
+    unsigned *col = a.chunks + threadIdx.x;
+    unsigned run = 0;
+    for (LL c = 0; c < a.numChunks; c++) { const unsigned v = col[c * kRadixBins]; col[c * kRadixBins] = run; run += v; }
+    a.digitBase[threadIdx.x] = radix_block_scan(run, warpSums);
+}
+
+// Step 3: stable scatter of every tile. The kernel is bound by instruction issue (about a hundred instructions per
+// key, half of them the ballots), so the common case, a full tile, is compiled without any bounds checks and all
+// tile-local arithmetic is 32-bit.
+template <class T, bool IN_RAW, bool FULL, class K, int KPT>
+ND_D void radix_rank_tile(const RadixArgs &a, const void *in, LL base, int live, K (&key)[KPT], unsigned (&rank)[KPT],
+                          unsigned (*cnt)[kRadixBins], int warp, int lane) {
+    const unsigned below = (1u << lane) - 1u;
+#pragma unroll
+    for (int r = 0; r < KPT; r++) {                       // all loads in flight before any ranking
+        const int o = r * 32 + lane;
+        key[r] = (FULL || o < live) ? radix_read<T, IN_RAW>(in, base + o, a.descending) : K(0);
+    }
+    // Rank among the warp's keys of equal digit, earlier rounds first, lower lanes first. The lanes that share a
+    // digit are found with one ballot per digit bit (a match.any instruction serialises over the distinct values
+    // of a warp, about thirty here); the lowest of them bumps the warp's counter for the digit and hands the old
+    // value to the others.
+#pragma unroll
+    for (int r = 0; r < KPT; r++) {
+        const bool valid = FULL || r * 32 + lane < live;
+        const unsigned d = (unsigned) (key[r] >> a.shift) & 0xffu;
+        unsigned peers = FULL ? 0xffffffffu : __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const bool bit = (d >> b) & 1u;
+            const unsigned has = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? has : ~has;
+        }
+        const int leader = FULL ? __ffs(peers) - 1 : max(__ffs(peers) - 1, 0);
+        unsigned before = 0;
+        if (valid && lane == leader) before = atomicAdd(&cnt[warp][d], (unsigned) __popc(peers));
+        before = __shfl_sync(0xffffffffu, before, leader);
+        rank[r] = before + __popc(peers & below);
+    }
+}
+
 template <class T, bool IN_RAW, bool OUT_RAW>
-__global__ void __launch_bounds__(kRadixThreads) k_radix_scatter(const RadixArgs a) {
+__global__ void __launch_bounds__(kRadixThreads, 3) k_radix_scatter(const RadixArgs a) {
     grid_dependency_sync();
     typedef typename RadixKey<T>::K K;
     constexpr int KPT = RadixKey<T>::kKpt;
     constexpr int TILE = kRadixThreads * KPT;
     __shared__ K keys[TILE];
-    __shared__ unsigned cnt[kRadixWarps][kRadixBins];
-    __shared__ unsigned tileBase[kRadixBins];      // first tile-local position of digit d
-    __shared__ unsigned digitBase[kRadixBins];     // first position of digit d in the whole array
-    __shared__ unsigned scan[kRadixThreads];
+    __shared__ unsigned cnt[kRadixWarps][kRadixBins];   // per warp and digit: keys counted so far, then (after the scan)
+                                                        // the tile-local position of the warp's first key of the digit
+    __shared__ unsigned tileBase[kRadixBins];           // first tile-local position of digit d
+    __shared__ LL outBase[kRadixBins];                  // output position of tile-local position 0 of digit d's run
+    __shared__ unsigned warpSums[kRadixWarps];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const unsigned below = (1u << lane) - 1u;
-
-    // first position of every digit in the whole array: exclusive scan of the totals (256 entries, one per thread)
-    {
-        const unsigned t = a.totals[threadIdx.x];
-        scan[threadIdx.x] = t;
-        __syncthreads();
-        for (int off = 1; off < kRadixThreads; off <<= 1) {
-            const unsigned add = threadIdx.x >= off ? scan[threadIdx.x - off] : 0u;
-            __syncthreads();
-            scan[threadIdx.x] += add;
-            __syncthreads();
-        }
-        digitBase[threadIdx.x] = scan[threadIdx.x] - t;
-        __syncthreads();
-    }
 
     for (LL tile = blockIdx.x; tile < a.tiles; tile += gridDim.x) {
         for (int i = threadIdx.x; i < kRadixWarps * kRadixBins; i += kRadixThreads) (&cnt[0][0])[i] = 0;
         __syncthreads();
-        const LL base = tile * (LL) TILE + (LL) warp * (32 * KPT);
+        const LL tileStart = tile * (LL) TILE;
+        const LL left = a.n - tileStart;
+        const int count = left < TILE ? (int) left : TILE;
+        const LL base = tileStart + warp * (32 * KPT);
+        const int live = count - warp * (32 * KPT);       // keys of this warp's run that exist
         K key[KPT];
-        unsigned short rank[KPT];
-        // ranks among the warp's keys of equal digit, earlier rounds first, lower lanes first
-#pragma unroll
-        for (int r = 0; r < KPT; r++) {
-            const LL i = base + r * 32 + lane;
-            const bool valid = i < a.n;
-            key[r] = valid ? radix_read<T, IN_RAW>(a.in, i, a.descending) : K(0);
-            const unsigned d = valid ? ((unsigned) (key[r] >> a.shift) & 0xffu) : 256u;
-            const unsigned peers = __match_any_sync(0xffffffffu, d);
-            unsigned before = 0;
-            if (valid) before = cnt[warp][d];
-            __syncwarp();
-            if (valid && (peers & below) == 0) cnt[warp][d] = before + __popc(peers);   // lowest lane of the group
-            __syncwarp();
-            rank[r] = (unsigned short) (before + __popc(peers & below));
-        }
+        unsigned rank[KPT];
+        if (count == TILE) radix_rank_tile<T, IN_RAW, true>(a, a.in, base, live, key, rank, cnt, warp, lane);
+        else radix_rank_tile<T, IN_RAW, false>(a, a.in, base, live, key, rank, cnt, warp, lane);
         __syncthreads();
-        // per digit: exclusive prefix over the warps, and the tile's histogram
+        // per digit: exclusive prefix over the warps, the tile's histogram, and where the digit's run goes
         {
             const int d = threadIdx.x;
-            unsigned run = 0;
+            unsigned c[kRadixWarps], run = 0;
 #pragma unroll
-            for (int w = 0; w < kRadixWarps; w++) { const unsigned c = cnt[w][d]; cnt[w][d] = run; run += c; }
-            scan[d] = run;
-            __syncthreads();
-            for (int off = 1; off < kRadixThreads; off <<= 1) {
-                const unsigned add = d >= off ? scan[d - off] : 0u;
-                __syncthreads();
-                scan[d] += add;
-                __syncthreads();
-            }
-            tileBase[d] = scan[d] - run;
+            for (int w = 0; w < kRadixWarps; w++) { c[w] = run; run += cnt[w][d]; }
+            const unsigned first = radix_block_scan(run, warpSums);
+#pragma unroll
+            for (int w = 0; w < kRadixWarps; w++) cnt[w][d] = first + c[w];
+            tileBase[d] = first;
+            outBase[d] = (LL) a.digitBase[d] + a.chunks[(tile / a.chunkTiles) * kRadixBins + d] + a.hist[tile * kRadixBins + d] - first;
             __syncthreads();
         }
-        LL left = a.n - tile * (LL) TILE;
-        const int count = left < TILE ? (int) left : TILE;
 #pragma unroll
         for (int r = 0; r < KPT; r++) {
-            const LL i = base + r * 32 + lane;
-            if (i < a.n) {
+            if (count == TILE || r * 32 + lane < live) {
                 const unsigned d = (unsigned) (key[r] >> a.shift) & 0xffu;
-                keys[tileBase[d] + cnt[warp][d] + rank[r]] = key[r];
+                keys[cnt[warp][d] + rank[r]] = key[r];
             }
         }
         __syncthreads();
         for (int i = threadIdx.x; i < count; i += kRadixThreads) {
             const K k = keys[i];
             const unsigned d = (unsigned) (k >> a.shift) & 0xffu;
-            const LL pos = (LL) digitBase[d] + a.hist[(LL) d * a.tiles + tile] + ((unsigned) i - tileBase[d]);
+            const LL pos = outBase[d] + i;
             if (OUT_RAW) RadixKey<T>::store(static_cast<T *>(a.out) + pos, k, a.descending);
             else static_cast<K *>(a.out)[pos] = k;
         }
@@ -237,13 +274,19 @@ Status run_radix_sort(T *x, LL n, int descending, cudaStream_t st) {
     RadixArgs a;
     a.n = n; a.tiles = ceil_div(n, TILE); a.descending = descending;
     const size_t keyBytes = ((size_t) n * sizeof(K) + 255) / 256 * 256;
+    // chunks of at least 64 tiles, and at most 1024 chunks for the single CTA of the top scan
+    a.chunkTiles = 64;
+    if (ceil_div(a.tiles, a.chunkTiles) > 1024) a.chunkTiles = ceil_div(a.tiles, 1024);
+    a.numChunks = ceil_div(a.tiles, a.chunkTiles);
     const size_t histBytes = (size_t) kRadixBins * a.tiles * sizeof(unsigned);
+    const size_t chunkBytes = (size_t) kRadixBins * a.numChunks * sizeof(unsigned);
     void *ws = nullptr;
-    ND_TRY(workspace(st, kWorkspaceScratch + keyBytes + histBytes + kRadixBins * sizeof(unsigned), &ws, nullptr));
+    ND_TRY(workspace(st, kWorkspaceScratch + keyBytes + histBytes + chunkBytes + kRadixBins * sizeof(unsigned), &ws, nullptr));
     char *scratch = static_cast<char *>(ws) + kWorkspaceScratch;
     K *tmp = reinterpret_cast<K *>(scratch);
     a.hist = reinterpret_cast<unsigned *>(scratch + keyBytes);
-    a.totals = a.hist + (size_t) kRadixBins * a.tiles;
+    a.chunks = a.hist + (size_t) kRadixBins * a.tiles;
+    a.digitBase = a.chunks + (size_t) kRadixBins * a.numChunks;
     LL blocks = a.tiles;
     const LL cap = (LL) kNumSMs * 32;
     if (blocks > cap) blocks = cap;
@@ -255,7 +298,8 @@ Status run_radix_sort(T *x, LL n, int descending, cudaStream_t st) {
         const bool first = p == 0, last = p == PASSES - 1;
         if (first) launch_kernel(k_radix_histogram<T, true>, dim3((unsigned) blocks), dim3(kRadixThreads), st, a);
         else launch_kernel(k_radix_histogram<T, false>, dim3((unsigned) blocks), dim3(kRadixThreads), st, a);
-        launch_kernel(k_radix_scan, dim3(kRadixBins), dim3(kRadixThreads), st, a);
+        launch_kernel(k_radix_scan_chunks, dim3((unsigned) a.numChunks), dim3(kRadixThreads), st, a);
+        launch_kernel(k_radix_scan_top, dim3(1), dim3(kRadixThreads), st, a);
         if (first) launch_kernel(k_radix_scatter<T, true, false>, dim3((unsigned) blocks), dim3(kRadixThreads), st, a);
         else if (last) launch_kernel(k_radix_scatter<T, false, true>, dim3((unsigned) blocks), dim3(kRadixThreads), st, a);
         else launch_kernel(k_radix_scatter<T, false, false>, dim3((unsigned) blocks), dim3(kRadixThreads), st, a);

@@ -205,8 +205,12 @@ __global__ void __launch_bounds__(kCopyBlock) k_swap_tads(const SwapArgs a) {
 // as one launch; the usual map (disjoint pairs) is a single round.
 // `flat` receives the swaps grouped by round (in map order inside a round), `counts` the swaps per round.
 Status shuffle_rounds(const int *map, LL numTads, std::vector<int2> *flat, std::vector<size_t> *counts) {
-    std::vector<int> last((size_t) numTads, 0), roundOf;
-    std::vector<int2> swaps;
+    // the work buffers live as long as the calling thread: a fresh vector of this size costs more in page faults
+    // than the loop below costs in arithmetic
+    thread_local std::vector<int> last, roundOf;
+    thread_local std::vector<int2> swaps;
+    last.assign((size_t) numTads, 0);
+    swaps.clear(); roundOf.clear();
     swaps.reserve((size_t) numTads);
     roundOf.reserve((size_t) numTads);
     int rounds = 0;
@@ -223,7 +227,7 @@ Status shuffle_rounds(const int *map, LL numTads, std::vector<int2> *flat, std::
     counts->assign((size_t) rounds, 0);
     if (rounds <= 1) {          // the usual map: disjoint pairs, one launch
         if (rounds == 1) (*counts)[0] = swaps.size();
-        flat->swap(swaps);
+        flat->assign(swaps.begin(), swaps.end());
         return kOk;
     }
     for (size_t i = 0; i < swaps.size(); i++) (*counts)[roundOf[i] - 1]++;
@@ -575,8 +579,8 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
         if (xt.length == 0) continue;
         const LL numTads = xd.length / xt.length;
         if (numTads > 0x7fffffffLL) return bad_arg("shuffle: more TADs than an int map can name");
-        std::vector<int2> flat;
-        std::vector<size_t> rounds;         // swaps per round
+        thread_local std::vector<int2> flat;
+        thread_local std::vector<size_t> rounds;         // swaps per round
         ND_TRY(shuffle_rounds(shuffleMap, numTads, &flat, &rounds));
         const size_t total = flat.size();
         if (total == 0) continue;
