@@ -3,14 +3,16 @@
  * declared with identical member names and parameter types so that the shared library exports
  * the same Itanium-mangled symbols JavaCPP binds in libnd4jcuda (for example
  * _ZN9NativeOps15execReduceFloatEPPviPfPxS2_S2_S3_Pii). Members of the reference class that are
- * not listed here (custom ops, graphs, concat/sort/conversion utilities, aggregates) are outside
- * this backend.
+ * not listed here (custom ops, graph execution, aggregates, the threshold / bitmap / float8 codecs, numpy and
+ * memory-mapping helpers, sortCooIndices, specialConcat) are outside this backend.
  *
  * Semantics follow the reference's CUDA build (blas/cuda/NativeOps.cu):
  *   - x / y / z / extraParams / scalars / dimension / *ShapeInfo arguments are DEVICE pointers;
- *   - extraPointers[0], [7], [8] carry HOST copies of the x, y and z shapeInfo and [1] the
- *     cudaStream_t (stored in the slot itself); when a host copy is absent the shapeInfo (and
- *     the dimension array) is fetched from the device once and cached by address;
+ *   - extraPointers[0], [7], [8] carry HOST copies of the x, y and z shapeInfo, [9] the HOST copy of x's TAD
+ *     shapeInfo and [1] the cudaStream_t (stored in the slot itself). With those slots filled no call reads
+ *     metadata from the device: the dimension list is recovered from [0] and [9]. When a slot is absent the
+ *     descriptor (or the dimension array) is read back with a blocking copy on every call and never cached,
+ *     because descriptor and dimension buffers get reused with other contents;
  *   - calls are asynchronous on that stream; the *Scalar* members synchronise it and return the
  *     value; failures throw std::runtime_error carrying nd4jb200_last_error().
  * Each member forwards to the C entry point of include/nd4j_b200.h named in its comment.
