@@ -10,7 +10,7 @@
 //   pullRows   TAD number indexes[k] of x is copied onto TAD k of z (blas/cpu/NativeOps.cpp:2045-2104)
 //   average    z[i] = sum_k x_k[i] / n, then (optionally) every x_k = z  (specials.cpp:374-433)
 //   accumulate z[i] += sum_k x_k[i]  (onto what z already holds)          (specials.cpp:343-359)
-//   convertTypes  z[i] = (D)(float) x[i] among int8 / uint8 / int16 / uint16 / float16 / float32 / double
+//   convertTypes  z[i] = (D)(float) x[i] among float8 / int8 / uint8 / int16 / uint16 / float16 / float32 / double
 //              (type_conversions.h:592-610, 696-880)
 //   tear       TAD k of x is copied into the array targets[k]               (blas/cpu/NativeOps.cpp:2119-2162)
 //   shuffle    TAD r and TAD map[r] of every array change places, r = 0, 1, ... (blas/cpu/NativeOps.cpp:2266-2326)
@@ -350,6 +350,7 @@ Status sum_sources(void *stream, int dtype, const void *const *sources, void *z,
 // type's range. Its uint16 wrapper clamps to 65536 and returns the value through a uint8_t, so only the low
 // byte survives; that is reproduced, not repaired.
 template <int CODE> struct ConvType;
+template <> struct ConvType<0> { typedef unsigned char T; };     // float8 ("quarter"): sign, 3 exponent bits, 4 mantissa bits
 template <> struct ConvType<1> { typedef signed char T; };
 template <> struct ConvType<2> { typedef unsigned char T; };
 template <> struct ConvType<3> { typedef __half T; };
@@ -363,12 +364,53 @@ ND_D int x86_float_to_int(float v) {
 }
 ND_D int clamp_int(int t, int lo, int hi) { return t > hi ? hi : (t < lo ? lo : t); }
 
+// float8 <-> float exactly as the reference's software routines do it (include/types/impl/float8.cpp:8-96),
+// quirks included: the overflow and underflow thresholds are those of half precision (values between 15.5 and
+// 65520 keep exponent bits that spill into the sign, values below 2^-14 are shifted by 0x90 - exponent, which the
+// x86 shifter the reference runs on takes modulo 32). Conversions are pinned bit for bit against the reference
+// on every float8 value and on a dense sweep of floats.
+ND_D float float8_to_float(unsigned char b) {
+    unsigned sign = (b >> 7) & 1u, exponent = (b >> 4) & 7u, mantissa = (unsigned) (b & 0xfu) << 19;
+    if (exponent == 7u) {                         // infinity, or NaN (which loses its sign)
+        if (mantissa) { sign = 0u; mantissa = 0x7fffffu; }
+        exponent = 0xffu;
+    } else if (exponent == 0u) {
+        if (mantissa) {                           // subnormal: normalise
+            const int up = __clz(mantissa) - 8;   // shifts until bit 23 is set
+            mantissa = (mantissa << up) & 0x7fffffu;
+            exponent = 0x7du - (unsigned) up;
+        }
+    } else {
+        exponent += 0x7cu;
+    }
+    return __uint_as_float((sign << 31) | (exponent << 23) | mantissa);
+}
+ND_D unsigned char float_to_float8(float f) {
+    const unsigned x = __float_as_uint(f), u = x & 0x7fffffffu;
+    if (u > 0x7f800000u) return 0x7fu;                                   // NaN
+    const unsigned sign = (x >> 24) & 0x80u;
+    if (u > 0x477fefffu) return (unsigned char) (sign | 0x70u);           // infinity
+    if (u < 0x33000001u) return (unsigned char) sign;                     // zero
+    unsigned exponent = (u >> 23) & 0xffu, mantissa = u & 0x7fffffu, shift;
+    if (exponent > 0x7cu) { shift = 19u; exponent -= 0x7cu; }
+    else { shift = (0x90u - exponent) & 31u; exponent = 0u; mantissa |= 0x800000u; }
+    const unsigned lsb = 1u << shift, half = lsb >> 1, rest = mantissa & (lsb - 1u);
+    mantissa >>= shift;
+    if (rest > half || (rest == half && (mantissa & 1u))) {               // round to nearest even
+        ++mantissa;
+        if (!(mantissa & 0xfu)) { ++exponent; mantissa = 0u; }
+    }
+    return (unsigned char) (sign | (exponent << 4) | mantissa);
+}
+
 template <int CODE> ND_D float as_float(typename ConvType<CODE>::T v) { return (float) (int) v; }   // the integer types
+template <> ND_D float as_float<0>(unsigned char v) { return float8_to_float(v); }
 template <> ND_D float as_float<3>(__half v) { return __half2float(v); }
 template <> ND_D float as_float<6>(float v) { return v; }
 template <> ND_D float as_float<7>(double v) { return (float) v; }
 
 template <int CODE> ND_D typename ConvType<CODE>::T from_float(float v);
+template <> ND_D unsigned char from_float<0>(float v) { return float_to_float8(v); }
 template <> ND_D signed char from_float<1>(float v) { return (signed char) clamp_int(x86_float_to_int(v), -128, 127); }
 template <> ND_D unsigned char from_float<2>(float v) { return (unsigned char) clamp_int(x86_float_to_int(v), 0, 255); }
 template <> ND_D __half from_float<3>(float v) { return __float2half_rn(v); }
@@ -432,6 +474,7 @@ Status launch_convert(const void *x, void *z, LL n, cudaStream_t stream) {
 template <int SC>
 Status convert_from(int dstType, const void *x, void *z, LL n, cudaStream_t stream) {
     switch (dstType) {
+        case 0: return launch_convert<SC, 0>(x, z, n, stream);
         case 1: return launch_convert<SC, 1>(x, z, n, stream);
         case 2: return launch_convert<SC, 2>(x, z, n, stream);
         case 3: return launch_convert<SC, 3>(x, z, n, stream);
@@ -616,18 +659,19 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
 int nd4jb200_convert_types(void *stream, int srcType, const void *x, Nd4jLong n, int dstType, void *z) {
     if (!x || !z) return bad_arg("convertTypes: null operand");
     if (n < 0) return bad_arg("convertTypes: negative length");
-    // ND4J_INT8 1, UINT8 2, FLOAT16 3, INT16 4, UINT16 5, FLOAT32 6, DOUBLE 7 (type_conversions.h:11-19)
-    const bool srcServed = srcType == 1 || srcType == 2 || srcType == 3 || srcType == 4 || srcType == 6 || srcType == 7;
-    if (!srcServed || dstType < 1 || dstType > 7)
-        return unsupported("convertTypes serves int8 (1), uint8 (2), float16 (3), int16 (4), float32 (6) and double (7) sources "
-                           "and the same plus uint16 (5) as results; the float8 and threshold encodings are not built, and "
+    // ND4J_FLOAT8 0, INT8 1, UINT8 2, FLOAT16 3, INT16 4, UINT16 5, FLOAT32 6, DOUBLE 7 (type_conversions.h:11-19)
+    const bool srcServed = srcType == 0 || srcType == 1 || srcType == 2 || srcType == 3 || srcType == 4 || srcType == 6 || srcType == 7;
+    if (!srcServed || dstType < 0 || dstType > 7)
+        return unsupported("convertTypes serves float8 (0), int8 (1), uint8 (2), float16 (3), int16 (4), float32 (6) and double "
+                           "(7) sources and the same plus uint16 (5) as results; the threshold encodings are not built, and "
                            "the reference has no conversion from uint16");
-    // pairs the reference's dispatch leaves out: the result is not touched (type_conversions.h:725-727, 853-854;
-    // there is no float32 -> float32 branch at all)
-    if (srcType == dstType && (srcType == 1 || srcType == 6 || srcType == 7)) return kOk;
+    // pairs the reference's dispatch leaves out: the result is not touched (type_conversions.h:701-702, 725-727,
+    // 853-854; there is no float32 -> float32 branch at all)
+    if (srcType == dstType && (srcType == 0 || srcType == 1 || srcType == 6 || srcType == 7)) return kOk;
     if (n == 0) return kOk;
     const cudaStream_t st = as_stream(stream);
     switch (srcType) {
+        case 0: return convert_from<0>(dstType, x, z, n, st);
         case 1: return convert_from<1>(dstType, x, z, n, st);
         case 2: return convert_from<2>(dstType, x, z, n, st);
         case 3: return convert_from<3>(dstType, x, z, n, st);

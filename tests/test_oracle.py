@@ -170,3 +170,29 @@ def test_convert_types_restatement_matches_reference(real_ref):
                 assert np.array_equal(np.isnan(z), nan)
                 z, want = np.where(nan, 0, z).astype(dst), np.where(nan, 0, want).astype(dst)
             assert np.array_equal(z.view(np.uint8), want.view(np.uint8)), (src, dst)
+
+
+def test_float8_restatement_matches_reference(real_ref):
+    """float8 <-> everything through NativeOps::convertTypes of the reference itself: all 256 float8 values as
+    sources, and a dense sweep of floats (every exponent, the thresholds, NaN, infinities) as float8 results."""
+    from tests import convert_truth as C
+    q = C.float8_inputs()
+    for dst in C.RESULTS:
+        z = real_ref.convert_types(C.FLOAT8, q, C.CODES[dst], np.full(q.size, 7, dst))
+        want = C.convert_truth_from_float8(q, dst)
+        if np.issubdtype(dst, np.floating):
+            nan = np.isnan(want)
+            assert np.array_equal(np.isnan(z), nan)
+            z, want = np.where(nan, 0, z).astype(dst), np.where(nan, 0, want).astype(dst)
+        assert np.array_equal(z.view(np.uint8), want.view(np.uint8)), dst
+    rng = np.random.default_rng(0)
+    bits = np.concatenate([rng.integers(0, 2 ** 32, 200000, dtype=np.uint64).astype(np.uint32),
+                           np.arange(0x33000000 - 40, 0x33000000 + 40, dtype=np.uint32),
+                           np.arange(0x477FEFFF - 40, 0x477FEFFF + 40, dtype=np.uint32)])
+    f = bits.view(np.float32)
+    got = real_ref.convert_types(C.CODES[np.float32], f.copy(), C.FLOAT8, np.full(f.size, 9, np.uint8))
+    np.testing.assert_array_equal(got, C.float_to_float8(f))
+    for src in C.SOURCES:
+        x = C.convert_inputs(src)
+        got = real_ref.convert_types(C.CODES[src], x, C.FLOAT8, np.full(x.size, 9, np.uint8))
+        np.testing.assert_array_equal(got, C.convert_truth_to_float8(x), err_msg=str(src))
