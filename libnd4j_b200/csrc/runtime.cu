@@ -1,5 +1,6 @@
 // Host-side runtime: error capture and the per-stream scratch workspace.
 #include "runtime.h"
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <sstream>
@@ -59,6 +60,56 @@ Status workspace(cudaStream_t stream, size_t bytes, void **dev, void **hostSlot)
     return kOk;
 }
 
+namespace {
+struct Staging {
+    void *buf[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t cap[4] = {0, 0, 0, 0};
+    cudaEvent_t done[4] = {nullptr, nullptr, nullptr, nullptr};
+    int next = 0;
+};
+std::map<std::pair<int, cudaStream_t>, Staging> g_staging;
+}  // namespace
+
+Status staging_begin(cudaStream_t stream, size_t bytes, void **host, int *slot) {
+    int device = 0;
+    ND_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_mu);
+    Staging &s = g_staging[std::make_pair(device, stream)];
+    const int k = s.next;
+    s.next = (s.next + 1) % 4;
+    if (s.done[k]) ND_CUDA(cudaEventSynchronize(s.done[k]));          // the copy that last used this buffer has left it
+    else ND_CUDA(cudaEventCreateWithFlags(&s.done[k], cudaEventDisableTiming));
+    if (bytes > s.cap[k]) {
+        if (s.buf[k]) ND_CUDA(cudaFreeHost(s.buf[k]));
+        s.buf[k] = nullptr; s.cap[k] = 0;
+        const size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes + bytes / 2;
+        ND_CUDA(cudaMallocHost(&s.buf[k], want));
+        s.cap[k] = want;
+    }
+    *host = s.buf[k];
+    *slot = k;
+    return kOk;
+}
+
+Status staging_commit(cudaStream_t stream, int slot, void *dev, size_t bytes) {
+    int device = 0;
+    ND_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_mu);
+    Staging &s = g_staging[std::make_pair(device, stream)];
+    if (bytes) ND_CUDA(cudaMemcpyAsync(dev, s.buf[slot], bytes, cudaMemcpyHostToDevice, stream));
+    ND_CUDA(cudaEventRecord(s.done[slot], stream));
+    return kOk;
+}
+
+Status staged_upload(cudaStream_t stream, void *dev, const void *host, size_t bytes) {
+    if (bytes == 0) return kOk;
+    void *pinned = nullptr;
+    int slot = 0;
+    ND_TRY(staging_begin(stream, bytes, &pinned, &slot));
+    memcpy(pinned, host, bytes);
+    return staging_commit(stream, slot, dev, bytes);
+}
+
 void release_workspaces() {
     std::lock_guard<std::mutex> lock(g_mu);
     for (auto &kv : g_blocks) {
@@ -68,6 +119,12 @@ void release_workspaces() {
     g_blocks.clear();
     for (void *p : g_retired) cudaFree(p);
     g_retired.clear();
+    for (auto &kv : g_staging)
+        for (int k = 0; k < 4; k++) {
+            if (kv.second.buf[k]) cudaFreeHost(kv.second.buf[k]);
+            if (kv.second.done[k]) cudaEventDestroy(kv.second.done[k]);
+        }
+    g_staging.clear();
 }
 
 }  // namespace nd4jb200

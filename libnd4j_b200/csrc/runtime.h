@@ -33,6 +33,17 @@ constexpr size_t kCounterSlots = 65536;
 constexpr size_t kWorkspaceScratch = 256 + kCounterSlots * sizeof(unsigned);
 void release_workspaces();
 
+// Host-to-device copy of a small list (pointer tables, swap lists) that does not stall the caller: the bytes are
+// copied into a pinned staging buffer owned by the library (a ring of four per device and stream, each guarded by
+// an event) and sent from there with a truly asynchronous copy. A copy straight from pageable memory is ordered
+// behind the stream's earlier work and keeps the calling thread blocked until it has run, which serialises the
+// host-side preparation of call k + 1 with the kernel of call k.
+Status staged_upload(cudaStream_t stream, void *dev, const void *host, size_t bytes);
+// The same in two steps, for callers that build the list in place: staging_begin hands out a pinned buffer of at
+// least `bytes` (and the slot to commit), staging_commit sends its first `bytes` bytes to `dev`.
+Status staging_begin(cudaStream_t stream, size_t bytes, void **host, int *slot);
+Status staging_commit(cudaStream_t stream, int slot, void *dev, size_t bytes);
+
 // Counts kernel launches issued by this library since load (read by the benchmark).
 extern std::atomic<unsigned long long> g_launches;
 inline void count_launch(int n = 1) { g_launches.fetch_add((unsigned long long) n, std::memory_order_relaxed); }

@@ -20,6 +20,7 @@
 #include "device_utils.cuh"
 #include "runtime.h"
 #include <sstream>
+#include <cstring>
 #include <vector>
 
 namespace nd4jb200 {
@@ -205,12 +206,8 @@ __global__ void __launch_bounds__(kCopyBlock) k_swap_tads(const SwapArgs a) {
 // as one launch; the usual map (disjoint pairs) is a single round.
 // `flat` receives the swaps grouped by round (in map order inside a round), `counts` the swaps per round.
 Status shuffle_rounds(const int *map, LL numTads, std::vector<int2> *flat, std::vector<size_t> *counts) {
-    // the work buffers live as long as the calling thread: a fresh vector of this size costs more in page faults
-    // than the loop below costs in arithmetic
-    thread_local std::vector<int> last, roundOf;
-    thread_local std::vector<int2> swaps;
-    last.assign((size_t) numTads, 0);
-    swaps.clear(); roundOf.clear();
+    std::vector<int> last((size_t) numTads, 0), roundOf;
+    std::vector<int2> swaps;
     swaps.reserve((size_t) numTads);
     roundOf.reserve((size_t) numTads);
     int rounds = 0;
@@ -227,7 +224,7 @@ Status shuffle_rounds(const int *map, LL numTads, std::vector<int2> *flat, std::
     counts->assign((size_t) rounds, 0);
     if (rounds <= 1) {          // the usual map: disjoint pairs, one launch
         if (rounds == 1) (*counts)[0] = swaps.size();
-        flat->assign(swaps.begin(), swaps.end());
+        flat->swap(swaps);
         return kOk;
     }
     for (size_t i = 0; i < swaps.size(); i++) (*counts)[roundOf[i] - 1]++;
@@ -589,7 +586,7 @@ int nd4jb200_tear(void *stream, int dtype, const void *x, const Nd4jLong *xShape
     void **devTargets = reinterpret_cast<void **>(static_cast<char *>(ws) + kWorkspaceScratch);
     for (LL k = 0; k < a.n; k++)
         if (!targets[k]) return bad_arg("tear: null target array");
-    ND_CUDA(cudaMemcpyAsync(devTargets, targets, sizeof(void *) * (size_t) a.n, cudaMemcpyHostToDevice, st));
+    ND_TRY(staged_upload(st, devTargets, targets, sizeof(void *) * (size_t) a.n));
     a.targets = devTargets;
     a.indexes = nullptr; a.xOffsets = tadOffsets; a.zOffsets = nullptr;
     if (zd.ews > 0 && xt.ews > 0) {
@@ -622,16 +619,43 @@ int nd4jb200_shuffle(void *stream, int dtype, int numArrays, void *const *x, con
         if (xt.length == 0) continue;
         const LL numTads = xd.length / xt.length;
         if (numTads > 0x7fffffffLL) return bad_arg("shuffle: more TADs than an int map can name");
-        thread_local std::vector<int2> flat;
-        thread_local std::vector<size_t> rounds;         // swaps per round
-        ND_TRY(shuffle_rounds(shuffleMap, numTads, &flat, &rounds));
-        const size_t total = flat.size();
-        if (total == 0) continue;
+        std::vector<int2> flat;
+        std::vector<size_t> rounds;         // swaps per round
+        // The usual map pairs every TAD with at most one other: one round, and the pair list is written straight
+        // into a pinned staging buffer while a byte per TAD watches for a TAD that turns up twice. Any other map
+        // takes the general ordering into rounds below.
+        void *pinned = nullptr;
+        int slot = 0;
+        ND_TRY(staging_begin(st, (size_t) numTads * sizeof(int2), &pinned, &slot));
+        int2 *pairs = static_cast<int2 *>(pinned);
+        size_t total = 0;
+        bool simple = true;
+        {
+            thread_local std::vector<unsigned char> tlSeen;
+            std::vector<unsigned char> &seen = tlSeen;
+            seen.assign((size_t) numTads, 0);
+            for (LL r = 0; r < numTads; r++) {
+                const int m = shuffleMap[r];
+                if (m < 0 || m == r) continue;
+                if (m >= numTads) return bad_arg("shuffle: the map names a TAD past the last one");
+                if (seen[r] | seen[m]) { simple = false; break; }
+                seen[r] = seen[m] = 1;
+                pairs[total++] = make_int2((int) r, m);
+            }
+        }
+        if (simple) {
+            rounds.assign(total ? 1 : 0, total);
+        } else {
+            ND_TRY(shuffle_rounds(shuffleMap, numTads, &flat, &rounds));
+            total = flat.size();
+            if (total) memcpy(pairs, flat.data(), total * sizeof(int2));
+        }
+        if (total == 0) { ND_TRY(staging_commit(st, slot, nullptr, 0)); continue; }
         // every array's lists get their own part of the workspace: an earlier array's launches may still read theirs
         void *ws = nullptr;
         ND_TRY(workspace(st, kWorkspaceScratch + used + total * sizeof(int2), &ws, nullptr));
         int2 *dev = reinterpret_cast<int2 *>(static_cast<char *>(ws) + kWorkspaceScratch + used);
-        ND_CUDA(cudaMemcpyAsync(dev, flat.data(), total * sizeof(int2), cudaMemcpyHostToDevice, st));
+        ND_TRY(staging_commit(st, slot, dev, total * sizeof(int2)));
         used += total * sizeof(int2);
         SwapArgs a;
         a.x = x[f]; a.offsets = tadOffsets[f]; a.tadLen = xt.length;
