@@ -687,20 +687,44 @@ def run_ours(args):
         ms_step = float(t.item())
     value = world * ELEMS / ms_step / 1e6   # Gelem/s over all ranks
 
-    # per-kernel durations, each timed alone on the launch stream over the same buffers
+    # Per-kernel durations, each kernel timed alone on the launch stream. Consecutive launches alternate between
+    # two complete sets of buffers, so that nothing a launch touches is left in the 126 MB L2 by the launch before
+    # it (a kernel replayed on one set finds the tail of its own previous output there and reads above the DRAM
+    # peak).
+    with torch.cuda.stream(stream):
+        dx2, dy2 = dx.clone(), dy.clone()
+        t1b, t2b, dzb = (torch.empty(ROWS, COLS, device="cuda") for _ in range(3))
+        t1b.copy_(t1); t2b.copy_(t2)
+    sets = ((dx, t1, t2, dy, dz), (dx2, t1b, t2b, dy2, dzb))
+    flip = [0]
+
+    def alt(kind):
+        def fn():
+            flip[0] ^= 1
+            ax, a1, a2, ay, az = sets[flip[0]]
+            if kind == 0:
+                calls.check(lib.nd4jb200_exec_broadcast(st, 0, 0, P(ax), xi, P(db), bi, P(a1), xi, d1, 1))
+            elif kind == 1:
+                calls.check(lib.nd4jb200_exec_transform(st, 0, 15, P(a1), xi, P(a2), xi, None))
+            elif kind == 2:
+                calls.check(lib.nd4jb200_exec_pairwise(st, 0, 6, P(a2), xi, P(ay), xi, P(az), xi, None))
+            else:
+                calls.check(lib.nd4jb200_exec_chain(st, 0, 0, P(ax), xi, P(db), bi, d1, 1, 15, None, 6, P(ay), xi, None, P(az), xi))
+        return fn
     per = {}
-    for name, fn in (("broadcast_add", k_broadcast), ("transform_tanh", k_tanh), ("pairwise_mul", k_mul)):
-        for _ in range(3):
+    for kind, name in enumerate(("broadcast_add", "transform_tanh", "pairwise_mul")):
+        fn = alt(kind)
+        for _ in range(4):
             fn()
         per[name] = time_graph(torch, stream, fn, 20)
     # the same chain as ONE fused pass (nd4jb200_exec_chain): x and y read once, z written once
     fused_bytes = 3 * ELEMS * 4 + COLS * 4
 
-    def k_fused():
-        calls.check(lib.nd4jb200_exec_chain(st, 0, 0, P(dx), xi, P(db), bi, d1, 1, 15, None, 6, P(dy), xi, None, P(dz), xi))
-    for _ in range(3):
+    k_fused = alt(3)
+    for _ in range(4):
         k_fused()
     fused_ms = time_graph(torch, stream, k_fused, 20)
+    del dx2, dy2, t1b, t2b, dzb, sets
     fused = {"ms_per_step": round(fused_ms, 5), "Gelem_s": round(ELEMS / fused_ms / 1e6, 2),
              "GBps": round(fused_bytes / fused_ms / 1e6, 1), "frac_of_measured_peak": round(fused_bytes / fused_ms / 1e6 / peak, 4),
              "algorithmic_bytes": fused_bytes,
@@ -712,7 +736,9 @@ def run_ours(args):
                 "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
                 "per_kernel_ms": {k: round(v, 5) for k, v in per.items()},
                 "per_kernel_GBps": {k: round(BYTES[k] / v / 1e6, 1) for k, v in per.items()},
-                "frac_of_nominal_8TBps": round(achieved / 8000.0, 4)}
+                "frac_of_nominal_8TBps": round(achieved / 8000.0, 4),
+                "note": "consecutive timed launches alternate between two buffer sets (no L2 residue); the peak is a "
+                        "one-read-one-write copy, which a two-reads-one-write kernel can exceed slightly"}
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(traffic_file):
         with open(traffic_file) as f:
@@ -799,7 +825,7 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "elementwise chain f32 [16384,4096]: execBroadcast Add(dim 1) -> execTransform Tanh -> "
-                                   "execPairwiseTransform Multiply", "l2": "inputs larger than L2 (3 x 268 MB streamed per step)",
+                                   "execPairwiseTransform Multiply", "l2": "inputs larger than L2 (3 x 268 MB streamed per step); per-kernel timings alternate two buffer sets",
                        "sharding": "one independent chain per GPU"},
             "roofline": roofline, "fused_chain": fused, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks,
