@@ -4,7 +4,7 @@
  * the same Itanium-mangled symbols JavaCPP binds in libnd4jcuda (for example
  * _ZN9NativeOps15execReduceFloatEPPviPfPxS2_S2_S3_Pii). Members of the reference class that are
  * not listed here (custom ops, graph execution, aggregates, the threshold / bitmap / float8 codecs, numpy and
- * memory-mapping helpers, sortCooIndices, specialConcat) are outside this backend.
+ * memory-mapping helpers, specialConcat) are outside this backend.
  *
  * Semantics follow the reference's CUDA build (blas/cuda/NativeOps.cu):
  *   - x / y / z / extraParams / scalars / dimension / *ShapeInfo arguments are DEVICE pointers;
@@ -172,6 +172,13 @@ public:
                                       float *dz, Nd4jLong *zShapeInfo, int *dimension, int dimensionLength,
                                       Nd4jLong *tadShapeInfo, Nd4jLong *tadOffsets, float *extraA, float *extraB,
                                       float scalarA, float scalarB, bool scalarReturned);
+
+    /* The reference's CUDA build throws "Not implemented yet" from these three (blas/cuda/NativeOps.cu:6072-6082) and
+     * its CPU build does not leave the coordinates sorted (include/ops/impl/specials_sparse.cpp:82-113 compares
+     * against a pivot position that its own partition loop moves); they are exported with the CUDA build's behaviour. */
+    void sortCooIndicesFloat(Nd4jPointer *extraPointers, Nd4jLong *indices, float *values, Nd4jLong length, int rank);
+    void sortCooIndicesDouble(Nd4jPointer *extraPointers, Nd4jLong *indices, double *values, Nd4jLong length, int rank);
+    void sortCooIndicesHalf(Nd4jPointer *extraPointers, Nd4jLong *indices, float16 *values, Nd4jLong length, int rank);
 
     /* nd4jb200_init_random and friends (NativeOps.h:2510-2539). extraPointers[0] = host table,
      * [1] = stream, ptrToBuffer = device table (blas/cuda/NativeOps.cu:5384-5391). */

@@ -393,6 +393,10 @@ void NativeOps::execMetaPredicateReduceFloat(Nd4jPointer *, const int, const int
                                              float *, Nd4jLong *, float *, Nd4jLong *, int *, int, Nd4jLong *, Nd4jLong *,
                                              float *, float *, float, float, bool) {}
 
+void NativeOps::sortCooIndicesFloat(Nd4jPointer *, Nd4jLong *, float *, Nd4jLong, int) { throw std::runtime_error("Not implemented yet"); }
+void NativeOps::sortCooIndicesDouble(Nd4jPointer *, Nd4jLong *, double *, Nd4jLong, int) { throw std::runtime_error("Not implemented yet"); }
+void NativeOps::sortCooIndicesHalf(Nd4jPointer *, Nd4jLong *, float16 *, Nd4jLong, int) { throw std::runtime_error("Not implemented yet"); }
+
 void NativeOps::convertTypes(Nd4jPointer *extras, int srcType, Nd4jPointer x, Nd4jLong N, int dstType, Nd4jPointer z) {
     check(nd4jb200_convert_types(stream_of(extras), srcType, x, N, dstType, z), "convertTypes");
 }
