@@ -744,10 +744,13 @@ def run_ours(args):
         with open(traffic_file) as f:
             roofline["traffic"] = json.load(f).get(dom)
 
-    # End to end through host buffers: H2D of x, b, y, the chain, D2H of the result. The arrays are
-    # cut into row blocks; block k's chain runs while block k+1 is copied in and block k-1 is copied
-    # out (three streams, the same exec* calls on [rows/blocks, COLS] shapeInfos), so the step costs
-    # about max(H2D, D2H) on a full-duplex link instead of their sum.
+    # End to end through host buffers: H2D of x, b, y, the chain, D2H of the result, every step. The arrays are
+    # cut into row blocks; block k's chain runs while block k+1 is copied in and block k-1 is copied out (three
+    # streams, the same exec* calls on [rows/blocks, COLS] shapeInfos), so a step costs about max(H2D, D2H) on a
+    # full-duplex link instead of their sum. Consecutive steps are chained by their data dependencies only, block
+    # by block (a block's inputs may be overwritten once the previous step's chain has read them, its result once
+    # the previous result has left the device; the vector b alternates between two device copies), so the copy-in
+    # of step n+1 starts while step n is still draining, as in any loop over batches.
     NBLK = args.e2e_blocks
     brow = ROWS // NBLK
     bbytes = brow * COLS * 4
@@ -755,23 +758,34 @@ def run_ours(args):
     h_in, h_cmp, h_out = (ctypes.c_void_p(q.cuda_stream) for q in (s_in, stream, s_out))
     ev_in = [torch.cuda.Event() for _ in range(NBLK)]
     ev_cmp = [torch.cuda.Event() for _ in range(NBLK)]
-    ev_begin, ev_end = torch.cuda.Event(), torch.cuda.Event()
+    ev_out = [torch.cuda.Event() for _ in range(NBLK)]
+    ev_step = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_end = torch.cuda.Event()
+    with torch.cuda.stream(stream):
+        dbs = (db, db.clone())
     xib = calls.longs(S.shape_info([brow, COLS]))
     cp = lib.nd4jb200_memcpy_async
     V = ctypes.c_void_p
+    step_no = [0]
 
     def e2e_step():
-        ev_begin.record(stream)             # the copies of this step follow the previous step's work
-        s_in.wait_event(ev_begin)
-        s_out.wait_event(ev_begin)
-        calls.check(cp(V(db.data_ptr()), V(hb.data_ptr()), COLS * 4, 1, h_in))
+        n = step_no[0]
+        step_no[0] += 1
+        dbn = dbs[n % 2]
+        if n >= 2:
+            s_in.wait_event(ev_step[n % 2])          # the chain of step n-2 has finished with this copy of b
+        calls.check(cp(V(dbn.data_ptr()), V(hb.data_ptr()), COLS * 4, 1, h_in))
         for k in range(NBLK):
             off = k * bbytes
+            if n >= 1:
+                s_in.wait_event(ev_cmp[k])           # the previous step's chain has read block k of x and y
             calls.check(cp(V(dx.data_ptr() + off), V(hx.data_ptr() + off), bbytes, 1, h_in))
             calls.check(cp(V(dy.data_ptr() + off), V(hy.data_ptr() + off), bbytes, 1, h_in))
             ev_in[k].record(s_in)
             stream.wait_event(ev_in[k])
-            calls.check(lib.nd4jb200_exec_broadcast(h_cmp, 0, 0, V(dx.data_ptr() + off), xib, P(db), bi,
+            if n >= 1:
+                stream.wait_event(ev_out[k])         # the previous result of block k has left the device
+            calls.check(lib.nd4jb200_exec_broadcast(h_cmp, 0, 0, V(dx.data_ptr() + off), xib, P(dbn), bi,
                                                     V(t1.data_ptr() + off), xib, d1, 1))
             calls.check(lib.nd4jb200_exec_transform(h_cmp, 0, 15, V(t1.data_ptr() + off), xib, V(t2.data_ptr() + off), xib, None))
             calls.check(lib.nd4jb200_exec_pairwise(h_cmp, 0, 6, V(t2.data_ptr() + off), xib, V(dy.data_ptr() + off), xib,
@@ -779,20 +793,36 @@ def run_ours(args):
             ev_cmp[k].record(stream)
             s_out.wait_event(ev_cmp[k])
             calls.check(cp(V(hz.data_ptr() + off), V(dz.data_ptr() + off), bbytes, 2, h_out))
+            ev_out[k].record(s_out)
+        ev_step[n % 2].record(stream)
+
+    def e2e_drain():
         ev_end.record(s_out)
-        stream.wait_event(ev_end)           # the step ends when the last block is back on the host
+        stream.wait_event(ev_end)                    # the last block of the last step is back on the host
 
     e2e_step()
+    e2e_drain()
     barrier()
-    e2e_iters = max(2, min(args.steps, 5))
-    e2e_ms = time_loop(torch, stream, e2e_step, e2e_iters)
+    e2e_iters = max(4, min(args.steps, 10))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(e2e_iters):
+        e2e_step()
+    e2e_drain()
+    stop.record(stream)
+    stop.synchronize()
+    e2e_ms = start.elapsed_time(stop) / e2e_iters
+    # the chain's result of the last step, as it arrived in host memory, against the device's copy
+    torch.cuda.synchronize()
+    if not torch.equal(hz.view(ROWS, COLS)[-brow:], dz[-brow:].cpu()):
+        raise SystemExit("end-to-end step: the result read back differs from the device's")
     if dist is not None:
         t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": round(world * ELEMS / e2e_ms / 1e6, 3), "unit": "Gelem/s", "ms_per_step": round(e2e_ms, 3),
            "h2d_bytes_per_step": 2 * ELEMS * 4 + COLS * 4, "d2h_bytes_per_step": ELEMS * 4,
-           "pipeline": "%d row blocks; H2D, chain and D2H on three streams" % NBLK,
+           "pipeline": "%d row blocks; H2D, chain and D2H on three streams; consecutive steps chained block by block" % NBLK,
            "per_rank_h2d_GBps": round((2 * ELEMS * 4 + COLS * 4) / e2e_ms / 1e6, 1),
            "per_rank_d2h_GBps": round(ELEMS * 4 / e2e_ms / 1e6, 1)}
 
