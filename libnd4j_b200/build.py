@@ -35,6 +35,7 @@ def _sources():
     units.append(("no_alloc", "no_alloc.cu", []))
     units.append(("utility_ops", "utility_ops.cu", []))
     units.append(("sort_ops", "sort_ops.cu", []))
+    units.append(("special_transforms", "special_transforms.cu", []))
     units.append(("device_env", "device_env.cu", []))
     units.append(("comm", "comm.cu", []))
     units.append(("runtime", "runtime.cu", []))

@@ -422,6 +422,8 @@ int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, c
     ShapeDesc xd, zd;
     ND_TRY(parse_shape(xShapeInfo, "xShapeInfo", &xd));
     ND_TRY(parse_shape(zShapeInfo, "zShapeInfo", &zd));
+    if (opNum == 36 || opNum == 37 || opNum == 48 || opNum == 70 || opNum == 71)
+        return run_special_transform(dtype, opNum, x, xd, z, zd, extraParams, as_stream(stream));
     if (xd.length != zd.length) return bad_arg("transform: x and z hold different numbers of elements");
     if (opNum == 41) {
         // IsMax: extraParams = {dimensionLength, dimension...} as element-type values on the device; absent, 0 or

@@ -31,7 +31,7 @@ Status ND_S(transform)(int opNum, const EwArgs &a, cudaStream_t st) {
 #undef X
         case 36: case 37: case 48: case 70: case 71:
             return unsupported("transform opNum " + std::to_string(opNum) +
-                               " is a composite (special) transform, not an elementwise functor");
+                               " is a whole-array (special) transform: it is served for shaped calls, not for strided or indexed ones");
         case 43: case 44:
             return unsupported("transform DropOut/DropOutInverted draw from rand()/clock in the reference and are "
                                "not reproducible; use the random family (execRandom opNum 1/2)");

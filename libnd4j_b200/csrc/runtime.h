@@ -95,6 +95,12 @@ inline void launch_kernel_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     count_launch();
 }
 
+// The whole-array ("special") transforms Col2Im 36, Im2col 37, Histogram 48, Reverse 70, Pooling2D 71
+// (special_transforms.cu); extraParams is a device pointer to element-type values.
+struct ShapeDesc;
+Status run_special_transform(int dtype, int opNum, const void *x, const ShapeDesc &xd, void *z, const ShapeDesc &zd,
+                             const void *extraParams, cudaStream_t stream);
+
 Status bad_arg(const std::string &msg);
 Status unsupported(const std::string &msg);
 Status unknown_op(const char *family, int opNum);
