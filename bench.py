@@ -476,6 +476,35 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
             out[incl]["sort_only_Gelem_s"] = round(elems / ms_ / 1e6, 2)
             out[incl]["sort_only_frac_of_measured_peak"] = round(2 * elems * 4 / ms_ / 1e6 / peak, 3)
     del unsorted_, work_
+    # whole-array transforms through execTransform: Im2col / Col2Im (3x3, stride 1, padding 1 on [32,64,56,56]), max
+    # Pooling2D 2x2 stride 2 on [64,64,112,112], Reverse and Histogram (256 bins) of 2^26 floats
+    img_ = torch.randn(32, 64, 56, 56, device=dev, generator=g)
+    col_ = torch.empty(32, 64, 3, 3, 56, 56, device=dev)
+    imgi_, coli_ = calls.longs(S.shape_info([32, 64, 56, 56])), calls.longs(S.shape_info([32, 64, 3, 3, 56, 56]))
+    e_i2c = torch.tensor([3, 3, 1, 1, 1, 1, 1, 1, 0, 0], dtype=torch.float32, device=dev)
+    e_c2i = torch.tensor([1, 1, 1, 1, 56, 56, 1, 1, 0], dtype=torch.float32, device=dev)
+    record("im2col_f32_32x64x56x56_k3", (col_.numel() + img_.numel()) * 4, col_.numel(),
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 37, P(img_), imgi_, P(col_), coli_, P(e_i2c))))
+    record("col2im_f32_32x64x56x56_k3", (col_.numel() + img_.numel()) * 4, col_.numel(),
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 36, P(col_), coli_, P(img_), imgi_, P(e_c2i))))
+    del img_, col_
+    pin_ = torch.randn(64, 64, 112, 112, device=dev, generator=g)
+    pout_ = torch.empty(64, 64, 56, 56, device=dev)
+    pini_, pouti_ = calls.longs(S.shape_info([64, 64, 112, 112])), calls.longs(S.shape_info([64, 64, 56, 56]))
+    e_pool = torch.tensor([2, 2, 2, 2, 0, 0, 1, 1, 0, 0, 0], dtype=torch.float32, device=dev)
+    record("pooling2d_max_f32_64x64x112x112_k2s2", (pin_.numel() + pout_.numel()) * 4, pin_.numel(),
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 71, P(pin_), pini_, P(pout_), pouti_, P(e_pool))))
+    del pin_, pout_
+    rv_ = torch.randn(1 << 26, device=dev, generator=g)
+    rvo_ = torch.empty_like(rv_)
+    rvi_ = calls.longs(S.shape_info([1, 1 << 26]))
+    record("reverse_f32_2p26", 2 * (1 << 26) * 4, 1 << 26,
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 70, P(rv_), rvi_, P(rvo_), rvi_, None)))
+    hz_ = torch.zeros(256, device=dev)
+    e_hist = torch.tensor([256, -4, 4], dtype=torch.float32, device=dev)
+    record("histogram_f32_2p26_256bins", (1 << 26) * 4, 1 << 26,
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 48, P(rv_), rvi_, P(hz_), calls.longs(S.shape_info([1, 256])), P(e_hist))))
+    del rv_, rvo_
     blocks_ = [torch.randn(4096, 4096, device=dev, generator=g) for _ in range(4)]
     cat_ = torch.empty(16384, 4096, device=dev)
     ptrs_ = (ctypes.c_void_p * 4)(*[b_.data_ptr() for b_ in blocks_])

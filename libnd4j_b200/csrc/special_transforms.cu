@@ -4,12 +4,14 @@
 // (include/loops/cpu/transform.cpp:30-60 hands ops with requiresSpecial to Op::execSpecial). The softmax family
 // and IsMax (38-41) live in softmax.cuh and api.cu.
 //
-// All five are pure data movement plus a few operations per element, so each kernel is laid out for coalesced
-// access along the innermost image axis: a CTA works on one or a few (batch, channel[, kernel row, kernel column])
-// planes, its threads walk the plane's positions with a stride of the CTA width, and a position's (row, column)
-// pair is advanced incrementally instead of being recomputed by division. The geometry that the reference keeps
-// in extraParams (kernel, stride, padding, dilation as element-type values in device memory) is read by the
-// kernels themselves, so no call waits for a device-to-host copy.
+// All five are data movement plus a few operations per element, so each kernel is laid out for the memory system.
+// In the three image kernels a CTA works on one or a few (batch, channel[, kernel row, kernel column]) planes and
+// a thread produces a run of 16 bytes of consecutive plane positions (one 128-bit store where the plane is dense
+// and aligned). The index arithmetic of a run is shared by its positions (a run that stays inside one image row
+// tests and addresses the row once) and is 32-bit inside a plane; the loop over the kernel taps runs inside the
+// thread, so the decomposition of a thread's index is paid once for all taps. The geometry that the reference keeps in
+// extraParams (kernel, stride, padding, dilation as element-type values in device memory) is read by the kernels
+// themselves, so no call waits for a device-to-host copy.
 #include "../../include/nd4j_b200.h"
 #include "device_utils.cuh"
 #include "runtime.h"
@@ -19,203 +21,335 @@ namespace nd4jb200 {
 
 namespace {
 
-// A plane is split over threadIdx.x (positions) and several planes share a CTA through threadIdx.y when a plane
-// has fewer positions than the CTA has threads.
+// A plane is split over threadIdx.x (runs of V positions) and several planes share a CTA through threadIdx.y when
+// a plane has fewer runs than the CTA has threads.
 struct PlaneGrid {
     int tx, ty;          // blockDim
-    unsigned gx, gy;     // gridDim: planes / ty, position chunks
-    int iters;           // positions per thread
+    unsigned gx, gy;     // gridDim: planes / ty, chunks of runs
 };
 
-inline PlaneGrid plane_grid(LL planes, LL positions) {
+inline PlaneGrid plane_grid(LL planes, LL positions, int v) {
+    const LL runs = ceil_div(positions, (LL) v);
     PlaneGrid g;
+    // the CTA width (a multiple of a warp) that leaves the fewest idle threads in a plane's last chunk; ties go to
+    // the wider CTA
     g.tx = 32;
-    while (g.tx < 256 && g.tx < positions) g.tx *= 2;
+    LL idle = -1;
+    for (int tx = 32; tx <= 256; tx += 32) {
+        const LL waste = ceil_div(runs, (LL) tx) * tx - runs;
+        if (idle < 0 || waste <= idle) { idle = waste; g.tx = tx; }
+        if (tx >= runs) break;
+    }
     g.ty = 256 / g.tx;
-    g.iters = positions >= 256 * 8 ? 8 : (int) ceil_div(positions, (LL) g.tx);
-    if (g.iters > 8) g.iters = 8;
+    // One short-lived thread per run and plane: fewer, longer-lived CTAs that walk the planes with the grid's stride
+    // were slower (Im2col 0.098 against 0.084 ms), the hardware keeps more independent loads in flight this way.
     g.gx = (unsigned) ceil_div(planes, (LL) g.ty);
-    g.gy = (unsigned) ceil_div(positions, (LL) g.tx * g.iters);
+    g.gy = (unsigned) ceil_div(runs, (LL) g.tx);
     return g;
 }
 
-template <class T> ND_D int param_int(const T *extra, int i) { return (int) Elem<T>::load(extra + i); }
+// extraParams are the same few words for every CTA: read through the read-only path so that they stay in L1
+template <class T> ND_D T param(const T *extra, int i) { return __ldg(extra + i); }
+template <> ND_D __half param(const __half *extra, int i) { return __ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(extra) + i)); }
+template <class T> ND_D int param_int(const T *extra, int i) { return (int) Elem<T>::to_c(param(extra, i)); }
+
+// What a kernel needs to place the positions of one result plane. Offsets inside a plane fit 32 bits (checked by
+// the host).
+struct PlaneOut {
+    int sRow, sCol;      // strides of the plane's two axes
+    int width;           // positions per row
+    int positions;
+    int dense;           // position p lies at offset p and runs may be stored as one 128-bit word
+};
+
+// Stores vals[0 .. V) at the positions p0 .. p0 + V of a plane, as far as they exist.
+template <class T, int V>
+ND_D void store_run(T *__restrict__ plane, const PlaneOut &o, int p0, const T (&vals)[V]) {
+    if (p0 >= o.positions) return;
+    if (o.dense && p0 + V <= o.positions) {
+        Pack<T> pk;
+#pragma unroll
+        for (int j = 0; j < V; j++) pk.v[j] = vals[j];
+        store_pack(plane + p0, pk);
+        return;
+    }
+    int row = p0 / o.width, col = p0 - row * o.width;
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        if (p0 + j < o.positions) plane[o.dense ? p0 + j : row * o.sRow + col * o.sCol] = vals[j];
+        if (++col == o.width) { col = 0; row++; }
+    }
+}
 
 // ---- Im2col (37): z[b, c, kr, kc, oh, ow] = x[b, c, oh * sH - pH + kr * dH, ow * sW - pW + kc * dW] or the padding
-// value (special_ops.h:414-640). extraParams = {kH, kW, sH, sW, pH, pW, dH, dW, sameMode, padValue}.
+// value (special_ops.h:414-640). extraParams = {kH, kW, sH, sW, pH, pW, dH, dW, sameMode, padValue}; the padding
+// value is the one the reference's CUDA build uses (its CPU build always pads with zero). A thread owns one run
+// of positions of the (oh, ow) plane and writes it for every kernel tap, so an image element is fetched from
+// DRAM once and then found in L1 by the taps that follow.
 struct Im2colArgs {
     const void *x, *extra;
     void *z;
-    LL planes;                  // bS * iC * kH * kW
-    int iC, iH, iW, kH, kW, oH, oW;
-    LL xs[4], zs[6];
-    int iters;
+    unsigned planes;            // bS * iC
+    int iC, iH, iW, kH, kW;
+    LL xs[2], zs[4];            // strides of the outer axes
+    int xRow, xCol;             // strides of x's image axes
+    PlaneOut out;               // z's last two axes
 };
 
 template <class T>
-__global__ void __launch_bounds__(256) k_im2col(const Im2colArgs a) {
+__global__ void __launch_bounds__(256, 4) k_im2col(const Im2colArgs a) {
     grid_dependency_sync();
+    constexpr int V = Elem<T>::kVec;
     const T *extra = static_cast<const T *>(a.extra);
     const int sH = param_int(extra, 2), sW = param_int(extra, 3), pH = param_int(extra, 4), pW = param_int(extra, 5);
     const int dH = param_int(extra, 6), dW = param_int(extra, 7);
-    const T pad = extra[9];
-    const LL plane = (LL) blockIdx.x * blockDim.y + threadIdx.y;
-    if (plane >= a.planes) return;
-    const int kc = (int) (plane % a.kW);
-    LL t = plane / a.kW;
-    const int kr = (int) (t % a.kH);
-    t /= a.kH;
-    const int c = (int) (t % a.iC);
-    const LL b = t / a.iC;
-    const T *in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
-    T *out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1] + kr * a.zs[2] + kc * a.zs[3];
-    const int row0 = kr * dH - pH, col0 = kc * dW - pW;
-    const int positions = a.oH * a.oW;
-    const int stepRows = blockDim.x / a.oW, stepCols = blockDim.x % a.oW;
-    int p = blockIdx.y * (blockDim.x * a.iters) + threadIdx.x;
-    int oh = p / a.oW, ow = p - oh * a.oW;
-    for (int it = 0; it < a.iters && p < positions; it++) {
-        const int ih = row0 + oh * sH, iw = col0 + ow * sW;
-        const bool inside = (unsigned) ih < (unsigned) a.iH && (unsigned) iw < (unsigned) a.iW;
-        out[oh * a.zs[4] + ow * a.zs[5]] = inside ? in[ih * a.xs[2] + iw * a.xs[3]] : pad;
-        p += blockDim.x; oh += stepRows; ow += stepCols;
-        if (ow >= a.oW) { ow -= a.oW; oh++; }
+    const T pad = param(extra, 9);
+    const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
+    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (plane >= a.planes || p0 >= a.out.positions) return;
+    const unsigned c = plane % a.iC, b = plane / a.iC;
+    const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
+    T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
+    const int oh0 = p0 / a.out.width, ow0 = p0 - oh0 * a.out.width;
+    const bool oneRow = ow0 + V <= a.out.width;           // the run stays in one row of the plane (it then also
+                                                          // lies wholly inside the plane)
+    for (int kr = 0; kr < a.kH; kr++) {
+        const int ih0 = kr * dH - pH + oh0 * sH;
+#pragma unroll 3
+        for (int kc = 0; kc < a.kW; kc++) {
+            T vals[V];
+            if (oneRow) {
+                const bool rowInside = (unsigned) ih0 < (unsigned) a.iH;
+                const T *row = in + ih0 * a.xRow;
+                int iw = kc * dW - pW + ow0 * sW;
+#pragma unroll
+                for (int j = 0; j < V; j++, iw += sW)
+                    vals[j] = rowInside && (unsigned) iw < (unsigned) a.iW ? row[iw * a.xCol] : pad;
+            } else {
+                int oh = oh0, ow = ow0;
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const int ih = kr * dH - pH + oh * sH, iw = kc * dW - pW + ow * sW;
+                    const bool inside = p0 + j < a.out.positions && (unsigned) ih < (unsigned) a.iH && (unsigned) iw < (unsigned) a.iW;
+                    vals[j] = inside ? in[ih * a.xRow + iw * a.xCol] : pad;
+                    if (++ow == a.out.width) { ow = 0; oh++; }
+                }
+            }
+            store_run<T, V>(out + kr * a.zs[2] + kc * a.zs[3], a.out, p0, vals);
+        }
     }
 }
 
 // ---- Col2Im (36): z[b, c, h, w] = sum of x[b, c, kr, kc, oh, ow] over the (kr, kc, oh, ow) that im2col reads (h, w)
 // for (special_ops.h:891-1120). extraParams = {sH, sW, pH, pW, iH, iW, dH, dW}. The reference adds into the zeroed
 // image with kr outermost and kc next, so for one image element the order of the additions is (kr, kc) ascending;
-// the gather below adds in that order and is therefore identical bit for bit, without atomics.
+// the gather below adds in that order and is therefore identical bit for bit, without atomics. (The reference
+// zeroes the first `length` elements of the result buffer whatever its strides; here every element of the result,
+// dense or not, ends as its sum.)
 struct Col2imArgs {
     const void *x, *extra;
     void *z;
-    LL planes;                  // bS * iC
-    int iC, iH, iW, kH, kW, oH, oW;
-    LL xs[6], zs[4];
-    int iters;
+    unsigned planes;            // bS * iC
+    int iC, kH, kW, oH, oW;
+    LL xs[4], zs[2];            // strides of the outer axes (x: batch, channel, kernel row, kernel column)
+    int xRow, xCol;             // strides of x's last two axes
+    PlaneOut out;               // z's last two axes (the image)
 };
 
 template <class T>
-__global__ void __launch_bounds__(256) k_col2im(const Col2imArgs a) {
+__global__ void __launch_bounds__(256, 4) k_col2im(const Col2imArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
+    constexpr int V = Elem<T>::kVec;
     const T *extra = static_cast<const T *>(a.extra);
     const int sH = param_int(extra, 0), sW = param_int(extra, 1), pH = param_int(extra, 2), pW = param_int(extra, 3);
     const int dH = param_int(extra, 6), dW = param_int(extra, 7);
-    const LL plane = (LL) blockIdx.x * blockDim.y + threadIdx.y;
-    if (plane >= a.planes) return;
-    const int c = (int) (plane % a.iC);
-    const LL b = plane / a.iC;
-    const T *in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
-    T *out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
-    const int positions = a.iH * a.iW;
-    const int stepRows = blockDim.x / a.iW, stepCols = blockDim.x % a.iW;
-    int p = blockIdx.y * (blockDim.x * a.iters) + threadIdx.x;
-    int h = p / a.iW, w = p - h * a.iW;
-    for (int it = 0; it < a.iters && p < positions; it++) {
-        C sum = 0;
+    const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
+    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (plane >= a.planes || p0 >= a.out.positions) return;
+    const unsigned c = plane % a.iC, b = plane / a.iC;
+    const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
+    T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
+    const int h0 = p0 / a.out.width, w0 = p0 - h0 * a.out.width;
+    C sum[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) sum[j] = 0;
+    if (w0 + V <= a.out.width && sH == 1 && sW == 1) {
+        // unit strides and a run inside one image row: one row test per kernel row, no divisions
         for (int kr = 0; kr < a.kH; kr++) {
-            const int hh = h + pH - kr * dH;
-            if (hh < 0) break;                            // decreases with kr
-            const int oh = hh / sH;
-            if (oh * sH != hh || oh >= a.oH) continue;
-            const T *row = in + kr * a.xs[2] + oh * a.xs[4];
+            const int oh = h0 + pH - kr * dH;
+            if ((unsigned) oh >= (unsigned) a.oH) continue;
+            const T *row = in + kr * a.xs[2] + oh * a.xRow;
+#pragma unroll 3
             for (int kc = 0; kc < a.kW; kc++) {
-                const int ww = w + pW - kc * dW;
-                if (ww < 0) break;
-                const int ow = ww / sW;
-                if (ow * sW != ww || ow >= a.oW) continue;
-                sum += Elem<T>::load(row + kc * a.xs[3] + ow * a.xs[5]);
+                const T *tap = row + kc * a.xs[3];
+                const int ow0 = w0 + pW - kc * dW;
+#pragma unroll
+                for (int j = 0; j < V; j++)
+                    if ((unsigned) (ow0 + j) < (unsigned) a.oW) sum[j] += Elem<T>::load(tap + (ow0 + j) * a.xCol);
             }
         }
-        Elem<T>::store(out + h * a.zs[2] + w * a.zs[3], sum);
-        p += blockDim.x; h += stepRows; w += stepCols;
-        if (w >= a.iW) { w -= a.iW; h++; }
+    } else {
+        for (int kr = 0; kr < a.kH; kr++) {
+            for (int kc = 0; kc < a.kW; kc++) {
+                const T *tap = in + kr * a.xs[2] + kc * a.xs[3];
+                int h = h0, w = w0;
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const int hh = h + pH - kr * dH, ww = w + pW - kc * dW;
+                    const int oh = hh / sH, ow = ww / sW;
+                    const bool hit = p0 + j < a.out.positions && hh >= 0 && ww >= 0 && oh * sH == hh && ow * sW == ww &&
+                                     oh < a.oH && ow < a.oW;
+                    if (hit) sum[j] += Elem<T>::load(tap + oh * a.xRow + ow * a.xCol);
+                    if (++w == a.out.width) { w = 0; h++; }
+                }
+            }
+        }
     }
+    T vals[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) vals[j] = Elem<T>::from_c(sum[j]);
+    store_run<T, V>(out, a.out, p0, vals);
 }
 
 // ---- Pooling2D (71): max (mode 0), average (1) or p-norm (2) over the dilated window of every output position
 // (special_ops.h:31-330). extraParams = {kH, kW, sH, sW, pH, pW, dH, dW, -, mode, extra0}; extra0 is the divisor
-// rule of the average (0: positions inside the image, 1: kH * kW) or the p of the p-norm. The window is clipped to
-// the image by whole dilation steps, as the reference does. A c-order result is written densely behind the
-// (batch, channel) base, an f-order one through its last two strides (special_ops.h:321-325).
+// rule of the average (0: positions inside the image, 1: kH * kW) or the p of the p-norm. The reference clips the
+// window to the image by whole dilation steps, which leaves exactly the taps that lie inside the image, visited
+// row by row; the loop below visits the same taps in the same order. A c-order result is written densely behind
+// the (batch, channel) base, an f-order one through its last two strides (special_ops.h:321-325).
 struct PoolArgs {
     const void *x, *extra;
     void *z;
-    LL planes;                  // bS * iC
-    int iC, iH, iW, oH, oW;
-    LL xs[4], zs[4];
-    int fOrder;
-    int iters;
+    unsigned planes;            // bS * iC
+    int iC, iH, iW;
+    LL xs[2], zs[2];
+    int xRow, xCol;
+    PlaneOut out;
 };
 
-ND_D int ceil_div_pos(int a, int b) { return a > 0 ? (a + b - 1) / b : -((-a) / b); }   // ceil(a / b) for b > 0
+ND_D int ceil_div_int(int a, int b) { return a > 0 ? (a + b - 1) / b : -((-a) / b); }   // ceil(a / b) for b > 0
 
 template <class T>
-__global__ void __launch_bounds__(256) k_pooling2d(const PoolArgs a) {
+__global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
     grid_dependency_sync();
     typedef typename Elem<T>::C C;
+    constexpr int V = Elem<T>::kVec;
     const T *extra = static_cast<const T *>(a.extra);
     const int kH = param_int(extra, 0), kW = param_int(extra, 1), sH = param_int(extra, 2), sW = param_int(extra, 3);
     const int pH = param_int(extra, 4), pW = param_int(extra, 5), dH = param_int(extra, 6), dW = param_int(extra, 7);
     const int mode = param_int(extra, 9);
-    const C extra0 = Elem<T>::load(extra + 10);
-    const int kHEff = kH + (kH - 1) * (dH - 1), kWEff = kW + (kW - 1) * (dW - 1);
-    const LL plane = (LL) blockIdx.x * blockDim.y + threadIdx.y;
-    if (plane >= a.planes) return;
-    const int c = (int) (plane % a.iC);
-    const LL b = plane / a.iC;
-    const T *in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
-    T *out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
-    const int positions = a.oH * a.oW;
-    const int stepRows = blockDim.x / a.oW, stepCols = blockDim.x % a.oW;
-    int p = blockIdx.y * (blockDim.x * a.iters) + threadIdx.x;
-    int yy = p / a.oW, xx = p - yy * a.oW;
-    for (int it = 0; it < a.iters && p < positions; it++) {
-        int hstart = yy * sH - pH, wstart = xx * sW - pW;
-        int hend = hstart + kHEff, wend = wstart + kWEff;
-        if (hstart < 0) hstart += ceil_div_pos(-hstart, dH) * dH;
-        if (wstart < 0) wstart += ceil_div_pos(-wstart, dW) * dW;
-        if (hend > a.iH) hend -= ceil_div_pos(hend - a.iH, dH) * dH;
-        if (wend > a.iW) wend -= ceil_div_pos(wend - a.iW, dW) * dW;
-        C acc = mode == 0 ? (C) Elem<T>::to_c(Elem<T>::from_c((C) -1e37)) : (C) 0;   // -MAX_FLOAT in the element type
-        for (int ky = hstart; ky < hend; ky += dH) {
-            const T *row = in + ky * a.xs[2];
-            for (int kx = wstart; kx < wend; kx += dW) {
-                const C v = Elem<T>::load(row + kx * a.xs[3]);
-                if (mode == 0) { if (v > acc) acc = v; }
-                else if (mode == 1) acc += v;
-                else acc += pow(fabs(v), extra0);
+    const C extra0 = Elem<T>::to_c(param(extra, 10));
+    const C lowest = Elem<T>::to_c(Elem<T>::from_c((C) -1e37));        // -MAX_FLOAT in the element type
+    const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
+    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (plane >= a.planes || p0 >= a.out.positions) return;
+    const unsigned c = plane % a.iC, b = plane / a.iC;
+    const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
+    T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
+    const int yy0 = p0 / a.out.width, xx0 = p0 - yy0 * a.out.width;
+    if (mode == 2) {
+        // p-norm: one position at a time (the power's code, unrolled over a run's positions, would set the register
+        // count of the whole kernel)
+#pragma unroll 1
+        for (int p = p0; p < p0 + V && p < a.out.positions; p++) {
+            const int yy = p / a.out.width, xx = p - yy * a.out.width;
+            C acc = 0;
+            for (int i = 0; i < kH; i++) {
+                for (int k = 0; k < kW; k++) {
+                    const int ky = yy * sH - pH + i * dH, kx = xx * sW - pW + k * dW;
+                    if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW)
+                        acc += pow(fabs(Elem<T>::load(in + ky * a.xRow + kx * a.xCol)), extra0);
+                }
+            }
+            Elem<T>::store(out + (a.out.dense ? p : yy * a.out.sRow + xx * a.out.sCol), pow(acc, (C) 1 / extra0));
+        }
+        return;
+    }
+    // top-left tap of every position's window; a position past the plane's end gets a window wholly above the image
+    int hs[V], ws[V];
+    C acc[V];
+    {
+        int yy = yy0, xx = xx0;
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+            hs[j] = p0 + j < a.out.positions ? yy * sH - pH : -(kH * dH + 1); ws[j] = xx * sW - pW;
+            acc[j] = mode == 0 ? lowest : (C) 0;
+            if (++xx == a.out.width) { xx = 0; yy++; }
+        }
+    }
+    if (xx0 + V <= a.out.width) {
+        // the run stays in one row of the result: its windows share their image rows
+        for (int i = 0; i < kH; i++) {
+            const int ky = hs[0] + i * dH;
+            if ((unsigned) ky >= (unsigned) a.iH) continue;
+            const T *row = in + ky * a.xRow;
+#pragma unroll 3
+            for (int k = 0; k < kW; k++) {
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const int kx = ws[j] + k * dW;
+                    if ((unsigned) kx < (unsigned) a.iW) {
+                        const C v = Elem<T>::load(row + kx * a.xCol);
+                        if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                        else acc[j] += v;
+                    }
+                }
             }
         }
+    } else {
+        for (int i = 0; i < kH; i++) {
+            for (int k = 0; k < kW; k++) {
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const int ky = hs[j] + i * dH, kx = ws[j] + k * dW;
+                    if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW) {
+                        const C v = Elem<T>::load(in + ky * a.xRow + kx * a.xCol);
+                        if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                        else acc[j] += v;
+                    }
+                }
+            }
+        }
+    }
+    T vals[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        C res = acc[j];
         if (mode == 1) {
             int divisor = 0;
             if ((int) extra0 == 0) {
-                divisor = ceil_div_pos(hend - hstart, dH) * ceil_div_pos(wend - wstart, dW);
+                // the window as the reference clips it (special_ops.h:236-262)
+                int hstart = hs[j], wstart = ws[j];
+                int hend = hstart + kH + (kH - 1) * (dH - 1), wend = wstart + kW + (kW - 1) * (dW - 1);
+                if (hstart < 0) hstart += ceil_div_int(-hstart, dH) * dH;
+                if (wstart < 0) wstart += ceil_div_int(-wstart, dW) * dW;
+                if (hend > a.iH) hend -= ceil_div_int(hend - a.iH, dH) * dH;
+                if (wend > a.iW) wend -= ceil_div_int(wend - a.iW, dW) * dW;
+                divisor = ceil_div_int(hend - hstart, dH) * ceil_div_int(wend - wstart, dW);
             } else if ((int) extra0 == 1) divisor = kH * kW;
-            acc = acc / (C) divisor;
-        } else if (mode == 2) acc = pow(acc, (C) 1 / extra0);
-        const LL at = a.fOrder ? yy * a.zs[2] + xx * a.zs[3] : (LL) p;
-        Elem<T>::store(out + at, acc);
-        p += blockDim.x; yy += stepRows; xx += stepCols;
-        if (xx >= a.oW) { xx -= a.oW; yy++; }
+            res = res / (C) divisor;
+        }
+        vals[j] = Elem<T>::from_c(res);
     }
+    store_run<T, V>(out, a.out, p0, vals);
 }
 
 // ---- Histogram (48): z[i] += number of x whose bin is i, bin = (int) ((x - min) / binSize) clamped to
 // [0, numBins), binSize = (max - min) / numBins (special_ops.h:713-880). extraParams = {numBins, min, max}. x is
 // read as one dense run of its length, as the reference does. Counts are integers (shared-memory counters per
-// CTA, then one global atomic per CTA and bin) and enter z in a second launch, so the result does not depend
-// on scheduling.
+// CTA, several copies of a small table so that neighbouring warps do not meet in one counter, then one global
+// atomic per CTA and bin) and enter z in a second launch, so the result does not depend on scheduling.
 struct HistArgs {
     const void *x, *extra;
     void *z;
     unsigned *counts;           // zLength zeroed words
     LL n, zLength;
+    int copies;                 // tables per CTA (a power of two, copies * zLength <= kHistShared), 0: global counters
+    int vec;                    // x may be read as 128-bit words
 };
 
-constexpr int kHistShared = 8192;                            // bins kept in shared memory
+constexpr int kHistShared = 8192;                            // counters kept in shared memory
 
 template <class T> ND_D T hist_sub(T a, T b) { return a - b; }
 template <class T> ND_D T hist_div(T a, T b) { return a / b; }
@@ -228,29 +362,50 @@ template <> ND_D int hist_int(__half v) { return (int) __half2float(v); }
 template <class T>
 __global__ void __launch_bounds__(256) k_histogram(const HistArgs a) {
     grid_dependency_sync();
+    constexpr int V = Elem<T>::kVec;
     __shared__ unsigned bins[kHistShared];
     const T *extra = static_cast<const T *>(a.extra);
     const int numBins = hist_int(extra[0]);
     const T lo = extra[1], hi = extra[2];
     const T binSize = hist_div(hist_sub(hi, lo), Elem<T>::from_c((typename Elem<T>::C) numBins));
-    const bool useShared = a.zLength <= kHistShared;
-    if (useShared) {
-        for (LL i = threadIdx.x; i < a.zLength; i += blockDim.x) bins[i] = 0;
-        __syncthreads();
-    }
-    const T *x = static_cast<const T *>(a.x);
-    for (LL i = (LL) blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (LL) gridDim.x * blockDim.x) {
-        int idx = hist_int(hist_div(hist_sub(x[i], lo), binSize));
+    const int tables = a.copies * (int) a.zLength;
+    for (int i = threadIdx.x; i < tables; i += blockDim.x) bins[i] = 0;
+    __syncthreads();
+    unsigned *mine = a.copies ? bins + ((threadIdx.x >> 5) & (a.copies - 1)) * a.zLength : a.counts;
+    auto count = [&](T v) {
+        int idx = hist_int(hist_div(hist_sub(v, lo), binSize));
         if (idx < 0) idx = 0;
         else if (idx >= numBins) idx = numBins - 1;
-        if (idx < 0 || idx >= a.zLength) continue;            // numBins beyond the result: nowhere to count
-        if (useShared) atomicAdd(&bins[idx], 1u);
-        else atomicAdd(a.counts + idx, 1u);
+        if (idx >= 0 && idx < a.zLength) atomicAdd(mine + idx, 1u);          // numBins beyond the result: nowhere to count
+    };
+    const T *__restrict__ x = static_cast<const T *>(a.x);
+    const LL tid = (LL) blockIdx.x * blockDim.x + threadIdx.x, threads = (LL) gridDim.x * blockDim.x;
+    if (a.vec) {
+        const LL packs = a.n / V;
+        LL i = tid;
+        for (; i + threads < packs; i += 2 * threads) {                       // two words in flight
+            const Pack<T> p = load_pack(x + i * V), q = load_pack(x + (i + threads) * V);
+#pragma unroll
+            for (int j = 0; j < V; j++) count(p.v[j]);
+#pragma unroll
+            for (int j = 0; j < V; j++) count(q.v[j]);
+        }
+        if (i < packs) {
+            const Pack<T> p = load_pack(x + i * V);
+#pragma unroll
+            for (int j = 0; j < V; j++) count(p.v[j]);
+        }
+        for (LL e = packs * V + tid; e < a.n; e += threads) count(x[e]);
+    } else {
+        for (LL e = tid; e < a.n; e += threads) count(x[e]);
     }
-    if (useShared) {
+    if (a.copies) {
         __syncthreads();
-        for (LL i = threadIdx.x; i < a.zLength; i += blockDim.x)
-            if (bins[i]) atomicAdd(a.counts + i, bins[i]);
+        for (int i = threadIdx.x; i < (int) a.zLength; i += blockDim.x) {
+            unsigned s = 0;
+            for (int c = 0; c < a.copies; c++) s += bins[c * a.zLength + i];
+            if (s) atomicAdd(a.counts + i, s);
+        }
     }
 }
 
@@ -258,9 +413,8 @@ template <class T>
 __global__ void __launch_bounds__(256) k_histogram_add(const HistArgs a) {
     grid_dependency_sync();
     T *z = static_cast<T *>(a.z);
-    for (LL i = (LL) blockIdx.x * blockDim.x + threadIdx.x; i < a.zLength; i += (LL) gridDim.x * blockDim.x) {
+    for (LL i = (LL) blockIdx.x * blockDim.x + threadIdx.x; i < a.zLength; i += (LL) gridDim.x * blockDim.x)
         Elem<T>::store(z + i, Elem<T>::load(z + i) + (typename Elem<T>::C) a.counts[i]);
-    }
 }
 
 // ---- Reverse (70): z at linear position n - 1 - e of its own order = x at linear position e of its own order
@@ -274,20 +428,80 @@ struct ReverseArgs {
     int swap;
 };
 
+// Any layout: four elements per thread and trip, all loads ahead of the stores.
 template <class T>
 __global__ void __launch_bounds__(256) k_reverse(const ReverseArgs a) {
     grid_dependency_sync();
     const T *x = static_cast<const T *>(a.x);
     T *z = static_cast<T *>(a.z);
-    for (LL e = (LL) blockIdx.x * blockDim.x + threadIdx.x; e < a.count; e += (LL) gridDim.x * blockDim.x) {
-        const LL from = view_offset(a.vx, e), to = view_offset(a.vz, a.n - 1 - e);
-        if (a.swap) {
-            const T lowV = z[from], highV = z[to];
-            z[from] = highV; z[to] = lowV;
-        } else {
-            z[to] = x[from];
+    const LL threads = (LL) gridDim.x * blockDim.x;
+    for (LL e0 = (LL) blockIdx.x * blockDim.x + threadIdx.x; e0 < a.count; e0 += 4 * threads) {
+        LL from[4], to[4];
+        T low[4], high[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const LL e = e0 + u * threads;
+            const bool live = e < a.count;
+            from[u] = live ? view_offset(a.vx, e) : -1;
+            to[u] = live ? view_offset(a.vz, a.n - 1 - e) : -1;
+            if (live) { low[u] = x[from[u]]; if (a.swap) high[u] = z[to[u]]; }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (from[u] < 0) continue;
+            z[to[u]] = low[u];
+            if (a.swap) z[from[u]] = high[u];
         }
     }
+}
+
+// Both arrays dense, their ends 16-byte aligned and the length a multiple of the word: 128-bit words, the elements
+// of a word turned round in registers. count = words to read (all of them, or half in place, where a word and its
+// mirror are exchanged; with an odd number of words the middle one is its own mirror).
+template <class T>
+__global__ void __launch_bounds__(256) k_reverse_words(const ReverseArgs a) {
+    grid_dependency_sync();
+    constexpr int V = Elem<T>::kVec;
+    const T *x = static_cast<const T *>(a.x);
+    T *z = static_cast<T *>(a.z);
+    const LL words = a.n / V, threads = (LL) gridDim.x * blockDim.x;
+    auto turned = [](const Pack<T> &p) {
+        Pack<T> r;
+#pragma unroll
+        for (int j = 0; j < V; j++) r.v[j] = p.v[V - 1 - j];
+        return r;
+    };
+    for (LL i0 = (LL) blockIdx.x * blockDim.x + threadIdx.x; i0 < a.count; i0 += 2 * threads) {
+        const LL i1 = i0 + threads;
+        const bool two = i1 < a.count;
+        const Pack<T> p0 = load_pack_rw(x + i0 * V), p1 = load_pack_rw(x + (two ? i1 : i0) * V);
+        Pack<T> m0, m1;
+        if (a.swap) { m0 = load_pack_rw(z + (words - 1 - i0) * V); m1 = load_pack_rw(z + (words - 1 - (two ? i1 : i0)) * V); }
+        store_pack(z + (words - 1 - i0) * V, turned(p0));
+        if (a.swap) store_pack(z + i0 * V, turned(m0));
+        if (two) {
+            store_pack(z + (words - 1 - i1) * V, turned(p1));
+            if (a.swap) store_pack(z + i1 * V, turned(m1));
+        }
+    }
+}
+
+// The last two axes of an array as a plane: dense when position p lies at offset p; 128-bit stores need every
+// plane to start on a 16-byte boundary as well (the buffer and all outer strides).
+template <class T>
+PlaneOut plane_out(const void *base, LL rows, LL cols, LL sRow, LL sCol, const LL *outer, int nOuter) {
+    PlaneOut o;
+    o.sRow = (int) sRow; o.sCol = (int) sCol; o.width = (int) cols; o.positions = (int) (rows * cols);
+    bool dense = sCol == 1 && (sRow == cols || rows == 1) && aligned16(base);
+    for (int i = 0; i < nOuter; i++) dense = dense && outer[i] % Elem<T>::kVec == 0;
+    o.dense = dense;
+    return o;
+}
+
+// Offsets inside a plane are computed in 32 bits.
+inline bool plane_fits(LL rows, LL cols, LL sRow, LL sCol) {
+    auto mag = [](LL v) { return v < 0 ? -v : v; };
+    return rows * cols < (1LL << 30) && rows * mag(sRow) + cols * mag(sCol) < (1LL << 30);
 }
 
 template <class T>
@@ -315,16 +529,22 @@ Status special_transform_typed(int opNum, const void *x, const ShapeDesc &xd, vo
             if (xd.rank != 4 || zd.rank != 6) return bad_arg("Im2col: x must have rank 4 [b, c, h, w] and z rank 6 [b, c, kH, kW, oH, oW]");
             if (xd.shape[0] != zd.shape[0] || xd.shape[1] != zd.shape[1]) return bad_arg("Im2col: x and z differ in batch size or channels");
             if (zd.length == 0) return kOk;
-            if (!fits_int(zd.shape[4] * zd.shape[5]) || !fits_int(xd.shape[2] * xd.shape[3])) { set_error("Im2col: an image plane of 2^31 or more positions"); return kTooLarge; }
+            LL zs[6];
+            strides(zd, zs);
+            if (descending_c(xd) && descending_c(zd)) dense_behind_batch(zd, 1, zs);
+            if (!fits_int(xd.shape[0] * xd.shape[1] * zd.shape[2] * zd.shape[3]) ||
+                !plane_fits(xd.shape[2], xd.shape[3], xd.stride[2], xd.stride[3]) || !plane_fits(zd.shape[4], zd.shape[5], zs[4], zs[5])) {
+                set_error("Im2col: 2^31 or more planes, or a plane that spans 2^30 or more elements"); return kTooLarge;
+            }
             Im2colArgs a;
             a.x = x; a.z = z; a.extra = extra;
             a.iC = (int) xd.shape[1]; a.iH = (int) xd.shape[2]; a.iW = (int) xd.shape[3];
-            a.kH = (int) zd.shape[2]; a.kW = (int) zd.shape[3]; a.oH = (int) zd.shape[4]; a.oW = (int) zd.shape[5];
-            a.planes = xd.shape[0] * xd.shape[1] * zd.shape[2] * zd.shape[3];
-            strides(xd, a.xs); strides(zd, a.zs);
-            if (descending_c(xd) && descending_c(zd)) dense_behind_batch(zd, 1, a.zs);
-            const PlaneGrid g = plane_grid(a.planes, (LL) a.oH * a.oW);
-            a.iters = g.iters;
+            a.kH = (int) zd.shape[2]; a.kW = (int) zd.shape[3];
+            a.planes = (unsigned) (xd.shape[0] * xd.shape[1]);
+            a.xs[0] = xd.stride[0]; a.xs[1] = xd.stride[1]; a.xRow = (int) xd.stride[2]; a.xCol = (int) xd.stride[3];
+            for (int i = 0; i < 4; i++) a.zs[i] = zs[i];
+            a.out = plane_out<T>(z, zd.shape[4], zd.shape[5], zs[4], zs[5], zs, 4);
+            const PlaneGrid g = plane_grid(a.planes, (LL) a.out.positions, Elem<T>::kVec);
             launch_kernel(k_im2col<T>, dim3(g.gx, g.gy), dim3(g.tx, g.ty), st, a);
             break;
         }
@@ -332,16 +552,23 @@ Status special_transform_typed(int opNum, const void *x, const ShapeDesc &xd, vo
             if (xd.rank != 6 || zd.rank != 4) return bad_arg("Col2Im: x must have rank 6 [b, c, kH, kW, oH, oW] and z rank 4 [b, c, h, w]");
             if (xd.shape[0] != zd.shape[0] || xd.shape[1] != zd.shape[1]) return bad_arg("Col2Im: x and z differ in batch size or channels");
             if (zd.length == 0) return kOk;
-            if (!fits_int(zd.shape[2] * zd.shape[3]) || !fits_int(xd.shape[4] * xd.shape[5])) { set_error("Col2Im: an image plane of 2^31 or more positions"); return kTooLarge; }
+            LL xs[6];
+            strides(xd, xs);
+            if (descending_c(xd) && descending_c(zd)) dense_behind_batch(xd, xd.stride[5], xs);
+            if (!fits_int(zd.shape[0] * zd.shape[1]) || !plane_fits(zd.shape[2], zd.shape[3], zd.stride[2], zd.stride[3]) ||
+                !plane_fits(xd.shape[4], xd.shape[5], xs[4], xs[5])) {
+                set_error("Col2Im: 2^31 or more planes, or a plane that spans 2^30 or more elements"); return kTooLarge;
+            }
             Col2imArgs a;
             a.x = x; a.z = z; a.extra = extra;
-            a.iC = (int) zd.shape[1]; a.iH = (int) zd.shape[2]; a.iW = (int) zd.shape[3];
+            a.iC = (int) zd.shape[1];
             a.kH = (int) xd.shape[2]; a.kW = (int) xd.shape[3]; a.oH = (int) xd.shape[4]; a.oW = (int) xd.shape[5];
-            a.planes = zd.shape[0] * zd.shape[1];
-            strides(xd, a.xs); strides(zd, a.zs);
-            if (descending_c(xd) && descending_c(zd)) dense_behind_batch(xd, xd.stride[5], a.xs);
-            const PlaneGrid g = plane_grid(a.planes, (LL) a.iH * a.iW);
-            a.iters = g.iters;
+            a.planes = (unsigned) (zd.shape[0] * zd.shape[1]);
+            for (int i = 0; i < 4; i++) a.xs[i] = xs[i];
+            a.xRow = (int) xs[4]; a.xCol = (int) xs[5];
+            a.zs[0] = zd.stride[0]; a.zs[1] = zd.stride[1];
+            a.out = plane_out<T>(z, zd.shape[2], zd.shape[3], zd.stride[2], zd.stride[3], zd.stride, 2);
+            const PlaneGrid g = plane_grid(a.planes, (LL) a.out.positions, Elem<T>::kVec);
             launch_kernel(k_col2im<T>, dim3(g.gx, g.gy), dim3(g.tx, g.ty), st, a);
             break;
         }
@@ -349,16 +576,20 @@ Status special_transform_typed(int opNum, const void *x, const ShapeDesc &xd, vo
             if (xd.rank != 4 || zd.rank != 4) return bad_arg("Pooling2D: x and z must have rank 4 [b, c, h, w]");
             if (xd.shape[0] != zd.shape[0] || xd.shape[1] != zd.shape[1]) return bad_arg("Pooling2D: x and z differ in batch size or channels");
             if (zd.length == 0) return kOk;
-            if (!fits_int(zd.shape[2] * zd.shape[3]) || !fits_int(xd.shape[2] * xd.shape[3])) { set_error("Pooling2D: an image plane of 2^31 or more positions"); return kTooLarge; }
+            LL zRow = zd.stride[2], zCol = zd.stride[3];
+            if (zd.order != 'f') { zCol = 1; zRow = zd.shape[3]; }          // written densely behind the plane's base
+            if (!fits_int(xd.shape[0] * xd.shape[1]) || !plane_fits(xd.shape[2], xd.shape[3], xd.stride[2], xd.stride[3]) ||
+                !plane_fits(zd.shape[2], zd.shape[3], zRow, zCol)) {
+                set_error("Pooling2D: 2^31 or more planes, or a plane that spans 2^30 or more elements"); return kTooLarge;
+            }
             PoolArgs a;
             a.x = x; a.z = z; a.extra = extra;
             a.iC = (int) xd.shape[1]; a.iH = (int) xd.shape[2]; a.iW = (int) xd.shape[3];
-            a.oH = (int) zd.shape[2]; a.oW = (int) zd.shape[3];
-            a.planes = xd.shape[0] * xd.shape[1];
-            a.fOrder = zd.order == 'f';
-            strides(xd, a.xs); strides(zd, a.zs);
-            const PlaneGrid g = plane_grid(a.planes, (LL) a.oH * a.oW);
-            a.iters = g.iters;
+            a.planes = (unsigned) (xd.shape[0] * xd.shape[1]);
+            a.xs[0] = xd.stride[0]; a.xs[1] = xd.stride[1]; a.xRow = (int) xd.stride[2]; a.xCol = (int) xd.stride[3];
+            a.zs[0] = zd.stride[0]; a.zs[1] = zd.stride[1];
+            a.out = plane_out<T>(z, zd.shape[2], zd.shape[3], zRow, zCol, zd.stride, 2);
+            const PlaneGrid g = plane_grid(a.planes, (LL) a.out.positions, Elem<T>::kVec);
             launch_kernel(k_pooling2d<T>, dim3(g.gx, g.gy), dim3(g.tx, g.ty), st, a);
             break;
         }
@@ -371,6 +602,9 @@ Status special_transform_typed(int opNum, const void *x, const ShapeDesc &xd, vo
             ND_TRY(workspace(st, kWorkspaceScratch + (size_t) zd.length * sizeof(unsigned), &ws, nullptr));
             a.counts = reinterpret_cast<unsigned *>(static_cast<char *>(ws) + kWorkspaceScratch);
             ND_CUDA(cudaMemsetAsync(a.counts, 0, (size_t) zd.length * sizeof(unsigned), st));
+            a.copies = 0;
+            if (zd.length <= kHistShared) { a.copies = 1; while (a.copies < 8 && a.copies * 2 * zd.length <= kHistShared) a.copies *= 2; }
+            a.vec = aligned16(x);
             LL blocks = ceil_div(xd.length, (LL) 256 * 16);
             if (blocks > (LL) kNumSMs * 8) blocks = (LL) kNumSMs * 8;
             launch_kernel(k_histogram<T>, dim3((unsigned) blocks), dim3(256), st, a);
@@ -402,6 +636,17 @@ Status special_transform_typed(int opNum, const void *x, const ShapeDesc &xd, vo
                 a.swap = 0;
             }
             if (a.count == 0) return kOk;
+            constexpr int V = Elem<T>::kVec;
+            if (xd.ews == 1 && zd.ews == 1 && (x == z || xd.order == zd.order || xd.rank <= 1) && xd.length % V == 0 &&
+                aligned16(x) && aligned16(z)) {
+                const LL words = xd.length / V;
+                a.swap = x == z;
+                a.count = a.swap ? (words + 1) / 2 : words;
+                LL blocks = ceil_div(a.count, (LL) 256 * 2);
+                if (blocks > (LL) kNumSMs * 16) blocks = (LL) kNumSMs * 16;
+                launch_kernel(k_reverse_words<T>, dim3((unsigned) blocks), dim3(256), st, a);
+                break;
+            }
             LL blocks = ceil_div(a.count, (LL) 256 * 4);
             if (blocks > (LL) kNumSMs * 16) blocks = (LL) kNumSMs * 16;
             launch_kernel(k_reverse<T>, dim3((unsigned) blocks), dim3(256), st, a);
