@@ -108,7 +108,16 @@ int nd4jb200_exec_reduce3_scalar(void *stream, int dtype, int opNum, const void 
                                  double *result);
 
 /* ---- transform: NativeOps::execTransform* shaped and strided (blas/NativeOps.h:1337-1443;
- *      blas/cuda/NativeOps.cu:3033-3343) -------------------------------------------------------- */
+ *      blas/cuda/NativeOps.cu:3033-3343) --------------------------------------------------------
+ * The shaped call also serves the whole-array ("special") transforms of include/ops/special_ops.h, where x and z
+ * may differ in shape: SoftMax 38, SoftMaxDerivative 39, LogSoftMax 40, IsMax 41 and
+ *   Col2Im 36    x [b, c, kH, kW, oH, oW] -> z [b, c, h, w]; extraParams {sH, sW, pH, pW, h, w, dH, dW}
+ *   Im2col 37    x [b, c, h, w] -> z [b, c, kH, kW, oH, oW]; extraParams {kH, kW, sH, sW, pH, pW, dH, dW, -, padValue}
+ *   Histogram 48 x dense -> z [numBins] (added to); extraParams {numBins, min, max}
+ *   Reverse 70   z at linear position n - 1 - e = x at linear position e; no extraParams
+ *   Pooling2D 71 x [b, c, h, w] -> z [b, c, oH, oW]; extraParams {kH, kW, sH, sW, pH, pW, dH, dW, -, mode, extra0},
+ *                mode 0 max, 1 average (extra0 0: divide by the taps inside the image, 1: by kH * kW), 2 p-norm (p = extra0)
+ * extraParams is a device pointer to values of the element type, as in the reference. */
 int nd4jb200_exec_transform(void *stream, int dtype, int opNum, const void *x, const Nd4jLong *xShapeInfo,
                             void *z, const Nd4jLong *zShapeInfo, const void *extraParams);
 int nd4jb200_exec_transform_strided(void *stream, int dtype, int opNum, const void *x, Nd4jLong xStride,
