@@ -334,8 +334,11 @@ def test_errors_are_reported_not_fatal(ops):
         ops.execTransformFloat(None, 57, x, info, x, info, None)   # hole in the transform table
     assert e.value.code == 2
     with pytest.raises(Nd4jError) as e:
-        ops.execTransformFloat(None, 36, x, info, x, info, None)   # a composite transform that is not served
+        ops.execTransformFloat(None, 43, x, info, x, info, None)   # DropOut by rand(): recognised, not served
     assert e.value.code == 3
+    with pytest.raises(Nd4jError) as e:
+        ops.execTransformFloat(None, 36, x, info, x, info, None)   # Col2Im wants a six-axis x
+    assert e.value.code == 1
     with pytest.raises(Nd4jError) as e:
         ops.execPairwiseTransformFloat(None, 0, x, info, x, S.shape_info([3, 3]), x, info, None)
     assert e.value.code == 1
