@@ -28,8 +28,10 @@ struct PlaneGrid {
     unsigned gx, gy;     // gridDim: planes / ty, chunks of runs
 };
 
+constexpr int kRunsPerThread = 1;      // 4 was measured: no gain for Im2col and Pooling2D, Col2Im 0.079 against 0.075 ms
+
 inline PlaneGrid plane_grid(LL planes, LL positions, int v) {
-    const LL runs = ceil_div(positions, (LL) v);
+    const LL runs = ceil_div(ceil_div(positions, (LL) v), (LL) kRunsPerThread);      // per thread: kRunsPerThread of them
     PlaneGrid g;
     // the CTA width (a multiple of a warp) that leaves the fewest idle threads in a plane's last chunk; ties go to
     // the wider CTA
@@ -105,39 +107,93 @@ __global__ void __launch_bounds__(256, 4) k_im2col(const Im2colArgs a) {
     const int dH = param_int(extra, 6), dW = param_int(extra, 7);
     const T pad = param(extra, 9);
     const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
-    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    if (plane >= a.planes || p0 >= a.out.positions) return;
+    if (plane >= a.planes) return;
     const unsigned c = plane % a.iC, b = plane / a.iC;
     const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
     T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
-    const int oh0 = p0 / a.out.width, ow0 = p0 - oh0 * a.out.width;
-    const bool oneRow = ow0 + V <= a.out.width;           // the run stays in one row of the plane (it then also
-                                                          // lies wholly inside the plane)
-    for (int kr = 0; kr < a.kH; kr++) {
-        const int ih0 = kr * dH - pH + oh0 * sH;
-#pragma unroll 3
-        for (int kc = 0; kc < a.kW; kc++) {
-            T vals[V];
-            if (oneRow) {
-                const bool rowInside = (unsigned) ih0 < (unsigned) a.iH;
-                const T *row = in + ih0 * a.xRow;
-                int iw = kc * dW - pW + ow0 * sW;
+    // a thread takes every stride-th run of the plane, so that what it derives once (the geometry, the plane) serves
+    // several runs
+    auto run = [&](const int p0) {
+        const int oh0 = p0 / a.out.width, ow0 = p0 - oh0 * a.out.width;
+        const bool oneRow = ow0 + V <= a.out.width;           // the run stays in one row of the plane (it then also
+                                                              // lies wholly inside the plane)
+        // Interior: the run stays in one row and every tap of every position lies inside the image. Then nothing is
+        // tested per element, and a tap is a few loads at a fixed step and one store.
+        const int top = oh0 * sH - pH, left = ow0 * sW - pW;
+        // Unit stride and dilation along contiguous image rows (the usual convolution): the kW taps of a kernel row read
+        // overlapping pieces of one span of V + kW - 1 image elements, so the span is loaded once per kernel row
+        // (elements outside the image become the padding value) and every tap's run is cut out of it in registers.
+        // The choice is the same for all threads of a warp, so no warp runs two forms of the loop.
+        constexpr int kMaxSpanTaps = 7;
+        if (sW == 1 && dW == 1 && a.xCol == 1 && a.kW <= kMaxSpanTaps && a.out.dense && __all_sync(__activemask(), oneRow)) {
+            for (int kr = 0; kr < a.kH; kr++) {
+                const int ih = top + kr * dH;
+                const bool rowInside = (unsigned) ih < (unsigned) a.iH;
+                const T *row = in + ih * a.xRow + left;
+                T span[V + kMaxSpanTaps - 1];
 #pragma unroll
-                for (int j = 0; j < V; j++, iw += sW)
-                    vals[j] = rowInside && (unsigned) iw < (unsigned) a.iW ? row[iw * a.xCol] : pad;
-            } else {
-                int oh = oh0, ow = ow0;
+                for (int t = 0; t < V + kMaxSpanTaps - 1; t++) {
+                    const bool ok = rowInside && t < V + a.kW - 1 && (unsigned) (left + t) < (unsigned) a.iW;
+                    span[t] = ok ? row[t] : pad;
+                }
+                T *dst = out + kr * a.zs[2] + p0;
 #pragma unroll
-                for (int j = 0; j < V; j++) {
-                    const int ih = kr * dH - pH + oh * sH, iw = kc * dW - pW + ow * sW;
-                    const bool inside = p0 + j < a.out.positions && (unsigned) ih < (unsigned) a.iH && (unsigned) iw < (unsigned) a.iW;
-                    vals[j] = inside ? in[ih * a.xRow + iw * a.xCol] : pad;
-                    if (++ow == a.out.width) { ow = 0; oh++; }
+                for (int kc = 0; kc < kMaxSpanTaps; kc++) {
+                    if (kc < a.kW) {
+                        Pack<T> pk;
+#pragma unroll
+                        for (int j = 0; j < V; j++) pk.v[j] = span[kc + j];
+                        store_pack(dst + kc * a.zs[3], pk);
+                    }
                 }
             }
-            store_run<T, V>(out + kr * a.zs[2] + kc * a.zs[3], a.out, p0, vals);
+            return;
         }
-    }
+        const bool interior = oneRow && a.out.dense && top >= 0 && top + (a.kH - 1) * dH < a.iH && left >= 0 &&
+                              left + (V - 1) * sW + (a.kW - 1) * dW < a.iW && dH >= 0 && dW >= 0 && sW >= 0;
+        if (__all_sync(__activemask(), interior)) {            // taken by whole warps only: no warp runs both forms
+            const int step = sW * a.xCol;
+            for (int kr = 0; kr < a.kH; kr++) {
+                const T *row = in + (top + kr * dH) * a.xRow + left * a.xCol;
+                T *dst = out + kr * a.zs[2] + p0;
+#pragma unroll 3
+                for (int kc = 0; kc < a.kW; kc++) {
+                    const T *src = row + kc * dW * a.xCol;
+                    Pack<T> pk;
+#pragma unroll
+                    for (int j = 0; j < V; j++) pk.v[j] = src[j * step];
+                    store_pack(dst + kc * a.zs[3], pk);
+                }
+            }
+            return;
+        }
+        for (int kr = 0; kr < a.kH; kr++) {
+            const int ih0 = kr * dH - pH + oh0 * sH;
+#pragma unroll 3
+            for (int kc = 0; kc < a.kW; kc++) {
+                T vals[V];
+                if (oneRow) {
+                    const bool rowInside = (unsigned) ih0 < (unsigned) a.iH;
+                    const T *row = in + ih0 * a.xRow;
+                    int iw = kc * dW - pW + ow0 * sW;
+#pragma unroll
+                    for (int j = 0; j < V; j++, iw += sW)
+                        vals[j] = rowInside && (unsigned) iw < (unsigned) a.iW ? row[iw * a.xCol] : pad;
+                } else {
+                    int oh = oh0, ow = ow0;
+#pragma unroll
+                    for (int j = 0; j < V; j++) {
+                        const int ih = kr * dH - pH + oh * sH, iw = kc * dW - pW + ow * sW;
+                        const bool inside = p0 + j < a.out.positions && (unsigned) ih < (unsigned) a.iH && (unsigned) iw < (unsigned) a.iW;
+                        vals[j] = inside ? in[ih * a.xRow + iw * a.xCol] : pad;
+                        if (++ow == a.out.width) { ow = 0; oh++; }
+                    }
+                }
+                store_run<T, V>(out + kr * a.zs[2] + kc * a.zs[3], a.out, p0, vals);
+            }
+        }
+    };
+    for (int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; p0 < a.out.positions; p0 += gridDim.y * blockDim.x * V) run(p0);
 }
 
 // ---- Col2Im (36): z[b, c, h, w] = sum of x[b, c, kr, kc, oh, ow] over the (kr, kc, oh, ow) that im2col reads (h, w)
@@ -165,51 +221,55 @@ __global__ void __launch_bounds__(256, 4) k_col2im(const Col2imArgs a) {
     const int sH = param_int(extra, 0), sW = param_int(extra, 1), pH = param_int(extra, 2), pW = param_int(extra, 3);
     const int dH = param_int(extra, 6), dW = param_int(extra, 7);
     const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
-    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    if (plane >= a.planes || p0 >= a.out.positions) return;
+    if (plane >= a.planes) return;
     const unsigned c = plane % a.iC, b = plane / a.iC;
     const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
     T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
-    const int h0 = p0 / a.out.width, w0 = p0 - h0 * a.out.width;
-    C sum[V];
+    // a thread takes every stride-th run of the plane, so that what it derives once (the geometry, the plane) serves
+    // several runs
+    auto run = [&](const int p0) {
+        const int h0 = p0 / a.out.width, w0 = p0 - h0 * a.out.width;
+        C sum[V];
 #pragma unroll
-    for (int j = 0; j < V; j++) sum[j] = 0;
-    if (w0 + V <= a.out.width && sH == 1 && sW == 1) {
-        // unit strides and a run inside one image row: one row test per kernel row, no divisions
-        for (int kr = 0; kr < a.kH; kr++) {
-            const int oh = h0 + pH - kr * dH;
-            if ((unsigned) oh >= (unsigned) a.oH) continue;
-            const T *row = in + kr * a.xs[2] + oh * a.xRow;
+        for (int j = 0; j < V; j++) sum[j] = 0;
+        if (w0 + V <= a.out.width && sH == 1 && sW == 1) {
+            // unit strides and a run inside one image row: one row test per kernel row, no divisions
+            for (int kr = 0; kr < a.kH; kr++) {
+                const int oh = h0 + pH - kr * dH;
+                if ((unsigned) oh >= (unsigned) a.oH) continue;
+                const T *row = in + kr * a.xs[2] + oh * a.xRow;
 #pragma unroll 3
-            for (int kc = 0; kc < a.kW; kc++) {
-                const T *tap = row + kc * a.xs[3];
-                const int ow0 = w0 + pW - kc * dW;
+                for (int kc = 0; kc < a.kW; kc++) {
+                    const T *tap = row + kc * a.xs[3];
+                    const int ow0 = w0 + pW - kc * dW;
 #pragma unroll
-                for (int j = 0; j < V; j++)
-                    if ((unsigned) (ow0 + j) < (unsigned) a.oW) sum[j] += Elem<T>::load(tap + (ow0 + j) * a.xCol);
+                    for (int j = 0; j < V; j++)
+                        if ((unsigned) (ow0 + j) < (unsigned) a.oW) sum[j] += Elem<T>::load(tap + (ow0 + j) * a.xCol);
+                }
             }
-        }
-    } else {
-        for (int kr = 0; kr < a.kH; kr++) {
-            for (int kc = 0; kc < a.kW; kc++) {
-                const T *tap = in + kr * a.xs[2] + kc * a.xs[3];
-                int h = h0, w = w0;
+        } else {
+            for (int kr = 0; kr < a.kH; kr++) {
+                for (int kc = 0; kc < a.kW; kc++) {
+                    const T *tap = in + kr * a.xs[2] + kc * a.xs[3];
+                    int h = h0, w = w0;
 #pragma unroll
-                for (int j = 0; j < V; j++) {
-                    const int hh = h + pH - kr * dH, ww = w + pW - kc * dW;
-                    const int oh = hh / sH, ow = ww / sW;
-                    const bool hit = p0 + j < a.out.positions && hh >= 0 && ww >= 0 && oh * sH == hh && ow * sW == ww &&
-                                     oh < a.oH && ow < a.oW;
-                    if (hit) sum[j] += Elem<T>::load(tap + oh * a.xRow + ow * a.xCol);
-                    if (++w == a.out.width) { w = 0; h++; }
+                    for (int j = 0; j < V; j++) {
+                        const int hh = h + pH - kr * dH, ww = w + pW - kc * dW;
+                        const int oh = hh / sH, ow = ww / sW;
+                        const bool hit = p0 + j < a.out.positions && hh >= 0 && ww >= 0 && oh * sH == hh && ow * sW == ww &&
+                                         oh < a.oH && ow < a.oW;
+                        if (hit) sum[j] += Elem<T>::load(tap + oh * a.xRow + ow * a.xCol);
+                        if (++w == a.out.width) { w = 0; h++; }
+                    }
                 }
             }
         }
-    }
-    T vals[V];
+        T vals[V];
 #pragma unroll
-    for (int j = 0; j < V; j++) vals[j] = Elem<T>::from_c(sum[j]);
-    store_run<T, V>(out, a.out, p0, vals);
+        for (int j = 0; j < V; j++) vals[j] = Elem<T>::from_c(sum[j]);
+        store_run<T, V>(out, a.out, p0, vals);
+    };
+    for (int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; p0 < a.out.positions; p0 += gridDim.y * blockDim.x * V) run(p0);
 }
 
 // ---- Pooling2D (71): max (mode 0), average (1) or p-norm (2) over the dilated window of every output position
@@ -230,6 +290,55 @@ struct PoolArgs {
 
 ND_D int ceil_div_int(int a, int b) { return a > 0 ? (a + b - 1) / b : -((-a) / b); }   // ceil(a / b) for b > 0
 
+// Pooling over a span: with unit dilation along contiguous image rows the windows of a run of V result positions
+// lie in one span of (V - 1) * SW + kW image elements per image row. The span is loaded once per row - as 128-bit
+// words when it starts on a 16-byte boundary and the words stay inside the row, else element by element, an
+// element outside the image becoming a value that cannot win (max) or zero (sum) - and the windows are cut out of
+// it in registers. SW (1 or 2) is a template constant so that the registers can be addressed.
+constexpr int kMaxPoolTaps = 4;
+
+template <class T, int SW, class C>
+ND_D void pool_span_rows(const T *__restrict__ in, int xRow, int iH, int iW, int top, int left, int kH, int kW, int dH,
+                         int mode, C neutral, C (&acc)[Elem<T>::kVec]) {
+    constexpr int V = Elem<T>::kVec, SPAN = (V - 1) * SW + kMaxPoolTaps, WORDS = (SPAN + V - 1) / V;
+    const int need = (V - 1) * SW + kW;
+    const bool words = left >= 0 && left + (need + V - 1) / V * V <= iW && (reinterpret_cast<uintptr_t>(in + left) & 15) == 0 &&
+                       (xRow * (int) sizeof(T)) % 16 == 0;
+    const bool wide = __all_sync(__activemask(), words);
+    for (int i = 0; i < kH; i++) {
+        const int ky = top + i * dH;
+        const bool rowInside = (unsigned) ky < (unsigned) iH;
+        const T *row = in + ky * xRow + left;
+        C span[WORDS * V];
+        if (wide) {
+#pragma unroll
+            for (int w = 0; w < WORDS; w++) {
+                Pack<T> pk;
+                if (rowInside && w * V < need) pk = load_pack(row + w * V);
+#pragma unroll
+                for (int j = 0; j < V; j++) span[w * V + j] = rowInside && w * V < need ? Elem<T>::to_c(pk.v[j]) : neutral;
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < SPAN; t++) {
+                const bool ok = rowInside && t < need && (unsigned) (left + t) < (unsigned) iW;
+                span[t] = ok ? Elem<T>::load(row + t) : neutral;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kMaxPoolTaps; k++) {
+            if (k < kW) {
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const C v = span[j * SW + k];
+                    if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                    else acc[j] += v;
+                }
+            }
+        }
+    }
+}
+
 template <class T>
 __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
     grid_dependency_sync();
@@ -242,97 +351,172 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
     const C extra0 = Elem<T>::to_c(param(extra, 10));
     const C lowest = Elem<T>::to_c(Elem<T>::from_c((C) -1e37));        // -MAX_FLOAT in the element type
     const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
-    const int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    if (plane >= a.planes || p0 >= a.out.positions) return;
+    if (plane >= a.planes) return;
     const unsigned c = plane % a.iC, b = plane / a.iC;
     const T *__restrict__ in = static_cast<const T *>(a.x) + b * a.xs[0] + c * a.xs[1];
     T *__restrict__ out = static_cast<T *>(a.z) + b * a.zs[0] + c * a.zs[1];
-    const int yy0 = p0 / a.out.width, xx0 = p0 - yy0 * a.out.width;
-    if (mode == 2) {
-        // p-norm: one position at a time (the power's code, unrolled over a run's positions, would set the register
-        // count of the whole kernel)
+    // a thread takes every stride-th run of the plane, so that what it derives once (the geometry, the plane) serves
+    // several runs
+    auto run = [&](const int p0) {
+        const int yy0 = p0 / a.out.width, xx0 = p0 - yy0 * a.out.width;
+        if (mode == 2) {
+            // p-norm: one position at a time (the power's code, unrolled over a run's positions, would set the register
+            // count of the whole kernel)
 #pragma unroll 1
-        for (int p = p0; p < p0 + V && p < a.out.positions; p++) {
-            const int yy = p / a.out.width, xx = p - yy * a.out.width;
-            C acc = 0;
+            for (int p = p0; p < p0 + V && p < a.out.positions; p++) {
+                const int yy = p / a.out.width, xx = p - yy * a.out.width;
+                C acc = 0;
+                for (int i = 0; i < kH; i++) {
+                    for (int k = 0; k < kW; k++) {
+                        const int ky = yy * sH - pH + i * dH, kx = xx * sW - pW + k * dW;
+                        if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW)
+                            acc += pow(fabs(Elem<T>::load(in + ky * a.xRow + kx * a.xCol)), extra0);
+                    }
+                }
+                Elem<T>::store(out + (a.out.dense ? p : yy * a.out.sRow + xx * a.out.sCol), pow(acc, (C) 1 / extra0));
+            }
+            return;
+        }
+        // Unit dilation along contiguous image rows, stride 1 or 2, at most four taps per row: the span form. The
+        // choice is the same for all threads of a warp.
+        if (dW == 1 && a.xCol == 1 && (sW == 1 || sW == 2) && kW <= kMaxPoolTaps && dH >= 1 &&
+            __all_sync(__activemask(), xx0 + V <= a.out.width)) {
+            const int top = yy0 * sH - pH, left = xx0 * sW - pW;
+            C acc[V];
+#pragma unroll
+            for (int j = 0; j < V; j++) acc[j] = mode == 0 ? lowest : (C) 0;
+            if (sW == 1) pool_span_rows<T, 1>(in, a.xRow, a.iH, a.iW, top, left, kH, kW, dH, mode, acc[0], acc);
+            else pool_span_rows<T, 2>(in, a.xRow, a.iH, a.iW, top, left, kH, kW, dH, mode, acc[0], acc);
+            T vals[V];
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+                C res = acc[j];
+                if (mode == 1) {
+                    int divisor = 0;
+                    if ((int) extra0 == 0) {
+                        // the window as the reference clips it (special_ops.h:236-262)
+                        int hstart = top, wstart = left + j * sW;
+                        int hend = hstart + kH + (kH - 1) * (dH - 1), wend = wstart + kW;
+                        if (hstart < 0) hstart += ceil_div_int(-hstart, dH) * dH;
+                        if (wstart < 0) wstart = 0;
+                        if (hend > a.iH) hend -= ceil_div_int(hend - a.iH, dH) * dH;
+                        if (wend > a.iW) wend = a.iW;
+                        divisor = ceil_div_int(hend - hstart, dH) * (wend - wstart);
+                    } else if ((int) extra0 == 1) divisor = kH * kW;
+                    res = res / (C) divisor;
+                }
+                vals[j] = Elem<T>::from_c(res);
+            }
+            store_run<T, V>(out, a.out, p0, vals);
+            return;
+        }
+        // Interior: the run stays in one row of the result and every tap of its windows lies inside the image. Then
+        // nothing is tested per tap: a tap is one load per position at a fixed step.
+        {
+            const int top = yy0 * sH - pH, left = xx0 * sW - pW;
+            const bool interior = xx0 + V <= a.out.width && top >= 0 && top + (kH - 1) * dH < a.iH && left >= 0 &&
+                                  left + (V - 1) * sW + (kW - 1) * dW < a.iW && dH >= 1 && dW >= 1 && sW >= 0;
+            if (__all_sync(__activemask(), interior)) {        // taken by whole warps only: no warp runs both forms
+                const int step = sW * a.xCol;
+                C acc[V];
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = mode == 0 ? lowest : (C) 0;
+                for (int i = 0; i < kH; i++) {
+                    const T *row = in + (top + i * dH) * a.xRow + left * a.xCol;
+                    if (mode == 0) {
+#pragma unroll 3
+                        for (int k = 0; k < kW; k++) {
+#pragma unroll
+                            for (int j = 0; j < V; j++) {
+                                const C v = Elem<T>::load(row + k * dW * a.xCol + j * step);
+                                if (v > acc[j]) acc[j] = v;
+                            }
+                        }
+                    } else {
+#pragma unroll 3
+                        for (int k = 0; k < kW; k++) {
+#pragma unroll
+                            for (int j = 0; j < V; j++) acc[j] += Elem<T>::load(row + k * dW * a.xCol + j * step);
+                        }
+                    }
+                }
+                T vals[V];
+                const int divisor = (int) extra0 == 0 || (int) extra0 == 1 ? kH * kW : 0;     // the whole window counts
+#pragma unroll
+                for (int j = 0; j < V; j++) vals[j] = Elem<T>::from_c(mode == 1 ? acc[j] / (C) divisor : acc[j]);
+                store_run<T, V>(out, a.out, p0, vals);
+                return;
+            }
+        }
+        // top-left tap of every position's window; a position past the plane's end gets a window wholly above the image
+        int hs[V], ws[V];
+        C acc[V];
+        {
+            int yy = yy0, xx = xx0;
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+                hs[j] = p0 + j < a.out.positions ? yy * sH - pH : -(kH * dH + 1); ws[j] = xx * sW - pW;
+                acc[j] = mode == 0 ? lowest : (C) 0;
+                if (++xx == a.out.width) { xx = 0; yy++; }
+            }
+        }
+        if (xx0 + V <= a.out.width) {
+            // the run stays in one row of the result: its windows share their image rows
+            for (int i = 0; i < kH; i++) {
+                const int ky = hs[0] + i * dH;
+                if ((unsigned) ky >= (unsigned) a.iH) continue;
+                const T *row = in + ky * a.xRow;
+#pragma unroll 3
+                for (int k = 0; k < kW; k++) {
+#pragma unroll
+                    for (int j = 0; j < V; j++) {
+                        const int kx = ws[j] + k * dW;
+                        if ((unsigned) kx < (unsigned) a.iW) {
+                            const C v = Elem<T>::load(row + kx * a.xCol);
+                            if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                            else acc[j] += v;
+                        }
+                    }
+                }
+            }
+        } else {
             for (int i = 0; i < kH; i++) {
                 for (int k = 0; k < kW; k++) {
-                    const int ky = yy * sH - pH + i * dH, kx = xx * sW - pW + k * dW;
-                    if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW)
-                        acc += pow(fabs(Elem<T>::load(in + ky * a.xRow + kx * a.xCol)), extra0);
+#pragma unroll
+                    for (int j = 0; j < V; j++) {
+                        const int ky = hs[j] + i * dH, kx = ws[j] + k * dW;
+                        if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW) {
+                            const C v = Elem<T>::load(in + ky * a.xRow + kx * a.xCol);
+                            if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                            else acc[j] += v;
+                        }
+                    }
                 }
             }
-            Elem<T>::store(out + (a.out.dense ? p : yy * a.out.sRow + xx * a.out.sCol), pow(acc, (C) 1 / extra0));
         }
-        return;
-    }
-    // top-left tap of every position's window; a position past the plane's end gets a window wholly above the image
-    int hs[V], ws[V];
-    C acc[V];
-    {
-        int yy = yy0, xx = xx0;
+        T vals[V];
 #pragma unroll
         for (int j = 0; j < V; j++) {
-            hs[j] = p0 + j < a.out.positions ? yy * sH - pH : -(kH * dH + 1); ws[j] = xx * sW - pW;
-            acc[j] = mode == 0 ? lowest : (C) 0;
-            if (++xx == a.out.width) { xx = 0; yy++; }
-        }
-    }
-    if (xx0 + V <= a.out.width) {
-        // the run stays in one row of the result: its windows share their image rows
-        for (int i = 0; i < kH; i++) {
-            const int ky = hs[0] + i * dH;
-            if ((unsigned) ky >= (unsigned) a.iH) continue;
-            const T *row = in + ky * a.xRow;
-#pragma unroll 3
-            for (int k = 0; k < kW; k++) {
-#pragma unroll
-                for (int j = 0; j < V; j++) {
-                    const int kx = ws[j] + k * dW;
-                    if ((unsigned) kx < (unsigned) a.iW) {
-                        const C v = Elem<T>::load(row + kx * a.xCol);
-                        if (mode == 0) { if (v > acc[j]) acc[j] = v; }
-                        else acc[j] += v;
-                    }
-                }
+            C res = acc[j];
+            if (mode == 1) {
+                int divisor = 0;
+                if ((int) extra0 == 0) {
+                    // the window as the reference clips it (special_ops.h:236-262)
+                    int hstart = hs[j], wstart = ws[j];
+                    int hend = hstart + kH + (kH - 1) * (dH - 1), wend = wstart + kW + (kW - 1) * (dW - 1);
+                    if (hstart < 0) hstart += ceil_div_int(-hstart, dH) * dH;
+                    if (wstart < 0) wstart += ceil_div_int(-wstart, dW) * dW;
+                    if (hend > a.iH) hend -= ceil_div_int(hend - a.iH, dH) * dH;
+                    if (wend > a.iW) wend -= ceil_div_int(wend - a.iW, dW) * dW;
+                    divisor = ceil_div_int(hend - hstart, dH) * ceil_div_int(wend - wstart, dW);
+                } else if ((int) extra0 == 1) divisor = kH * kW;
+                res = res / (C) divisor;
             }
+            vals[j] = Elem<T>::from_c(res);
         }
-    } else {
-        for (int i = 0; i < kH; i++) {
-            for (int k = 0; k < kW; k++) {
-#pragma unroll
-                for (int j = 0; j < V; j++) {
-                    const int ky = hs[j] + i * dH, kx = ws[j] + k * dW;
-                    if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW) {
-                        const C v = Elem<T>::load(in + ky * a.xRow + kx * a.xCol);
-                        if (mode == 0) { if (v > acc[j]) acc[j] = v; }
-                        else acc[j] += v;
-                    }
-                }
-            }
-        }
-    }
-    T vals[V];
-#pragma unroll
-    for (int j = 0; j < V; j++) {
-        C res = acc[j];
-        if (mode == 1) {
-            int divisor = 0;
-            if ((int) extra0 == 0) {
-                // the window as the reference clips it (special_ops.h:236-262)
-                int hstart = hs[j], wstart = ws[j];
-                int hend = hstart + kH + (kH - 1) * (dH - 1), wend = wstart + kW + (kW - 1) * (dW - 1);
-                if (hstart < 0) hstart += ceil_div_int(-hstart, dH) * dH;
-                if (wstart < 0) wstart += ceil_div_int(-wstart, dW) * dW;
-                if (hend > a.iH) hend -= ceil_div_int(hend - a.iH, dH) * dH;
-                if (wend > a.iW) wend -= ceil_div_int(wend - a.iW, dW) * dW;
-                divisor = ceil_div_int(hend - hstart, dH) * ceil_div_int(wend - wstart, dW);
-            } else if ((int) extra0 == 1) divisor = kH * kW;
-            res = res / (C) divisor;
-        }
-        vals[j] = Elem<T>::from_c(res);
-    }
-    store_run<T, V>(out, a.out, p0, vals);
+        store_run<T, V>(out, a.out, p0, vals);
+    };
+    for (int p0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; p0 < a.out.positions; p0 += gridDim.y * blockDim.x * V) run(p0);
 }
 
 // ---- Histogram (48): z[i] += number of x whose bin is i, bin = (int) ((x - min) / binSize) clamped to
