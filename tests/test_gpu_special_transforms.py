@@ -17,7 +17,11 @@ pytestmark = pytest.mark.gpu
 
 NAMES = {np.float32: "Float", np.float64: "Double", np.float16: "Half"}
 BIG = [(4, 16, 28, 28, 3, 3, 1, 1, 1, 1, 1, 1), (2, 8, 57, 43, 5, 3, 2, 2, 2, 1, 1, 2), (3, 5, 64, 64, 2, 2, 2, 2, 0, 0, 1, 1),
-       (1, 3, 224, 224, 7, 7, 2, 2, 3, 3, 1, 1)]
+       (1, 3, 224, 224, 7, 7, 2, 2, 3, 3, 1, 1),
+       # rows whose length is a multiple of the 16-byte run of every element type, so that whole warps take the span
+       # forms: seven taps per kernel row, a single tap, dilated kernel rows, four-tap pooling windows, mixed strides
+       (2, 4, 32, 40, 7, 7, 1, 1, 3, 3, 1, 1), (2, 4, 32, 32, 1, 1, 1, 1, 0, 0, 1, 1), (1, 4, 40, 48, 5, 5, 1, 1, 2, 2, 2, 1),
+       (2, 4, 32, 32, 4, 4, 2, 2, 1, 1, 1, 1), (2, 3, 33, 64, 3, 3, 2, 1, 1, 1, 1, 1), (2, 2, 16, 128, 2, 2, 1, 2, 0, 0, 1, 1)]
 
 
 def dev(a):
@@ -89,7 +93,7 @@ def test_col2im(ops, maybe_ref, dt, g, kinds):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64, np.float16])
-@pytest.mark.parametrize("g", GEOMETRIES + BIG[:3])
+@pytest.mark.parametrize("g", GEOMETRIES + BIG[:3] + BIG[4:])
 @pytest.mark.parametrize("mode,extra0", [(0, 0.0), (1, 0.0), (1, 1.0), (2, 2.0), (2, 3.0)])
 @pytest.mark.parametrize("kinds", [("c", "c"), ("f", "f"), ("cview2", "c")])
 def test_pooling2d(ops, maybe_ref, dt, g, mode, extra0, kinds):
