@@ -28,7 +28,9 @@ struct PlaneGrid {
     unsigned gx, gy;     // gridDim: planes / ty, chunks of runs
 };
 
-constexpr int kRunsPerThread = 1;      // 4 was measured: no gain for Im2col and Pooling2D, Col2Im 0.079 against 0.075 ms
+// Runs per thread that the grid is sized for (a thread loops over every gridDim.y-th chunk of runs). 4 was
+// measured: no gain for Im2col and Pooling2D, Col2Im 0.079 against 0.075 ms.
+constexpr int kRunsPerThread = 1;
 
 inline PlaneGrid plane_grid(LL planes, LL positions, int v) {
     const LL runs = ceil_div(ceil_div(positions, (LL) v), (LL) kRunsPerThread);      // per thread: kRunsPerThread of them
@@ -46,7 +48,8 @@ inline PlaneGrid plane_grid(LL planes, LL positions, int v) {
     // One short-lived thread per run and plane: fewer, longer-lived CTAs that walk the planes with the grid's stride
     // were slower (Im2col 0.098 against 0.084 ms), the hardware keeps more independent loads in flight this way.
     g.gx = (unsigned) ceil_div(planes, (LL) g.ty);
-    g.gy = (unsigned) ceil_div(runs, (LL) g.tx);
+    const LL chunks = ceil_div(runs, (LL) g.tx);
+    g.gy = (unsigned) (chunks < 65535 ? chunks : 65535);        // the kernels loop over what a larger plane leaves
     return g;
 }
 
