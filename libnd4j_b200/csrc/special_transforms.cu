@@ -413,44 +413,6 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
             store_run<T, V>(out, a.out, p0, vals);
             return;
         }
-        // Interior: the run stays in one row of the result and every tap of its windows lies inside the image. Then
-        // nothing is tested per tap: a tap is one load per position at a fixed step.
-        {
-            const int top = yy0 * sH - pH, left = xx0 * sW - pW;
-            const bool interior = xx0 + V <= a.out.width && top >= 0 && top + (kH - 1) * dH < a.iH && left >= 0 &&
-                                  left + (V - 1) * sW + (kW - 1) * dW < a.iW && dH >= 1 && dW >= 1 && sW >= 0;
-            if (__all_sync(__activemask(), interior)) {        // taken by whole warps only: no warp runs both forms
-                const int step = sW * a.xCol;
-                C acc[V];
-#pragma unroll
-                for (int j = 0; j < V; j++) acc[j] = mode == 0 ? lowest : (C) 0;
-                for (int i = 0; i < kH; i++) {
-                    const T *row = in + (top + i * dH) * a.xRow + left * a.xCol;
-                    if (mode == 0) {
-#pragma unroll 3
-                        for (int k = 0; k < kW; k++) {
-#pragma unroll
-                            for (int j = 0; j < V; j++) {
-                                const C v = Elem<T>::load(row + k * dW * a.xCol + j * step);
-                                if (v > acc[j]) acc[j] = v;
-                            }
-                        }
-                    } else {
-#pragma unroll 3
-                        for (int k = 0; k < kW; k++) {
-#pragma unroll
-                            for (int j = 0; j < V; j++) acc[j] += Elem<T>::load(row + k * dW * a.xCol + j * step);
-                        }
-                    }
-                }
-                T vals[V];
-                const int divisor = (int) extra0 == 0 || (int) extra0 == 1 ? kH * kW : 0;     // the whole window counts
-#pragma unroll
-                for (int j = 0; j < V; j++) vals[j] = Elem<T>::from_c(mode == 1 ? acc[j] / (C) divisor : acc[j]);
-                store_run<T, V>(out, a.out, p0, vals);
-                return;
-            }
-        }
         // top-left tap of every position's window; a position past the plane's end gets a window wholly above the image
         int hs[V], ws[V];
         C acc[V];
