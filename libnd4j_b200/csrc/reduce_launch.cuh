@@ -113,7 +113,12 @@ Status run_reduction(const ReduceCall &c, cudaStream_t stream) {
         // Segments of a TAD tile are grouped into thread-block clusters of 2, 4 or 8 CTAs that merge
         // through distributed shared memory; only one partial state per cluster reaches global memory.
         LL cluster = 1;
-        const LL maxCluster = g_tuning[kTuneMaxCluster] < 8 ? g_tuning[kTuneMaxCluster] : 8;
+        LL maxCluster = g_tuning[kTuneMaxCluster] < 8 ? g_tuning[kTuneMaxCluster] : 8;
+        // Clusters of 4 by default (with 28 segments per tile, seven clusters of 4 beat four of 8: Variance over
+        // dimension 0 of [65536,1024] 0.053 against 0.059 ms), but where one cluster of 8 holds all segments of a
+        // tile nothing passes through global memory and no arrival counter is needed (Sum over dimension 0 of
+        // [8192,4096]: 0.0225 against 0.0249 ms).
+        if (maxCluster == 4 && splits > 4 && splits <= 8) maxCluster = 8;
         while (cluster < splits && cluster * 2 <= maxCluster && cluster * 2 <= maxSplits) cluster *= 2;
         LL groups = ceil_div(splits, cluster);
         while (groups > 1 && groups * cluster > maxSplits) groups--;
