@@ -1050,7 +1050,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="smaller sizes for the families table")
     ap.add_argument("--no-families", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--e2e-blocks", type=int, default=16, help="row blocks of the pipelined end-to-end step (divides 16384)")
+    ap.add_argument("--e2e-blocks", type=int, default=4, help="row blocks of the pipelined end-to-end step (divides 16384)")
     ap.add_argument("--only", default=None, help="run only the families whose name contains one of these comma-separated texts")
     ap.add_argument("--profile", action="store_true", help="profiling aid: three plain timed launches per family, no graph")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
