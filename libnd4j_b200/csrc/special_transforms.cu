@@ -353,6 +353,9 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
     const int mode = param_int(extra, 9);
     const C extra0 = Elem<T>::to_c(param(extra, 10));
     const C lowest = Elem<T>::to_c(Elem<T>::from_c((C) -1e37));        // -MAX_FLOAT in the element type
+    // Taps beyond the image (plus its padding) cannot lie inside it, so the loops over a window stop there: the
+    // window's size comes from device memory, and a wild value must not turn into a launch that never ends.
+    const int tapRows = min(kH, a.iH + max(pH, 0) + 1), tapCols = min(kW, a.iW + max(pW, 0) + 1);
     const unsigned plane = blockIdx.x * blockDim.y + threadIdx.y;
     if (plane >= a.planes) return;
     const unsigned c = plane % a.iC, b = plane / a.iC;
@@ -369,8 +372,8 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
             for (int p = p0; p < p0 + V && p < a.out.positions; p++) {
                 const int yy = p / a.out.width, xx = p - yy * a.out.width;
                 C acc = 0;
-                for (int i = 0; i < kH; i++) {
-                    for (int k = 0; k < kW; k++) {
+                for (int i = 0; i < tapRows; i++) {
+                    for (int k = 0; k < tapCols; k++) {
                         const int ky = yy * sH - pH + i * dH, kx = xx * sW - pW + k * dW;
                         if ((unsigned) ky < (unsigned) a.iH && (unsigned) kx < (unsigned) a.iW)
                             acc += pow(fabs(Elem<T>::load(in + ky * a.xRow + kx * a.xCol)), extra0);
@@ -388,8 +391,8 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
             C acc[V];
 #pragma unroll
             for (int j = 0; j < V; j++) acc[j] = mode == 0 ? lowest : (C) 0;
-            if (sW == 1) pool_span_rows<T, 1>(in, a.xRow, a.iH, a.iW, top, left, kH, kW, dH, mode, acc[0], acc);
-            else pool_span_rows<T, 2>(in, a.xRow, a.iH, a.iW, top, left, kH, kW, dH, mode, acc[0], acc);
+            if (sW == 1) pool_span_rows<T, 1>(in, a.xRow, a.iH, a.iW, top, left, tapRows, kW, dH, mode, acc[0], acc);
+            else pool_span_rows<T, 2>(in, a.xRow, a.iH, a.iW, top, left, tapRows, kW, dH, mode, acc[0], acc);
             T vals[V];
 #pragma unroll
             for (int j = 0; j < V; j++) {
@@ -427,12 +430,12 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
         }
         if (xx0 + V <= a.out.width) {
             // the run stays in one row of the result: its windows share their image rows
-            for (int i = 0; i < kH; i++) {
+            for (int i = 0; i < tapRows; i++) {
                 const int ky = hs[0] + i * dH;
                 if ((unsigned) ky >= (unsigned) a.iH) continue;
                 const T *row = in + ky * a.xRow;
 #pragma unroll 3
-                for (int k = 0; k < kW; k++) {
+                for (int k = 0; k < tapCols; k++) {
 #pragma unroll
                     for (int j = 0; j < V; j++) {
                         const int kx = ws[j] + k * dW;
@@ -445,8 +448,8 @@ __global__ void __launch_bounds__(256, 4) k_pooling2d(const PoolArgs a) {
                 }
             }
         } else {
-            for (int i = 0; i < kH; i++) {
-                for (int k = 0; k < kW; k++) {
+            for (int i = 0; i < tapRows; i++) {
+                for (int k = 0; k < tapCols; k++) {
 #pragma unroll
                     for (int j = 0; j < V; j++) {
                         const int ky = hs[j] + i * dH, kx = ws[j] + k * dW;
