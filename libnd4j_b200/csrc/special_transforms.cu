@@ -524,11 +524,13 @@ __global__ void __launch_bounds__(256) k_histogram(const HistArgs a) {
     for (int i = threadIdx.x; i < tables; i += blockDim.x) bins[i] = 0;
     __syncthreads();
     unsigned *mine = a.copies ? bins + ((threadIdx.x >> 5) & (a.copies - 1)) * a.zLength : a.counts;
+    // the kernel is bound by instruction issue, so the clamps are two min / max instead of branches and the test
+    // against the result's length is only made where numBins exceeds it (then there is nowhere to count those)
+    const int last = numBins - 1;
+    const bool any = numBins >= 1, fits = any && numBins <= a.zLength;
     auto count = [&](T v) {
-        int idx = hist_int(hist_div(hist_sub(v, lo), binSize));
-        if (idx < 0) idx = 0;
-        else if (idx >= numBins) idx = numBins - 1;
-        if (idx >= 0 && idx < a.zLength) atomicAdd(mine + idx, 1u);          // numBins beyond the result: nowhere to count
+        const int idx = max(min(hist_int(hist_div(hist_sub(v, lo), binSize)), last), 0);
+        if (fits || (any && idx < a.zLength)) atomicAdd(mine + idx, 1u);
     };
     const T *__restrict__ x = static_cast<const T *>(a.x);
     const LL tid = (LL) blockIdx.x * blockDim.x + threadIdx.x, threads = (LL) gridDim.x * blockDim.x;
