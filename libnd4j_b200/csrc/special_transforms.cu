@@ -235,7 +235,38 @@ __global__ void __launch_bounds__(256, 4) k_col2im(const Col2imArgs a) {
         C sum[V];
 #pragma unroll
         for (int j = 0; j < V; j++) sum[j] = 0;
-        if (w0 + V <= a.out.width && sH == 1 && sW == 1) {
+        if (sH == 1 && sW == 1 && a.kH == 3 && a.kW == 3 && __all_sync(__activemask(), w0 + V <= a.out.width)) {
+            // the 3 x 3 kernel with unit strides (chosen per warp): all nine taps' loads - none depends on another -
+            // are issued before the first addition (the general loop below keeps one kernel row's loads in flight:
+            // 0.070 against 0.061 ms); the additions keep the reference's order
+            C v[3][3][V];
+#pragma unroll
+            for (int kr = 0; kr < 3; kr++) {
+                const int oh = h0 + pH - kr * dH;
+                const bool rowOk = (unsigned) oh < (unsigned) a.oH;
+                const T *row = in + kr * a.xs[2] + oh * a.xRow;
+#pragma unroll
+                for (int kc = 0; kc < 3; kc++) {
+                    const int ow0 = w0 + pW - kc * dW;
+#pragma unroll
+                    for (int j = 0; j < V; j++)
+                        v[kr][kc][j] = rowOk && (unsigned) (ow0 + j) < (unsigned) a.oW
+                                           ? Elem<T>::load(row + kc * a.xs[3] + (ow0 + j) * a.xCol) : (C) 0;
+                }
+            }
+#pragma unroll
+            for (int kr = 0; kr < 3; kr++) {
+                const int oh = h0 + pH - kr * dH;
+                if ((unsigned) oh >= (unsigned) a.oH) continue;
+#pragma unroll
+                for (int kc = 0; kc < 3; kc++) {
+                    const int ow0 = w0 + pW - kc * dW;
+#pragma unroll
+                    for (int j = 0; j < V; j++)
+                        if ((unsigned) (ow0 + j) < (unsigned) a.oW) sum[j] += v[kr][kc][j];
+                }
+            }
+        } else if (w0 + V <= a.out.width && sH == 1 && sW == 1) {
             // unit strides and a run inside one image row: one row test per kernel row, no divisions
             for (int kr = 0; kr < a.kH; kr++) {
                 const int oh = h0 + pH - kr * dH;
