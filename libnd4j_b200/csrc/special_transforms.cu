@@ -339,6 +339,35 @@ ND_D void pool_span_rows(const T *__restrict__ in, int xRow, int iH, int iW, int
     const bool words = left >= 0 && left + (need + V - 1) / V * V <= iW && (reinterpret_cast<uintptr_t>(in + left) & 15) == 0 &&
                        (xRow * (int) sizeof(T)) % 16 == 0;
     const bool wide = __all_sync(__activemask(), words);
+    if (V <= 4 && kH == 2 && wide && need <= 2 * V) {
+        // the usual two-row window over an aligned span of at most two words: both rows' words are loaded before
+        // either is used
+        const int k0 = top, k1 = top + dH;
+        const bool in0 = (unsigned) k0 < (unsigned) iH, in1 = (unsigned) k1 < (unsigned) iH;
+        const T *r0 = in + k0 * xRow + left, *r1 = in + k1 * xRow + left;
+        Pack<T> p[2][2];
+        if (in0) { p[0][0] = load_pack(r0); if (need > V) p[0][1] = load_pack(r0 + V); }
+        if (in1) { p[1][0] = load_pack(r1); if (need > V) p[1][1] = load_pack(r1 + V); }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (!(i == 0 ? in0 : in1)) continue;
+#pragma unroll
+            for (int k = 0; k < kMaxPoolTaps; k++) {
+                if (k < kW) {
+#pragma unroll
+                    for (int j = 0; j < V; j++) {
+                        const int t = j * SW + k;
+                        if (t < 2 * V) {
+                            const C v = Elem<T>::to_c(p[i][t / V].v[t % V]);
+                            if (mode == 0) { if (v > acc[j]) acc[j] = v; }
+                            else acc[j] += v;
+                        }
+                    }
+                }
+            }
+        }
+        return;
+    }
     for (int i = 0; i < kH; i++) {
         const int ky = top + i * dH;
         const bool rowInside = (unsigned) ky < (unsigned) iH;
