@@ -160,7 +160,8 @@ def test_reverse(ops, maybe_ref, dt, shape, kinds):
 
 
 @pytest.mark.parametrize("kind", ["c", "f", "cview2", "fview2"])
-@pytest.mark.parametrize("shape", [(1, 16), (1, 17), (5, 6), (1, (1 << 20) + 1), (257, 513)])
+@pytest.mark.parametrize("shape", [(1, 16), (1, 17), (5, 6), (1, 12), (1, 20), (1, 1 << 20), (1, (1 << 20) + 4), (1, (1 << 20) + 1),
+                                   (257, 513), (256, 516)])
 def test_reverse_in_place(ops, maybe_ref, kind, shape):
     x = np.random.default_rng(3).standard_normal(shape).astype(np.float32)
     lx = Layout(x, kind)
