@@ -488,6 +488,14 @@ def family_table(torch, ops, calls, stream, peak, quick, only=None, profile=Fals
     record("col2im_f32_32x64x56x56_k3", (col_.numel() + img_.numel()) * 4, col_.numel(),
            lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 36, P(col_), coli_, P(img_), imgi_, P(e_c2i))))
     del img_, col_
+    # the 7x7 stride-2 kernel of an image network's first layer: [32,3,224,224] -> [32,3,7,7,112,112]
+    img_ = torch.randn(32, 3, 224, 224, device=dev, generator=g)
+    col_ = torch.empty(32, 3, 7, 7, 112, 112, device=dev)
+    imgi_, coli_ = calls.longs(S.shape_info([32, 3, 224, 224])), calls.longs(S.shape_info([32, 3, 7, 7, 112, 112]))
+    e_i2c7 = torch.tensor([7, 7, 2, 2, 3, 3, 1, 1, 0, 0], dtype=torch.float32, device=dev)
+    record("im2col_f32_32x3x224x224_k7s2", (col_.numel() + img_.numel()) * 4, col_.numel(),
+           lambda: calls.check(lib.nd4jb200_exec_transform(st, 0, 37, P(img_), imgi_, P(col_), coli_, P(e_i2c7))))
+    del img_, col_
     pin_ = torch.randn(64, 64, 112, 112, device=dev, generator=g)
     pout_ = torch.empty(64, 64, 56, 56, device=dev)
     pini_, pouti_ = calls.longs(S.shape_info([64, 64, 112, 112])), calls.longs(S.shape_info([64, 64, 56, 56]))

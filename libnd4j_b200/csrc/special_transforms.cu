@@ -101,6 +101,37 @@ struct Im2colArgs {
     PlaneOut out;               // z's last two axes
 };
 
+constexpr int kMaxSpanTaps = 7;
+
+// One run of V result positions for every tap of the kernel, through a span per kernel row. SW (the stride along
+// the row, 1 or 2) is a template constant so that the span's registers can be addressed.
+template <class T, int SW>
+ND_D void im2col_span(const T *__restrict__ in, T *__restrict__ out, const Im2colArgs &a, int top, int left, int dH, T pad, int p0) {
+    constexpr int V = Elem<T>::kVec, SPAN = (V - 1) * SW + kMaxSpanTaps;
+    const int need = (V - 1) * SW + a.kW;
+    for (int kr = 0; kr < a.kH; kr++) {
+        const int ih = top + kr * dH;
+        const bool rowInside = (unsigned) ih < (unsigned) a.iH;
+        const T *row = in + ih * a.xRow + left;
+        T span[SPAN];
+#pragma unroll
+        for (int t = 0; t < SPAN; t++) {
+            const bool ok = rowInside && t < need && (unsigned) (left + t) < (unsigned) a.iW;
+            span[t] = ok ? row[t] : pad;
+        }
+        T *dst = out + kr * a.zs[2] + p0;
+#pragma unroll
+        for (int kc = 0; kc < kMaxSpanTaps; kc++) {
+            if (kc < a.kW) {
+                Pack<T> pk;
+#pragma unroll
+                for (int j = 0; j < V; j++) pk.v[j] = span[kc + j * SW];
+                store_pack(dst + kc * a.zs[3], pk);
+            }
+        }
+    }
+}
+
 template <class T>
 __global__ void __launch_bounds__(256, 4) k_im2col(const Im2colArgs a) {
     grid_dependency_sync();
@@ -123,33 +154,14 @@ __global__ void __launch_bounds__(256, 4) k_im2col(const Im2colArgs a) {
         // Interior: the run stays in one row and every tap of every position lies inside the image. Then nothing is
         // tested per element, and a tap is a few loads at a fixed step and one store.
         const int top = oh0 * sH - pH, left = ow0 * sW - pW;
-        // Unit stride and dilation along contiguous image rows (the usual convolution): the kW taps of a kernel row read
-        // overlapping pieces of one span of V + kW - 1 image elements, so the span is loaded once per kernel row
-        // (elements outside the image become the padding value) and every tap's run is cut out of it in registers.
-        // The choice is the same for all threads of a warp, so no warp runs two forms of the loop.
-        constexpr int kMaxSpanTaps = 7;
-        if (sW == 1 && dW == 1 && a.xCol == 1 && a.kW <= kMaxSpanTaps && a.out.dense && __all_sync(__activemask(), oneRow)) {
-            for (int kr = 0; kr < a.kH; kr++) {
-                const int ih = top + kr * dH;
-                const bool rowInside = (unsigned) ih < (unsigned) a.iH;
-                const T *row = in + ih * a.xRow + left;
-                T span[V + kMaxSpanTaps - 1];
-#pragma unroll
-                for (int t = 0; t < V + kMaxSpanTaps - 1; t++) {
-                    const bool ok = rowInside && t < V + a.kW - 1 && (unsigned) (left + t) < (unsigned) a.iW;
-                    span[t] = ok ? row[t] : pad;
-                }
-                T *dst = out + kr * a.zs[2] + p0;
-#pragma unroll
-                for (int kc = 0; kc < kMaxSpanTaps; kc++) {
-                    if (kc < a.kW) {
-                        Pack<T> pk;
-#pragma unroll
-                        for (int j = 0; j < V; j++) pk.v[j] = span[kc + j];
-                        store_pack(dst + kc * a.zs[3], pk);
-                    }
-                }
-            }
+        // Stride 1 or 2 and unit dilation along contiguous image rows (the usual convolutions): the kW taps of a
+        // kernel row read overlapping pieces of one span of (V - 1) * sW + kW image elements, so the span is loaded
+        // once per kernel row (elements outside the image become the padding value) and every tap's run is cut out
+        // of it in registers. The choice is the same for all threads of a warp, so no warp runs two forms of the loop.
+        if ((sW == 1 || sW == 2) && dW == 1 && a.xCol == 1 && a.kW <= kMaxSpanTaps && a.out.dense &&
+            __all_sync(__activemask(), oneRow)) {
+            if (sW == 1) im2col_span<T, 1>(in, out, a, top, left, dH, pad, p0);
+            else im2col_span<T, 2>(in, out, a, top, left, dH, pad, p0);
             return;
         }
         const bool interior = oneRow && a.out.dense && top >= 0 && top + (a.kH - 1) * dH < a.iH && left >= 0 &&
